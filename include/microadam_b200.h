@@ -1,0 +1,166 @@
+/*
+ * microadam_b200.h - C ABI of the B200 (sm_100a) MicroAdam step library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
+ * it is a cudaStream_t; NULL = the legacy default stream), enqueues its work on that stream
+ * without synchronising, and returns MAB_OK or a negative status; mab_last_error() then
+ * holds a message for the calling thread.  Nothing here allocates device memory, and there
+ * is no CPU implementation behind any of these calls: without a CUDA device they fail.
+ *
+ * bf16 data is passed as uint16_t bit patterns.  Element types of x / param / grad buffers
+ * are given by a dtype code (MAB_F32, MAB_BF16).
+ *
+ * Citations are to files of IST-DASLab/ISTA-DASLab-Optimizers; the functions that
+ * micro_adam.py imports from `ista_daslab_cuda_tools` and `ista_daslab_cuda_micro_adam` come
+ * from the separate package `ista-daslab-optimizers-cuda`, so each replacement cites the call
+ * site that fixes its meaning.
+ */
+#ifndef MICROADAM_B200_H
+#define MICROADAM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAB_OK               0
+#define MAB_ERR_BAD_ARG     (-1)  /* null pointer, negative size, misaligned buffer, bad enum     */
+#define MAB_ERR_UNSUPPORTED (-2)  /* dtype / geometry outside what the kernels were written for   */
+#define MAB_ERR_CUDA        (-3)  /* a CUDA runtime call or a kernel launch failed                */
+#define MAB_ERR_LIMIT       (-4)  /* size beyond a documented maximum                             */
+
+#define MAB_F32   0
+#define MAB_BF16  1
+
+#define MAB_K2D 0                 /* tools.py:12-14 CopyDirection.k2d */
+#define MAB_D2K 1                 /* tools.py:12-14 CopyDirection.d2k */
+
+#define MAB_MAX_WINDOW 128        /* largest m (window rows) the update kernels accept */
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* mab_last_error(void);
+
+/* ---- device queries ------------------------------------------------------------------- */
+
+/* Replaces ista_daslab_cuda_tools.get_sm_count() (micro_adam.py:40).  < 0 on failure. */
+int mab_get_sm_count(void);
+
+/* Replaces ista_daslab_cuda_tools.get_max_floats_for_shared_memory_per_thread_block()
+ * (micro_adam.py:43): opt-in dynamic shared memory per block / 4.  58112 on a B200, which makes
+ * d_block_size = 29056.  < 0 on failure. */
+int mab_get_max_floats_for_shared_memory_per_thread_block(void);
+
+/* ---- operator-for-operator replacements of the reference's native calls ------------------ */
+
+/* x += alpha * Qinv(error).  Replaces ista_daslab_cuda_micro_adam.asymm_block_quant_inv
+ * (micro_adam.py:190,267,298,313,322). */
+int mab_asymm_block_quant_inv(int64_t d, int64_t quant_block_size, const uint8_t* error,
+                              const uint16_t* min_vals, const uint16_t* max_vals,
+                              void* x, int x_dtype, float alpha, void* stream);
+
+/* error = Q(x; min_vals, max_vals), 4-bit codes, two per byte, even element in the high nibble.
+ * Replaces ista_daslab_cuda_micro_adam.asymm_block_quant (micro_adam.py:231,316). */
+int mab_asymm_block_quant(int64_t d, int64_t quant_block_size, uint8_t* error,
+                          const uint16_t* min_vals, const uint16_t* max_vals,
+                          const void* x, int x_dtype, void* stream);
+
+/* d2k: out[j] = inp[(j / k_block_size) * d_block_size + indices[j]]  (out has k elements);
+ * k2d: out[(j / k_block_size) * d_block_size + indices[j]] = inp[j]   (out has d elements).
+ * Replaces ista_daslab_cuda_tools.copy_values (micro_adam.py:202-209;
+ * sparse_mfac/sparse_core_mfac_w_ef.py:105-124). */
+int mab_copy_values(int64_t d, int64_t k, int64_t d_block_size, int64_t k_block_size,
+                    const int16_t* indices, const void* inp, int inp_dtype,
+                    void* out, int out_dtype, int direction, void* stream);
+
+/* x[(j / k_block_size) * d_block_size + indices[j]] = 0 for j < k.
+ * Replaces ista_daslab_cuda_tools.zerorize_block_components (micro_adam.py:214). */
+int mab_zerorize_block_components(void* x, int x_dtype, const int16_t* indices, int64_t d, int64_t k,
+                                  int64_t d_block_size, int64_t k_block_size, void* stream);
+
+/* out = Adam-style update from the sparse window (I, V), dense over d, 0 where no row touches.
+ * Replaces ista_daslab_cuda_micro_adam.compute_microadam_update (micro_adam.py:277-291).
+ * blocks / threads / carveout are accepted for signature compatibility and ignored. */
+int mab_compute_microadam_update(int blocks, int threads, int carveout, int64_t steps,
+                                 double beta1, double beta2, double eps,
+                                 int64_t d_block_size, int64_t k_block_size, int64_t d, int64_t m, int64_t k,
+                                 const int16_t* I, const uint16_t* V, void* out, int out_dtype, void* stream);
+
+/* indices_row[k] = per block of d_block_size elements of x, the in-block positions of the
+ * k_block_size_many (last short block: k_block_size_few) largest |x|, ties to the lower
+ * position, ascending.  Replaces the two torch.topk calls at micro_adam.py:193-200. */
+int mab_block_topk(int64_t d, int64_t d_block_size, int64_t k_block_size_many, int64_t k_block_size_few,
+                   const void* x, int x_dtype, int16_t* indices_row, void* stream);
+
+/* min_vals[b], max_vals[b] = bf16(min / max of x over quantisation block b), b = i / quant_block_size.
+ * Replaces the torch min/max calls of _update_quantization_statistics (micro_adam.py:217-226). */
+int mab_quant_stats(int64_t d, int64_t quant_block_size, uint16_t* min_vals, uint16_t* max_vals,
+                    const void* x, int x_dtype, void* stream);
+
+/* ---- fused step over a list of tensors ------------------------------------------------------ */
+
+/* One parameter tensor of the step.  State buffers have the shapes micro_adam.py:86-94 gives them. */
+typedef struct mab_tensor {
+    void*     param;             /* [d], param_dtype; updated in place                         */
+    const void* grad;            /* [d], grad_dtype; read only (the fused step leaves it as is) */
+    uint8_t*  error;             /* [ceil(d/2)] 4-bit error feedback                            */
+    uint16_t* min_vals;          /* [d / qbs + 1] bf16                                         */
+    uint16_t* max_vals;          /* [d / qbs + 1] bf16                                         */
+    int16_t*  I;                 /* [m, k] window indices                                      */
+    uint16_t* V;                 /* [m, k] window values, bf16                                 */
+    int64_t   d;
+    int64_t   k;                 /* row length of I and V                                       */
+    int32_t   d_block_size;      /* st['d_block_size']                                          */
+    int32_t   topk_full_blocks_count;
+    int32_t   k_block_size_many;
+    int32_t   k_block_size_few;
+    int32_t   param_dtype;
+    int32_t   grad_dtype;
+    int32_t   ring_index;        /* st['index']: row of I, V written this step                  */
+    int32_t   reserved0;
+    double    lr;                /* group['lr'] of this step                                    */
+    double    weight_decay;      /* group['weight_decay'] of this step                          */
+    /* filled in by the library */
+    float     decay_f32;         /* f32(1 - lr * weight_decay)                                  */
+    float     neg_lr_f32;        /* f32(-lr)                                                    */
+    int32_t   first_unit_a;      /* first work unit (top-k block) of this tensor in kernel A    */
+    int32_t   first_unit_b;      /* first work unit (block sub-range) of this tensor in kernel B */
+} mab_tensor;
+
+/* Scalars of one step, the same for every tensor. */
+typedef struct mab_step_args {
+    int64_t steps;               /* 1-based step counter (self.steps after the increment)        */
+    int32_t m;                   /* window rows                                                   */
+    int32_t quant_block_size;
+    float   alpha;               /* 0 <= alpha < 1                                                */
+    int32_t reserved0;
+    double  beta1, beta2, eps;
+} mab_step_args;
+
+/* Bytes of device workspace mab_fused_step needs for n_tensors tensors. */
+int64_t mab_fused_step_workspace_bytes(int n_tensors);
+
+/* 1 if the fused kernels cover this geometry (quant_block_size a power of two in [8, 128] that
+ * divides d_block_size, d_block_size <= 32768, supported dtypes, aligned pointers), else 0. */
+int mab_fused_supported(const mab_tensor* t, const mab_step_args* args);
+
+/* The whole step of micro_adam.py:146-328 (alpha >= 0) for n_tensors tensors in two kernels:
+ *   A  dequantise EF + add gradient, block top-k into row ring_index of I / V, zero the selected
+ *      entries, block min / max, requantise EF                      (micro_adam.py:190-231)
+ *   B  window -> Adam update, weight decay, alpha EF integration, parameter update, EF shrink
+ *                                                                   (micro_adam.py:234-235, 276-316)
+ * `tensors` is host memory; it is copied to `workspace` (device, >= workspace_bytes) on `stream`
+ * and its first_unit_* fields are overwritten.  Every tensor must satisfy mab_fused_supported. */
+int mab_fused_step(mab_tensor* tensors, int n_tensors, const mab_step_args* args,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The two halves of mab_fused_step on their own (same arguments). */
+int mab_fused_ef_topk_quant(mab_tensor* tensors, int n_tensors, const mab_step_args* args,
+                            void* workspace, int64_t workspace_bytes, void* stream);
+int mab_fused_window_adam_update(mab_tensor* tensors, int n_tensors, const mab_step_args* args,
+                                 void* workspace, int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MICROADAM_B200_H */

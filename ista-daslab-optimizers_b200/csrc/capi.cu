@@ -1,0 +1,177 @@
+// Host side of the C ABI: error reporting, device queries and the driver of the fused step.
+#include <math.h>
+#include <string.h>
+#include <vector>
+#include <algorithm>
+#include "common.cuh"
+#include "fused.cuh"
+#include "select.cuh"
+
+namespace mab {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    return MAB_ERR_CUDA;
+}
+
+static int device_attr(cudaDeviceAttr attr, const char* what) {
+    int dev = 0, v = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&v, attr, dev);
+    if (e != cudaSuccess) { cuda_fail(e, what); return -1; }
+    return v;
+}
+
+int device_sm_count() {
+    static thread_local int cached_dev = -1, cached = -1;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != cached_dev || cached < 0) {
+        cached = device_attr(cudaDevAttrMultiProcessorCount, "query SM count");
+        cached_dev = (cached < 0) ? -1 : dev;
+    }
+    return cached;
+}
+
+int device_max_optin_smem() { return device_attr(cudaDevAttrMaxSharedMemoryPerBlockOptin, "query shared memory per block"); }
+
+}  // namespace mab
+
+using namespace mab;
+
+extern "C" const char* mab_last_error(void) { return g_error; }
+
+extern "C" int mab_get_sm_count(void) { return device_sm_count(); }
+
+extern "C" int mab_get_max_floats_for_shared_memory_per_thread_block(void) {
+    const int bytes = device_max_optin_smem();
+    return bytes < 0 ? bytes : bytes / 4;
+}
+
+extern "C" int64_t mab_fused_step_workspace_bytes(int n_tensors) {
+    return (int64_t)std::max(n_tensors, 1) * (int64_t)sizeof(mab_tensor);
+}
+
+static bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// Why a tensor cannot take the fused path, or nullptr if it can.
+static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
+    if (!t || !a) return "null argument";
+    if (t->d <= 0) return "empty tensor";
+    if (!t->param || !t->grad || !t->error || !t->min_vals || !t->max_vals || !t->I || !t->V) return "null buffer";
+    if (t->param_dtype != MAB_F32 && t->param_dtype != MAB_BF16) return "param dtype is neither f32 nor bf16";
+    if (t->grad_dtype != MAB_F32 && t->grad_dtype != MAB_BF16) return "grad dtype is neither f32 nor bf16";
+    const int qbs = a->quant_block_size;
+    if (!is_pow2(qbs) || qbs < 8 || qbs > 128) return "quant_block_size is not a power of two in [8, 128]";
+    if (!(a->alpha >= 0.0f && a->alpha < 1.0f)) return "alpha outside [0, 1)";
+    if (a->m < 1 || a->m > MAB_MAX_WINDOW) return "window rows outside [1, MAB_MAX_WINDOW]";
+    if (t->d_block_size <= 0 || t->d_block_size > SEL_MAX_TILE) return "d_block_size outside (0, 32768]";
+    const int64_t nfull = t->topk_full_blocks_count;
+    const int64_t covered = nfull * t->d_block_size;
+    if (nfull < 0 || covered > t->d || t->d - covered >= t->d_block_size) return "block counts inconsistent with d";
+    const bool multi = covered < t->d ? nfull >= 1 : nfull > 1;
+    if (multi && t->d_block_size % qbs != 0) return "d_block_size is not a multiple of quant_block_size";
+    if (t->k_block_size_many < 1 || t->k_block_size_many > t->d_block_size) return "k_block_size_many out of range";
+    if ((covered < t->d) != (t->k_block_size_few > 0) || t->k_block_size_few > t->d - covered) return "k_block_size_few out of range";
+    if (t->k != nfull * t->k_block_size_many + t->k_block_size_few) return "k inconsistent with the block geometry";
+    if (nfull + 1 >= (int64_t)1 << 28) return "too many blocks";
+    if (t->ring_index < 0 || t->ring_index >= a->m) return "ring_index outside [0, m)";
+    const size_t pe = t->param_dtype == MAB_F32 ? 4 : 2, ge = t->grad_dtype == MAB_F32 ? 4 : 2;
+    if (!aligned_to(t->param, pe) || !aligned_to(t->grad, ge) || !aligned_to(t->min_vals, 2) ||
+        !aligned_to(t->max_vals, 2) || !aligned_to(t->I, 2) || !aligned_to(t->V, 2)) return "buffer not aligned to its element size";
+    return nullptr;
+}
+
+extern "C" int mab_fused_supported(const mab_tensor* t, const mab_step_args* args) {
+    return fused_obstacle(t, args) == nullptr ? 1 : 0;
+}
+
+enum { RUN_A = 1, RUN_B = 2 };
+
+static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void* workspace, int64_t workspace_bytes,
+                     void* stream, int what) {
+    MAB_REQUIRE(n >= 0, MAB_ERR_BAD_ARG, "fused step: n_tensors=%d", n);
+    if (n == 0) return MAB_OK;
+    MAB_REQUIRE(tensors && args && workspace, MAB_ERR_BAD_ARG, "fused step: null argument");
+    MAB_REQUIRE(workspace_bytes >= mab_fused_step_workspace_bytes(n), MAB_ERR_BAD_ARG,
+                "fused step: workspace of %lld bytes, %lld needed", (long long)workspace_bytes,
+                (long long)mab_fused_step_workspace_bytes(n));
+    MAB_REQUIRE(aligned_to(workspace, 16), MAB_ERR_BAD_ARG, "fused step: workspace must be 16-byte aligned");
+    MAB_REQUIRE(args->steps >= 1, MAB_ERR_BAD_ARG, "fused step: steps=%lld", (long long)args->steps);
+    for (int i = 0; i < n; ++i) {
+        const char* why = fused_obstacle(&tensors[i], args);
+        MAB_REQUIRE(why == nullptr, MAB_ERR_UNSUPPORTED, "fused step: tensor %d: %s", i, why);
+    }
+    if (device_sm_count() < 0) return MAB_ERR_CUDA;
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // Group tensors by (grad dtype, param dtype): each group is launched with its own kernel
+    // instantiation, in chunks whose unit prefix fits the kernels' shared-memory table.
+    std::vector<int> order(n);
+    for (int i = 0; i < n; ++i) order[i] = i;
+    auto key = [&](int i) { return tensors[i].grad_dtype * 2 + tensors[i].param_dtype; };
+    std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return key(x) < key(y); });
+
+    struct Chunk { int first, count, units_a, units_b, grad_dtype, param_dtype; };
+    std::vector<Chunk> chunks;
+    static thread_local std::vector<mab_tensor> staged;
+    staged.resize(n);
+    const int max_tensors = std::min(WIN_MAX_TENSORS, 512);
+    const int64_t unit_cap = (int64_t)1 << 30;
+    for (int pos = 0; pos < n;) {
+        Chunk c = {pos, 0, 0, 0, tensors[order[pos]].grad_dtype, tensors[order[pos]].param_dtype};
+        int64_t ua = 0, ub = 0;
+        while (pos < n && c.count < max_tensors && key(order[pos]) == c.grad_dtype * 2 + c.param_dtype) {
+            mab_tensor& t = tensors[order[pos]];
+            const int64_t na = units_a_of(t), nb = units_b_of(t);
+            if (c.count > 0 && (ua + na > unit_cap || ub + nb > unit_cap)) break;
+            MAB_REQUIRE(na <= unit_cap && nb <= unit_cap, MAB_ERR_LIMIT, "fused step: tensor %d has too many blocks", order[pos]);
+            t.decay_f32 = (float)(1.0 - t.lr * t.weight_decay);
+            t.neg_lr_f32 = (float)(-t.lr);
+            t.first_unit_a = (int32_t)ua;
+            t.first_unit_b = (int32_t)ub;
+            staged[pos] = t;
+            ua += na; ub += nb;
+            ++c.count; ++pos;
+        }
+        c.units_a = (int)ua; c.units_b = (int)ub;
+        chunks.push_back(c);
+    }
+    MAB_CUDA_TRY(cudaMemcpyAsync(workspace, staged.data(), (size_t)n * sizeof(mab_tensor), cudaMemcpyHostToDevice, s));
+    const mab_tensor* dev = reinterpret_cast<const mab_tensor*>(workspace);
+
+    if (what & RUN_A)
+        for (const Chunk& c : chunks)
+            if (int rc = launch_ef_topk_quant(dev + c.first, c.count, c.units_a, c.grad_dtype, args->quant_block_size, s)) return rc;
+    if (what & RUN_B) {
+        WindowArgs wa;
+        if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
+                                      args->quant_block_size)) return rc;
+        for (const Chunk& c : chunks)
+            if (int rc = launch_window_step(dev + c.first, c.count, c.units_b, c.param_dtype, wa, s)) return rc;
+    }
+    return MAB_OK;
+}
+
+extern "C" int mab_fused_step(mab_tensor* tensors, int n_tensors, const mab_step_args* args, void* workspace,
+                              int64_t workspace_bytes, void* stream) {
+    return fused_run(tensors, n_tensors, args, workspace, workspace_bytes, stream, RUN_A | RUN_B);
+}
+
+extern "C" int mab_fused_ef_topk_quant(mab_tensor* tensors, int n_tensors, const mab_step_args* args, void* workspace,
+                                       int64_t workspace_bytes, void* stream) {
+    return fused_run(tensors, n_tensors, args, workspace, workspace_bytes, stream, RUN_A);
+}
+
+extern "C" int mab_fused_window_adam_update(mab_tensor* tensors, int n_tensors, const mab_step_args* args, void* workspace,
+                                            int64_t workspace_bytes, void* stream) {
+    return fused_run(tensors, n_tensors, args, workspace, workspace_bytes, stream, RUN_B);
+}

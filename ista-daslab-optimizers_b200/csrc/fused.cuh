@@ -1,0 +1,32 @@
+// Declarations shared by the two fused kernels and the host-side step driver.
+#pragma once
+#include "common.cuh"
+#include "window.cuh"
+
+namespace mab {
+
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Index of the tensor whose unit range contains `unit`: largest i with first[i] <= unit.
+// first[0..n] is ascending with first[n] = total units; tensors without units repeat a value.
+__device__ __forceinline__ int find_tensor(const int* first, int n, int unit) {
+    int lo = 0, hi = n;                      // invariant: first[lo] <= unit < first[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (first[mid] <= unit) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// window_adam.cu
+int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double beta2, double eps, float alpha, int qbs);
+int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int total_units, int param_dtype,
+                       const WindowArgs& a, cudaStream_t s);
+int units_b_of(const mab_tensor& t);
+
+// ef_topk_quant.cu
+int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
+                         int qbs, cudaStream_t s);
+int units_a_of(const mab_tensor& t);
+
+}  // namespace mab

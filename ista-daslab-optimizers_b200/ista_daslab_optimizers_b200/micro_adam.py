@@ -1,0 +1,281 @@
+"""MicroAdam on B200: the reference's `torch.optim` interface over the sm_100a kernels.
+
+Drop-in for `ista_daslab_optimizers.MicroAdam` (ista_daslab_optimizers/micro_adam/micro_adam.py:13-328):
+same constructor, same per-parameter state keys, dtypes and shapes (micro_adam.py:61-94), same
+order of sub-steps.  Differences a caller can observe:
+
+* the step runs as two fused kernels over all tensors (plus the operator-level kernels for
+  geometries the fused kernels do not cover), not ~25 launches per tensor;
+* top-k ties go to the lower index and indices are stored in ascending order
+  (torch.topk(sorted=False) at micro_adam.py:193-200 leaves both unspecified);
+* on the fused path `p.grad` is left untouched (the reference uses it as scratch and leaves the
+  update in it, micro_adam.py:276-313); on the operator-level path it is scratch as in the reference;
+* alpha == -2 (micro_adam.py:238-273) is rejected with NotImplementedError;
+* `state_dict()` also carries the step counter (the reference loses it, micro_adam.py:35).
+
+There is no CPU path: parameters must live on a CUDA device and the native library must be built.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _native as N
+from .tools import CopyDirection, block_split, get_first_device
+
+
+class _Entry:
+    """One flat slice of one parameter that this process updates."""
+    __slots__ = ('p', 'st', 'lo', 'hi', 'fused', 'group')
+
+    def __init__(self, p, st, lo, hi, group):
+        self.p, self.st, self.lo, self.hi, self.fused, self.group = p, st, lo, hi, False, group
+
+
+class MicroAdam(torch.optim.Optimizer):
+    def __init__(self, params, m, lr, quant_block_size, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0,
+                 eps=1e-8, *, d_block_size: Optional[int] = None, use_fused: bool = True):
+        defaults = dict(lr=lr, weight_decay=weight_decay, eps=eps, alpha=alpha)
+        super().__init__(params, defaults)
+
+        assert (0 <= alpha < 1) or alpha == -2, 'Alpha must be in the [0, 1) interval or -2'   # micro_adam.py:18
+        if alpha == -2:
+            raise NotImplementedError('alpha == -2 (densify the update with the quantisation error, '
+                                      'micro_adam.py:238-273) has no B200 kernel yet')
+        if not (1 <= int(m) <= N.MAB_MAX_WINDOW):
+            raise ValueError(f'm must be in [1, {N.MAB_MAX_WINDOW}]')
+
+        self.m = int(m)
+        self.lr = lr
+        self.quant_block_size = int(quant_block_size)
+        self.k_init = k_init
+        self.alpha = alpha
+        self.weight_decay = weight_decay
+        self.beta1 = betas[0]
+        self.beta2 = betas[1]
+        self.eps = eps
+
+        self.densify_update_using_ef = (self.alpha > 0)
+        self.densify_update_using_quant_error = False
+
+        self.model_size = sum(p.numel() for group in self.param_groups for p in group['params'])
+
+        self.steps = 0
+        self.log_interval = 100
+        self.device = get_first_device()
+        self.shared_memory_carveout = 100
+        self.threads = 512
+        self.use_fused = bool(use_fused)
+
+        N.load()   # fail here, loudly, if the native library is not built
+        if d_block_size is None:
+            self.blocks = N.get_sm_count() * int(100 / self.shared_memory_carveout)                  # micro_adam.py:40
+            self.max_floats = N.get_max_floats_for_shared_memory_per_thread_block()                    # micro_adam.py:43
+            self.d_block_size = self.max_floats // 2 // int(100 / self.shared_memory_carveout)       # micro_adam.py:44
+        else:
+            self.blocks = N.get_sm_count()
+            self.d_block_size = int(d_block_size)
+            self.max_floats = 2 * self.d_block_size
+
+        self.dict_size_count: Dict[int, int] = {}                                                     # micro_adam.py:52-57
+        for group in self.param_groups:
+            for p in group['params']:
+                self.dict_size_count[p.numel()] = 1 + self.dict_size_count.get(p.numel(), 0)
+
+        self._entries: List[_Entry] = []
+        self._entries_key: Optional[tuple] = None
+        self._descs = None
+        self._workspace: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------------------ state
+    def _slice_of(self, p) -> Optional[Tuple[int, int]]:
+        """Flat element range of `p` this process owns.  The whole tensor here; a sharded subclass
+        returns a sub-range cut on top-k block boundaries, or None."""
+        return 0, p.numel()
+
+    def _initialize_parameter_state(self, p, lr, wd, lo: int = 0, hi: Optional[int] = None):
+        """micro_adam.py:61-94, for the flat slice [lo, hi) of p (the whole tensor by default)."""
+        hi = p.numel() if hi is None else hi
+        layer_size = hi - lo
+        st = self.state[p]
+        dev = p.device
+
+        st['blocks'] = max(1, int(math.floor(self.blocks * p.numel() * self.dict_size_count.get(p.numel(), 1) / self.model_size)))
+        st['lr'] = lr
+        st['weight_decay'] = wd
+        st['d'] = layer_size
+
+        st['d_block_size'] = layer_size if layer_size < self.d_block_size else self.d_block_size
+        st['topk_full_blocks_count'], st['d_index_topk'] = block_split(st['d'], st['d_block_size'])
+        st['k_block_size_many'] = int(math.ceil(st['d_block_size'] * self.k_init))
+        st['k_block_size_few'] = int(math.ceil((st['d'] - st['d_index_topk']) * self.k_init))
+        st['k_index'] = st['topk_full_blocks_count'] * st['k_block_size_many']
+        st['k'] = st['k_block_size_many'] * st['topk_full_blocks_count'] + st['k_block_size_few']
+
+        st['index'] = 0
+        st['I'] = torch.zeros(self.m, st['k'], dtype=torch.int16, device=dev)
+        st['V'] = torch.zeros(self.m, st['k'], dtype=torch.bfloat16, device=dev)
+
+        st['quant_full_blocks_count'], st['d_index_quant'] = block_split(st['d'], self.quant_block_size)
+        st['error'] = torch.zeros(int(math.ceil(st['d'] / 2)), dtype=torch.uint8, device=dev)
+        st['min_vals'] = torch.zeros(st['quant_full_blocks_count'] + 1, dtype=torch.bfloat16, device=dev)
+        st['max_vals'] = torch.zeros(st['quant_full_blocks_count'] + 1, dtype=torch.bfloat16, device=dev)
+        if (lo, hi) != (0, p.numel()):
+            st['shard_lo'], st['shard_hi'] = lo, hi
+
+    def state_dict(self):
+        sd = super().state_dict()
+        sd['steps'] = self.steps
+        return sd
+
+    def load_state_dict(self, state_dict):
+        state_dict = dict(state_dict)
+        steps = state_dict.pop('steps', None)
+        super().load_state_dict(state_dict)
+        if steps is not None:
+            self.steps = int(steps)
+        self._entries_key = None
+
+    # ------------------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self, closure=None):
+        self.steps += 1                                                                                # micro_adam.py:98
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+
+        self._refresh_entries()
+        fused = [e for e in self._entries if e.fused]
+        generic = [e for e in self._entries if not e.fused]
+        if fused:
+            self._fused_step(fused)
+        for e in generic:
+            self._generic_update(e)
+        self._after_update()
+        return loss
+
+    def _after_update(self):
+        """Hook for subclasses (the sharded optimizer gathers the updated parameters here)."""
+
+    def _refresh_entries(self):
+        active = []
+        for gi, group in enumerate(self.param_groups):
+            for p in group['params']:
+                if p.grad is None:                                                                     # micro_adam.py:125
+                    continue
+                sl = self._slice_of(p)
+                if sl is None or sl[0] == sl[1]:
+                    continue
+                if not p.is_cuda:
+                    raise N.NativeError(f'parameter on {p.device}: MicroAdam for B200 has no CPU implementation')
+                if p.grad.is_sparse:
+                    raise N.NativeError('sparse gradients are not supported')
+                active.append((p, sl, gi))
+        key = tuple((id(p), sl, p.dtype, p.grad.dtype) for p, sl, _ in active)
+        if key == self._entries_key:
+            return
+        entries = []
+        for p, (lo, hi), gi in active:
+            st = self.state[p]
+            if len(st) == 0 or 'I' not in st:                                                          # micro_adam.py:158-160
+                group = self.param_groups[gi]
+                self._initialize_parameter_state(p, group['lr'], group.get('weight_decay', self.weight_decay), lo, hi)
+            if st['I'].dtype != torch.int16:                                                           # micro_adam.py:175-178
+                st['I'] = st['I'].to(torch.int16)
+            if st['d'] != hi - lo:
+                raise RuntimeError(f'state of a parameter holds d={st["d"]} but the slice to update has {hi - lo} elements')
+            entries.append(_Entry(p, st, lo, hi, gi))
+        self._entries = entries
+        self._entries_key = key
+        self._descs = None
+        if self.use_fused and entries:
+            args = self._step_args()
+            for e in entries:
+                d = N.MabTensor()
+                self._fill_static(d, e)
+                self._fill_dynamic(d, e)
+                e.fused = bool(N.load().mab_fused_supported(ctypes.byref(d), ctypes.byref(args)))
+
+    def _step_args(self) -> N.MabStepArgs:
+        a = N.MabStepArgs()
+        a.steps, a.m, a.quant_block_size = self.steps, self.m, self.quant_block_size
+        a.alpha = float(self.alpha)
+        a.beta1, a.beta2, a.eps = float(self.beta1), float(self.beta2), float(self.eps)
+        return a
+
+    @staticmethod
+    def _fill_static(d: N.MabTensor, e: _Entry):
+        st = e.st
+        d.error, d.min_vals, d.max_vals = st['error'].data_ptr(), st['min_vals'].data_ptr(), st['max_vals'].data_ptr()
+        d.I, d.V = st['I'].data_ptr(), st['V'].data_ptr()
+        d.d, d.k = st['d'], st['k']
+        d.d_block_size = st['d_block_size']
+        d.topk_full_blocks_count = st['topk_full_blocks_count'] if st['d_index_topk'] > 0 else 0
+        d.k_block_size_many, d.k_block_size_few = st['k_block_size_many'], st['k_block_size_few']
+        d.param_dtype, d.grad_dtype = N.dtype_code(e.p), N.dtype_code(e.p.grad)
+
+    def _fill_dynamic(self, d: N.MabTensor, e: _Entry):
+        p, g = e.p, e.p.grad
+        if not (p.is_contiguous() and g.is_contiguous()):
+            raise N.NativeError('parameters and gradients must be contiguous (the reference requires p.grad.view(-1))')
+        group = self.param_groups[e.group]
+        d.param = p.data_ptr() + e.lo * p.element_size()
+        d.grad = g.data_ptr() + e.lo * g.element_size()
+        d.ring_index = e.st['index']
+        d.lr = float(group['lr'])                                                                      # micro_adam.py:121
+        d.weight_decay = float(group.get('weight_decay', self.weight_decay))                           # micro_adam.py:122
+
+    def _fused_step(self, entries: List[_Entry]):
+        lib = N.load()
+        n = len(entries)
+        if self._descs is None or len(self._descs) != n:
+            self._descs = (N.MabTensor * n)()
+            for d, e in zip(self._descs, entries):
+                self._fill_static(d, e)
+        for d, e in zip(self._descs, entries):
+            self._fill_dynamic(d, e)
+            e.st['index'] = (e.st['index'] + 1) % self.m                                               # micro_adam.py:211
+        device = entries[0].p.device
+        need = lib.mab_fused_step_workspace_bytes(n)
+        if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
+            self._workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        args = self._step_args()
+        with torch.cuda.device(device):
+            N.check(lib.mab_fused_step(self._descs, n, ctypes.byref(args), self._workspace.data_ptr(),
+                                       self._workspace.numel(), N.current_stream(device)), 'mab_fused_step')
+
+    def _generic_update(self, e: _Entry):
+        """The reference's update_step (micro_adam.py:146-328) on the operator-level kernels."""
+        p, st = e.p, e.st
+        group = self.param_groups[e.group]
+        lr, wd = group['lr'], group.get('weight_decay', self.weight_decay)
+        pf = p.data.view(-1)[e.lo:e.hi]
+        grad = p.grad.view(-1)[e.lo:e.hi]
+        d, qbs = st['d'], self.quant_block_size
+        dbs, k_many, k_few, k = st['d_block_size'], st['k_block_size_many'], st['k_block_size_few'], st['k']
+        index, I, V = st['index'], st['I'], st['V']
+        error, min_vals, max_vals = st['error'], st['min_vals'], st['max_vals']
+
+        N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1.0)                          # :190
+        N.block_topk(d, dbs, k_many, k_few, grad, I[index])                                            # :193-200
+        N.copy_values(d, k, dbs, k_many, I[index], grad, V[index], CopyDirection.d2k.value)            # :202-209
+        st['index'] = (index + 1) % self.m                                                             # :211
+        N.zerorize_block_components(grad, I[index], d, k, dbs, k_many)                                 # :214
+        N.quant_stats(d, qbs, min_vals, max_vals, grad)                                                # :217-228
+        N.asymm_block_quant(d, qbs, error, min_vals, max_vals, grad)                                   # :231
+        if wd > 0:
+            pf.mul_(1 - lr * wd)                                                                       # :234-235
+        N.compute_microadam_update(st['blocks'], self.threads, self.shared_memory_carveout, self.steps, self.beta1,
+                                   self.beta2, self.eps, dbs, k_many, d, self.m, k, I, V, grad)        # :276-291
+        if self.densify_update_using_ef:
+            N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, self.alpha)               # :298
+        pf.add_(grad, alpha=-lr)                                                                       # :304
+        if self.densify_update_using_ef:                                                               # :311-316
+            grad.zero_()
+            N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1 - self.alpha)
+            N.quant_stats(d, qbs, min_vals, max_vals, grad)
+            N.asymm_block_quant(d, qbs, error, min_vals, max_vals, grad)

@@ -1,0 +1,198 @@
+"""Seeded parity cases shared by the golden-vector generator and the tests.
+
+A case fixes shapes, element type, hyper-parameters and the number of steps; parameters and
+per-step gradients come from ista_daslab_optimizers_b200.synthetic, so every machine sees the
+same bits.  `run_case` drives any implementation exposing the small adapter interface below and
+returns, per step and tensor, a digest of the bit-exact state plus a sample of the parameters.
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Sequence, Tuple
+
+import torch
+
+from ista_daslab_optimizers_b200 import synthetic as S
+
+
+@dataclass
+class Case:
+    name: str
+    shapes: Sequence[Tuple[int, ...]]
+    dtype: torch.dtype
+    steps: int
+    m: int = 10
+    lr: float = 1e-3
+    k_init: float = 0.01
+    qbs: int = 64
+    alpha: float = 0.0
+    weight_decay: float = 0.0
+    betas: Tuple[float, float] = (0.9, 0.999)
+    eps: float = 1e-8
+    grad_sigma: float = 1e-3
+    grad_kind: str = 'normal'          # 'normal' | 'student_t3_ties'
+    zero_tensors: Sequence[int] = ()   # tensors that start at zero with an all-zero first gradient
+    seed: int = 0
+    d_block_size: int = 29056
+
+    def params(self) -> List[torch.Tensor]:
+        out = []
+        for i, s in enumerate(self.shapes):
+            n = int(torch.Size(s).numel())
+            if i in self.zero_tensors:
+                out.append(torch.zeros(s, dtype=self.dtype))
+            else:
+                out.append(S.normal_tensor(self.seed, 100 + i, n, 0.02, self.dtype).view(s))
+        return out
+
+    def grads(self, step: int) -> List[torch.Tensor]:
+        """Gradients of 0-based `step`."""
+        out = []
+        for i, s in enumerate(self.shapes):
+            n = int(torch.Size(s).numel())
+            if i in self.zero_tensors and step == 0:
+                out.append(torch.zeros(s, dtype=self.dtype))
+                continue
+            stream = 10_000 * (step + 1) + i
+            if self.grad_kind == 'normal':
+                g = S.normal_tensor(self.seed + 1, stream, n, self.grad_sigma)
+            else:
+                g = S.round_to_8_mantissa_bits(S.student_t3_tensor(self.seed + 1, stream, n, self.grad_sigma))
+            out.append(g.to(self.dtype).view(s))
+        return out
+
+
+CASES: Dict[str, Case] = {c.name: c for c in [
+    # BASELINE config 1: one fp32 parameter [1048576], 12 steps so that the m=10 window wraps
+    Case('c1_fp32_1m', [(1048576,)], torch.float32, 12),
+    # small mixed shapes, heavy-tailed gradients with exact ties, a zero tensor, alpha and weight decay
+    Case('mixed_fp32_alpha', [(7,), (65,), (64, 64), (333, 77), (100001,), (256, 256, 3, 3), (4096,)], torch.float32, 12,
+         alpha=0.5, weight_decay=0.1, grad_kind='student_t3_ties', zero_tensors=(2, 6)),
+    # bf16 parameters and gradients with weight decay (the Llama configuration's element type)
+    Case('bf16_wd', [(4096,), (1024, 256), (100001,), (29056 * 2 + 640,)], torch.bfloat16, 12, weight_decay=0.1,
+         grad_sigma=1e-4),
+    Case('bf16_alpha', [(4096,), (70000,)], torch.bfloat16, 6, alpha=0.25, weight_decay=0.1, grad_kind='student_t3_ties'),
+    # quantisation blocks that straddle top-k blocks: only the operator-level kernels apply
+    Case('qbs_100000', [(100001,), (300, 200)], torch.float32, 3, qbs=100000, alpha=0.5),
+    Case('qbs_32_m5', [(65536,), (1000,)], torch.float32, 7, qbs=32, m=5, k_init=0.05),
+]}
+
+
+def _h(*tensors: torch.Tensor) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        t = t.detach().cpu().contiguous()
+        h.update(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.uint8 else t.numpy().tobytes())
+    return h.hexdigest()
+
+
+def state_digest(I_row, V_row, error, min_vals, max_vals, d: int, qbs: int) -> str:
+    """Digest of everything that must match bit for bit after a step.  Statistics slot d // qbs is
+    compared only when the tensor has a short last block (it is never written otherwise)."""
+    used = (d + qbs - 1) // qbs
+    return _h(I_row, V_row, error, min_vals[:used], max_vals[:used])
+
+
+PARAM_SAMPLES = 32
+
+
+def param_sample(p: torch.Tensor) -> List[float]:
+    """Up to PARAM_SAMPLES evenly strided elements, as float32."""
+    flat = p.detach().float().cpu().view(-1)
+    return flat[::max(1, flat.numel() // PARAM_SAMPLES)][:PARAM_SAMPLES].tolist()
+
+
+@dataclass
+class Trace:
+    digests: List[List[str]] = field(default_factory=list)       # [step][tensor]
+    samples: List[List[List[float]]] = field(default_factory=list)  # [step][tensor][i]
+
+
+class Adapter:
+    """What run_case needs from an implementation."""
+
+    def step(self, grads: List[torch.Tensor]) -> None: ...
+    def state(self, i: int) -> dict: ...       # keys: I, V, error, min_vals, max_vals, index (after the step), d
+    def param(self, i: int) -> torch.Tensor: ...
+
+
+def run_case(case: Case, make: Callable[[Case, List[torch.Tensor]], Adapter]) -> Trace:
+    params = case.params()
+    impl = make(case, params)
+    tr = Trace()
+    for t in range(case.steps):
+        impl.step(case.grads(t))
+        dg, sm = [], []
+        for i in range(len(case.shapes)):
+            st = impl.state(i)
+            row = (st['index'] - 1) % case.m
+            dg.append(state_digest(st['I'][row], st['V'][row], st['error'], st['min_vals'], st['max_vals'], st['d'], case.qbs))
+            sm.append(param_sample(impl.param(i)))
+        tr.digests.append(dg)
+        tr.samples.append(sm)
+    return tr
+
+
+class OracleAdapter(Adapter):
+    def __init__(self, case: Case, params):
+        from oracle.microadam_oracle import MicroAdamOracle
+        self.params = params
+        self.opt = MicroAdamOracle(params, m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init,
+                                   alpha=case.alpha, betas=case.betas, weight_decay=case.weight_decay, eps=case.eps,
+                                   d_block_size=case.d_block_size)
+
+    def step(self, grads):
+        self.opt.step([g.clone() for g in grads])
+
+    def state(self, i):
+        st = self.opt.state[i]
+        return dict(I=st['I'], V=st['V'], error=st['error'], min_vals=st['min_vals'], max_vals=st['max_vals'],
+                    index=st['index'], d=st['geo'].d)
+
+    def param(self, i):
+        return self.params[i]
+
+
+class ReferenceAdapter(Adapter):
+    """The unmodified reference class on CPU (needs a reference checkout)."""
+
+    def __init__(self, case: Case, params):
+        from oracle.reference_harness import load_reference_microadam
+        Ref = load_reference_microadam(max_floats=2 * case.d_block_size)
+        self.params = [torch.nn.Parameter(p) for p in params]
+        self.opt = Ref(self.params, m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init, alpha=case.alpha,
+                       betas=case.betas, weight_decay=case.weight_decay, eps=case.eps)
+
+    def step(self, grads):
+        for p, g in zip(self.params, grads):
+            p.grad = g.clone()
+        self.opt.step()
+
+    def state(self, i):
+        return self.opt.state[self.params[i]]
+
+    def param(self, i):
+        return self.params[i].data
+
+
+class CudaAdapter(Adapter):
+    """The shipped optimizer on cuda:0."""
+
+    def __init__(self, case: Case, params, use_fused=True):
+        from ista_daslab_optimizers_b200 import MicroAdam
+        self.params = [torch.nn.Parameter(p.cuda()) for p in params]
+        self.opt = MicroAdam(self.params, m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init,
+                             alpha=case.alpha, betas=case.betas, weight_decay=case.weight_decay, eps=case.eps,
+                             d_block_size=case.d_block_size, use_fused=use_fused)
+
+    def step(self, grads):
+        for p, g in zip(self.params, grads):
+            p.grad = g.cuda()
+        self.opt.step()
+
+    def state(self, i):
+        return self.opt.state[self.params[i]]
+
+    def param(self, i):
+        return self.params[i].data

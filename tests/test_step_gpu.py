@@ -1,0 +1,93 @@
+"""The whole optimizer step on the GPU against the CPU oracle and the golden vectors."""
+import struct
+
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def decode_samples(hexstr):
+    return [struct.unpack('>f', bytes.fromhex(hexstr[i:i + 8]))[0] for i in range(0, len(hexstr), 8)]
+
+
+def check_trace(case, tr, ref_digests, ref_samples):
+    assert tr.digests == ref_digests, [(s, i) for s, (a, b) in enumerate(zip(tr.digests, ref_digests))
+                                       for i, (x, y) in enumerate(zip(a, b)) if x != y][:5]
+    # parameters: rel 1e-5 (fp32) / 1e-2 (bf16), the tolerance the path's specification states
+    tol = 1e-5 if case.dtype == torch.float32 else 1e-2
+    for mine, theirs in zip(tr.samples, ref_samples):
+        for a, b in zip(mine, theirs):
+            torch.testing.assert_close(torch.tensor(a), torch.tensor(b), rtol=tol, atol=1e-9)
+
+
+@pytest.mark.parametrize('use_fused', [True, False], ids=['fused', 'operators'])
+@pytest.mark.parametrize('name', list(cases.CASES))
+def test_step_matches_golden_and_oracle(name, use_fused, golden):
+    case = cases.CASES[name]
+    tr = cases.run_case(case, lambda c, p: cases.CudaAdapter(c, p, use_fused=use_fused))
+    g = golden['cases'][name]
+    check_trace(case, tr, g['digests'], [[decode_samples(s) for s in step] for step in g['samples']])
+    ref = cases.run_case(case, cases.OracleAdapter)
+    check_trace(case, tr, ref.digests, ref.samples)
+
+
+def test_fused_path_is_taken_when_supported():
+    case = cases.CASES['bf16_wd']
+    ad = cases.CudaAdapter(case, case.params())
+    ad.step(case.grads(0))
+    assert all(e.fused for e in ad.opt._entries)
+    case = cases.CASES['qbs_100000']
+    ad = cases.CudaAdapter(case, case.params())
+    ad.step(case.grads(0))
+    assert not any(e.fused for e in ad.opt._entries)
+
+
+def test_fused_step_leaves_grad_untouched_and_is_deterministic():
+    case = cases.CASES['mixed_fp32_alpha']
+    runs = []
+    for _ in range(2):
+        ad = cases.CudaAdapter(case, case.params())
+        for t in range(3):
+            grads = case.grads(t)
+            ad.step(grads)
+            for p, g in zip(ad.params, grads):
+                assert torch.equal(p.grad.cpu(), g)
+        runs.append([p.detach().cpu().clone() for p in ad.params])
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+
+
+def test_grad_none_and_param_groups():
+    from ista_daslab_optimizers_b200 import MicroAdam
+    p1 = torch.nn.Parameter(torch.randn(5000, device='cuda'))
+    p2 = torch.nn.Parameter(torch.randn(300, 70, device='cuda'))
+    p3 = torch.nn.Parameter(torch.randn(64, device='cuda'))
+    opt = MicroAdam([{'params': [p1], 'lr': 1e-2}, {'params': [p2, p3], 'weight_decay': 0.5}], m=4, lr=1e-3, quant_block_size=64)
+    before = [p.detach().clone() for p in (p1, p2, p3)]
+    p1.grad = torch.randn_like(p1)
+    p2.grad = torch.randn_like(p2)
+    opt.step()
+    assert not torch.equal(p1, before[0]) and not torch.equal(p2, before[1]) and torch.equal(p3, before[2])
+    assert len(opt.state[p3]) == 0 and opt.state[p1]['index'] == 1
+    # weight decay of the second group: untouched entries shrink by exactly 1 - lr * wd
+    untouched = (p2.detach() - before[1] * (1 - 1e-3 * 0.5)).abs() < 1e-7
+    assert untouched.float().mean() > 0.9
+    sd = opt.state_dict()
+    assert sd['steps'] == 1
+    opt2 = MicroAdam([{'params': [p1], 'lr': 1e-2}, {'params': [p2, p3], 'weight_decay': 0.5}], m=4, lr=1e-3, quant_block_size=64)
+    opt2.load_state_dict(sd)
+    assert opt2.steps == 1 and torch.equal(opt2.state[p1]['I'], opt.state[p1]['I'])
+
+
+def test_rejects_alpha_minus_two_and_cpu_params():
+    from ista_daslab_optimizers_b200 import MicroAdam, _native
+    with pytest.raises(NotImplementedError):
+        MicroAdam([torch.nn.Parameter(torch.zeros(8, device='cuda'))], m=10, lr=1e-3, quant_block_size=64, alpha=-2)
+    p = torch.nn.Parameter(torch.zeros(8))
+    p.grad = torch.zeros(8)
+    opt = MicroAdam([p], m=10, lr=1e-3, quant_block_size=64)
+    with pytest.raises(_native.NativeError):
+        opt.step()
