@@ -1,0 +1,192 @@
+"""ZeRO-1 style sharding of the MicroAdam step over the GPUs of one node.
+
+The reference has no counterpart (its only multi-GPU provision is to size the state lazily so
+that FSDP shards work, micro_adam.py:158-160).  Every top-k block of a tensor is an independent
+unit of the step: its window rows, error-feedback codes and block statistics depend on nothing
+outside the block.  So the flattened parameter list is cut into `world_size` contiguous runs of
+top-k blocks, balanced by element count; a rank keeps optimizer state only for its run, updates
+only those parameters, and the updated ranges are then exchanged so that every rank again holds
+all parameters (one all-gather with unequal pieces).
+
+A cut inside a tensor is made only on a top-k block boundary that is also a quantisation block
+boundary, so a rank's slice of a tensor behaves exactly like a smaller tensor of its own and the
+sharded result is bit-identical to the unsharded one.  Tensors where that is impossible
+(d_block_size not a multiple of quant_block_size, or a single block) are never cut.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .micro_adam import MicroAdam
+
+
+@dataclass(frozen=True)
+class Piece:
+    """Flat element range [lo, hi) of parameter `index`, owned by `rank`."""
+    rank: int
+    index: int
+    lo: int
+    hi: int
+
+
+def plan_shards(numels: Sequence[int], d_block_size: int, quant_block_size: int, world_size: int) -> List[Piece]:
+    """Cuts the parameter list into world_size contiguous runs of top-k blocks.
+
+    A block goes to rank floor(midpoint * world_size / total), where midpoint is the position of
+    the block's middle in the concatenation of all tensors: ranks are non-decreasing along the
+    list, every rank's share is within one block of total / world_size, and the plan depends only
+    on the sizes, so every rank computes the same one.
+    """
+    total = sum(numels)
+    pieces: List[Piece] = []
+    if total == 0:
+        return pieces
+    start = 0
+    for idx, d in enumerate(numels):
+        if d == 0:
+            continue
+        splittable = d > d_block_size and d_block_size % quant_block_size == 0
+        if not splittable:
+            r = min(world_size - 1, (2 * start + d) * world_size // (2 * total))
+            pieces.append(Piece(r, idx, 0, d))
+        else:
+            nblocks = -(-d // d_block_size)
+            # first block of rank r: smallest b with (2*(start + b*dbs) + len_b) * W >= 2*total*r
+            cuts = [0]
+            for r in range(1, world_size):
+                # with full-size blocks: 2*start + (2b+1)*dbs >= 2*total*r / W
+                num = 2 * total * r - world_size * (2 * start + d_block_size)
+                b = 0 if num <= 0 else -(-num // (2 * d_block_size * world_size))
+                cuts.append(min(max(b, cuts[-1]), nblocks))
+            cuts.append(nblocks)
+            # the last block may be short: its midpoint is earlier than the formula assumes, which can
+            # only move it to an earlier rank; recheck it explicitly
+            last_lo = (nblocks - 1) * d_block_size
+            last_rank = min(world_size - 1, (2 * (start + last_lo) + (d - last_lo)) * world_size // (2 * total))
+            for r in range(world_size):
+                b0, b1 = cuts[r], cuts[r + 1]
+                if r > last_rank and b1 == nblocks and b0 < nblocks:
+                    b0 = b1 = nblocks                      # handled by last_rank below
+                if b0 < b1:
+                    lo, hi = b0 * d_block_size, min(d, b1 * d_block_size)
+                    if b1 == nblocks and r != last_rank:
+                        hi = last_lo                        # the short block belongs to last_rank
+                    if lo < hi:
+                        pieces.append(Piece(r, idx, lo, hi))
+            if not any(p.index == idx and p.hi == d for p in pieces):
+                # the short block alone (or appended to last_rank's run)
+                prev = [p for p in pieces if p.index == idx and p.rank == last_rank]
+                if prev and prev[-1].hi == last_lo:
+                    pieces[pieces.index(prev[-1])] = Piece(last_rank, idx, prev[-1].lo, d)
+                else:
+                    pieces.append(Piece(last_rank, idx, last_lo, d))
+        start += d
+    pieces.sort(key=lambda p: (p.index, p.lo))
+    return pieces
+
+
+class ShardedMicroAdam(MicroAdam):
+    """MicroAdam whose state and update are sharded over the ranks of `process_group`.
+
+    Every rank constructs it over the same full parameter list and, each step, provides the
+    gradients of (at least) its own slices in `p.grad`.  After `step()` every rank holds all updated
+    parameters.  `rank` / `world_size` may be given explicitly without a process group to run one
+    shard on its own (no exchange), which is how the sharded arithmetic is tested on one GPU.
+    """
+
+    def __init__(self, params, m, lr, quant_block_size, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0,
+                 eps=1e-8, *, process_group=None, rank: Optional[int] = None, world_size: Optional[int] = None,
+                 gather: bool = True, **kw):
+        super().__init__(params, m, lr, quant_block_size, k_init, alpha, betas, weight_decay, eps, **kw)
+        self.process_group = process_group
+        if rank is None or world_size is None:
+            if not (dist.is_available() and dist.is_initialized()):
+                raise RuntimeError('ShardedMicroAdam needs torch.distributed initialised, or explicit rank and world_size')
+            rank, world_size = dist.get_rank(process_group), dist.get_world_size(process_group)
+        self.rank, self.world_size = int(rank), int(world_size)
+        self.gather = gather and self.world_size > 1
+        self._all_params = [p for g in self.param_groups for p in g['params']]
+        self.plan = plan_shards([p.numel() for p in self._all_params], self.d_block_size, self.quant_block_size,
+                                self.world_size)
+        self._my_slice: Dict[int, Tuple[int, int]] = {}
+        for pc in self.plan:
+            if pc.rank == self.rank:
+                assert id(self._all_params[pc.index]) not in self._my_slice
+                self._my_slice[id(self._all_params[pc.index])] = (pc.lo, pc.hi)
+        self._gather_views = None
+        self.last_gather_bytes = 0
+
+    def _slice_of(self, p):
+        return self._my_slice.get(id(p))
+
+    # ---------------------------------------------------------------------------- exchange
+    def _build_gather_views(self):
+        """Per rank, the flat views it owns; views adjacent in memory (parameters that are slices
+        of one flat buffer) are merged, so that a flat model needs one piece per rank."""
+        per_rank: List[List[torch.Tensor]] = [[] for _ in range(self.world_size)]
+        last: List[Optional[Tuple[int, int, int, torch.dtype]]] = [None] * self.world_size   # storage ptr, begin, end, dtype
+        for pc in self.plan:
+            p = self._all_params[pc.index]
+            if not p.is_contiguous():
+                raise RuntimeError('sharded parameters must be contiguous')
+            es = p.element_size()
+            sp = p.untyped_storage().data_ptr()
+            begin = p.data_ptr() + pc.lo * es
+            end = p.data_ptr() + pc.hi * es
+            prev = last[pc.rank]
+            if prev is not None and prev[0] == sp and prev[2] == begin and prev[3] == p.dtype:
+                begin = prev[1]
+                per_rank[pc.rank].pop()
+            n = (end - begin) // es
+            view = torch.empty(0, dtype=p.dtype, device=p.device).set_(p.untyped_storage(), (begin - sp) // es, (n,))
+            per_rank[pc.rank].append(view)
+            last[pc.rank] = (sp, begin, end, p.dtype)
+        return per_rank
+
+    def _after_update(self):
+        if not self.gather:
+            return
+        if self._gather_views is None:
+            self._gather_views = self._build_gather_views()
+        views = self._gather_views
+        group = self.process_group
+        counts = {len(v) for v in views}
+        self.last_gather_bytes = sum(v.numel() * v.element_size() for r, vs in enumerate(views) if r != self.rank for v in vs)
+        backend = dist.get_backend(group)
+        if counts == {1} and backend == 'nccl' and len({v[0].dtype for v in views}) == 1:
+            # one piece per rank (flat model): a single all-gather with unequal pieces, in place
+            dist.all_gather([v[0] for v in views], views[self.rank][0], group=group)
+            return
+        works = []
+        for r, vs in enumerate(views):
+            src = dist.get_global_rank(group, r) if group is not None else r
+            for v in vs:
+                works.append(dist.broadcast(v, src=src, group=group, async_op=True))
+        for w in works:
+            w.wait()
+
+
+def flatten_parameters(params: Sequence[torch.nn.Parameter]) -> torch.Tensor:
+    """Re-homes the parameters (same dtype and device) as consecutive views of one flat buffer, each
+    starting on a 256-byte boundary, and returns the buffer.  With flat parameters the exchange after
+    a sharded step is one collective instead of one per tensor."""
+    params = list(params)
+    dtype, device = params[0].dtype, params[0].device
+    es = params[0].element_size()
+    align = 256 // es
+    offsets, total = [], 0
+    for p in params:
+        if p.dtype != dtype or p.device != device:
+            raise ValueError('flatten_parameters needs one dtype and one device')
+        offsets.append(total)
+        total += -(-p.numel() // align) * align
+    flat = torch.zeros(total, dtype=dtype, device=device)
+    for p, off in zip(params, offsets):
+        view = flat[off:off + p.numel()].view(p.shape)
+        view.copy_(p.data)
+        p.data = view
+    return flat
