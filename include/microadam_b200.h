@@ -41,6 +41,10 @@ extern "C" {
 /* Message of the last failure on the calling thread ("" if none). */
 const char* mab_last_error(void);
 
+/* Number of kernels this library has launched in this process (all threads, all devices).
+ * No counterpart in the reference; it lets a benchmark state how many launches it timed. */
+int64_t mab_kernel_launch_count(void);
+
 /* ---- device queries ------------------------------------------------------------------- */
 
 /* Replaces ista_daslab_cuda_tools.get_sm_count() (micro_adam.py:40).  < 0 on failure. */

@@ -1,6 +1,7 @@
 // Host side of the C ABI: error reporting, device queries and the driver of the fused step.
 #include <math.h>
 #include <string.h>
+#include <atomic>
 #include <vector>
 #include <algorithm>
 #include "common.cuh"
@@ -10,6 +11,9 @@
 namespace mab {
 
 static thread_local char g_error[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -48,6 +52,8 @@ int device_max_optin_smem() { return device_attr(cudaDevAttrMaxSharedMemoryPerBl
 using namespace mab;
 
 extern "C" const char* mab_last_error(void) { return g_error; }
+
+extern "C" int64_t mab_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int mab_get_sm_count(void) { return device_sm_count(); }
 

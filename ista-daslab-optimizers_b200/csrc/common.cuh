@@ -14,7 +14,8 @@ namespace mab {
 void set_error(const char* fmt, ...);
 int  cuda_fail(cudaError_t e, const char* what);   // records and returns MAB_ERR_CUDA
 int  device_sm_count();                            // cached per device, < 0 on failure
-int  device_max_optin_smem();                      // cached per device, < 0 on failure
+int  device_max_optin_smem();                      // < 0 on failure
+void count_launch();                               // bumps the process-wide kernel launch counter
 
 #define MAB_CUDA_TRY(expr)                                                     \
     do { cudaError_t _e = (expr); if (_e != cudaSuccess) return mab::cuda_fail(_e, #expr); } while (0)

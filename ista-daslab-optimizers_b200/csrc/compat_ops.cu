@@ -154,7 +154,7 @@ static int grid_for(int64_t work_items, int threads) {
 using namespace mab;
 
 #define MAB_CHECK_LAUNCH(name)                                                     \
-    do { cudaError_t _e = cudaGetLastError(); if (_e != cudaSuccess) return cuda_fail(_e, name); } while (0)
+    do { mab::count_launch(); cudaError_t _e = cudaGetLastError(); if (_e != cudaSuccess) return cuda_fail(_e, name); } while (0)
 
 static int check_dtype(int dt, const char* what) {
     MAB_REQUIRE(dt == MAB_F32 || dt == MAB_BF16, MAB_ERR_UNSUPPORTED, "%s: dtype code %d is neither MAB_F32 nor MAB_BF16", what, dt);

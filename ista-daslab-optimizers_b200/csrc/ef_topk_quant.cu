@@ -159,6 +159,7 @@ int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total
         ef_topk_quant_kernel<float><<<grid, SEL_THREADS, 0, s>>>(dev_tensors, n_tensors, total_units, qbs, lanes);
     else
         ef_topk_quant_kernel<uint16_t><<<grid, SEL_THREADS, 0, s>>>(dev_tensors, n_tensors, total_units, qbs, lanes);
+    count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_kernel launch");
     return MAB_OK;

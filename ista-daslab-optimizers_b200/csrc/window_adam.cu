@@ -207,6 +207,7 @@ static int launch_window(const mab_tensor* dev_tensors, const mab_tensor* single
         MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WIN_SMEM_BYTES));
         kern<<<grid, WIN_THREADS, WIN_SMEM_BYTES, s>>>(dev_tensors, n_tensors, total_units, a);
     }
+    count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "window_adam_kernel launch");
     return MAB_OK;

@@ -54,6 +54,7 @@ class MabStepArgs(Structure):
 # name -> (restype, argtypes); every symbol include/microadam_b200.h declares
 SIGNATURES = {
     'mab_last_error': (c_char_p, []),
+    'mab_kernel_launch_count': (c_int64, []),
     'mab_get_sm_count': (c_int, []),
     'mab_get_max_floats_for_shared_memory_per_thread_block': (c_int, []),
     'mab_asymm_block_quant_inv': (c_int, [c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
@@ -119,6 +120,10 @@ def current_stream(device) -> int:
 # ------------------------------------------------------------------------------------------------
 # Operator-level calls with the argument order of the reference's native modules
 # (micro_adam.py:40,43,190,202-209,214,231,277-291), on torch CUDA tensors.
+
+def kernel_launch_count() -> int:
+    return load().mab_kernel_launch_count()
+
 
 def get_sm_count() -> int:
     v = load().mab_get_sm_count()

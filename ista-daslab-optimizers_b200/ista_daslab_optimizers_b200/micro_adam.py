@@ -89,6 +89,8 @@ class MicroAdam(torch.optim.Optimizer):
         self._entries_key: Optional[tuple] = None
         self._descs = None
         self._workspace: Optional[torch.Tensor] = None
+        # set to a list to have every fused step append [start, between the two kernels, end] CUDA events
+        self.kernel_events: Optional[list] = None
 
     # ------------------------------------------------------------------------------ state
     def _slice_of(self, p) -> Optional[Tuple[int, int]]:
@@ -156,6 +158,10 @@ class MicroAdam(torch.optim.Optimizer):
         for e in generic:
             self._generic_update(e)
         self._after_update()
+        if self.kernel_events and len(self.kernel_events[-1]) == 3:
+            ev = torch.cuda.Event(enable_timing=True)   # end of whatever _after_update enqueued
+            ev.record()
+            self.kernel_events[-1].append(ev)
         return loss
 
     def _after_update(self):
@@ -244,9 +250,22 @@ class MicroAdam(torch.optim.Optimizer):
         if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
             self._workspace = torch.empty(need, dtype=torch.uint8, device=device)
         args = self._step_args()
+        ws, ws_bytes = self._workspace.data_ptr(), self._workspace.numel()
         with torch.cuda.device(device):
-            N.check(lib.mab_fused_step(self._descs, n, ctypes.byref(args), self._workspace.data_ptr(),
-                                       self._workspace.numel(), N.current_stream(device)), 'mab_fused_step')
+            stream = N.current_stream(device)
+            if self.kernel_events is None:
+                N.check(lib.mab_fused_step(self._descs, n, ctypes.byref(args), ws, ws_bytes, stream), 'mab_fused_step')
+            else:
+                # the same two kernels through their own entry points, with CUDA events between them
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                ev[0].record()
+                N.check(lib.mab_fused_ef_topk_quant(self._descs, n, ctypes.byref(args), ws, ws_bytes, stream),
+                        'mab_fused_ef_topk_quant')
+                ev[1].record()
+                N.check(lib.mab_fused_window_adam_update(self._descs, n, ctypes.byref(args), ws, ws_bytes, stream),
+                        'mab_fused_window_adam_update')
+                ev[2].record()
+                self.kernel_events.append(ev)
 
     def _generic_update(self, e: _Entry):
         """The reference's update_step (micro_adam.py:146-328) on the operator-level kernels."""
