@@ -126,14 +126,14 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
     auto key = [&](int i) { return tensors[i].grad_dtype * 2 + tensors[i].param_dtype; };
     std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return key(x) < key(y); });
 
-    struct Chunk { int first, count, units_a, units_b, grad_dtype, param_dtype; };
+    struct Chunk { int first, count, units_a, units_b, grad_dtype, param_dtype, max_k; };
     std::vector<Chunk> chunks;
     static thread_local std::vector<mab_tensor> staged;
     staged.resize(n);
     const int max_tensors = std::min(WIN_MAX_TENSORS, 512);
     const int64_t unit_cap = (int64_t)1 << 30;
     for (int pos = 0; pos < n;) {
-        Chunk c = {pos, 0, 0, 0, tensors[order[pos]].grad_dtype, tensors[order[pos]].param_dtype};
+        Chunk c = {pos, 0, 0, 0, tensors[order[pos]].grad_dtype, tensors[order[pos]].param_dtype, 0};
         int64_t ua = 0, ub = 0;
         while (pos < n && c.count < max_tensors && key(order[pos]) == c.grad_dtype * 2 + c.param_dtype) {
             mab_tensor& t = tensors[order[pos]];
@@ -146,6 +146,7 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
             t.first_unit_b = (int32_t)ub;
             staged[pos] = t;
             ua += na; ub += nb;
+            c.max_k = std::max(c.max_k, std::max(t.k_block_size_many, t.k_block_size_few));
             ++c.count; ++pos;
         }
         c.units_a = (int)ua; c.units_b = (int)ub;
@@ -161,8 +162,10 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
         WindowArgs wa;
         if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
                                       args->quant_block_size)) return rc;
-        for (const Chunk& c : chunks)
-            if (int rc = launch_window_step(dev + c.first, c.count, c.units_b, c.param_dtype, wa, s)) return rc;
+        for (const Chunk& c : chunks) {
+            const int max_entries = (int)std::min<int64_t>((int64_t)wa.rows * c.max_k, INT32_MAX);
+            if (int rc = launch_window_step(dev + c.first, c.count, c.units_a, c.units_b, max_entries, c.param_dtype, wa, s)) return rc;
+        }
     }
     return MAB_OK;
 }
