@@ -55,6 +55,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
               '-Xcompiler', '-fPIC', '-I', INCLUDE]
     if verbose:
         common += ['-Xptxas', '-v']
+    if os.environ.get('MAB_STATS'):
+        common += ['-DMAB_STATS']       # development-only tile statistics
     procs = []
     for src in sources():
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + '.o')

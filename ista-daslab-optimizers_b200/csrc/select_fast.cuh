@@ -1,0 +1,239 @@
+// Fast exact top-k for a tile held in registers (layout of select.cuh).
+//
+// The bisection in select.cuh costs 32 passes over all 32 values of every thread.  Here the
+// full-width work is two passes:
+//   1. a lower bound T_lo of the k-th largest key is found on per-thread (or per-octet) maxima
+//      only: if at least k groups have a maximum >= T_lo, at least k elements do.  The search
+//      walks T_lo up until between k and ~1.5 k groups qualify, one barrier per probe, starting
+//      from the previous tile's bound;
+//   2. the elements >= T_lo ("candidates", typically 1.2-2 k of them) are compacted into shared
+//      memory with one block scan.
+// The exact k-th key is then found among the candidates alone by a 256-bin radix histogram over
+// [T_lo, max], refined until the bin holding the k-th key has at most 32 members, which one warp
+// ranks (key descending, position ascending), or until the bin is a single key value, whose
+// members are ties resolved by position through the bitmap scan of select.cuh.
+// The result is delivered exactly like the slow path's: sel_bm / sel_before in SelectSmem.
+// Any tile that does not fit (too many candidates, k larger than the number of groups, ...)
+// returns false with no side effect the slow path cares about, and the caller bisects.
+#pragma once
+#include "common.cuh"
+#include "select.cuh"
+
+namespace mab {
+
+#ifdef MAB_STATS
+// Development-only tile statistics (compiled in with -DMAB_STATS): [0] fast tiles, [1..6] tiles sent
+// to the slow path by reason, [7] lower-bound probes, [8] candidates, [9] histogram levels.
+__device__ unsigned long long g_stats[16];
+#define MAB_STAT(i, v) do { if (threadIdx.x == 0) atomicAdd(&g_stats[i], (unsigned long long)(v)); } while (0)
+#else
+#define MAB_STAT(i, v) do { } while (0)
+#endif
+
+constexpr int FS_CAND_CAP = 4096;
+constexpr int FS_OCTET_LEVEL_K = 384;     // above this k the bound is searched on octet maxima
+
+struct FastSelSmem {
+    float    cand_val[FS_CAND_CAP];       // signed value
+    uint16_t cand_pos[FS_CAND_CAP];       // position in the tile; bit 15 set once selected
+    int      hist[256];
+    int      member[32];                  // candidate indices of the members of the final bin
+    int      rot[64];                     // rotating counters of the octet-level probes
+    int      ctrl[8];                     // broadcast slots
+    int      n_member;
+    int      kmax;
+};
+
+__device__ __forceinline__ int fs_key(float v) { return __float_as_int(fabsf(v)); }
+
+// Probes on group maxima until count(groups with max >= T_lo) lies in [k, ~1.5 k].  Returns the
+// bound as key bits (0 = none found).  `guess` carries the bound of the previous tile.
+__device__ __forceinline__ int fs_lower_bound(const float (&omax)[SEL_OCTETS], float tmax, int k, bool octets, int kmax,
+                                              int& guess, FastSelSmem& fs) {
+    const int ti = __float_as_int(tmax);
+    int oi[SEL_OCTETS];
+#pragma unroll
+    for (int j = 0; j < SEL_OCTETS; ++j) oi[j] = __float_as_int(omax[j]);
+    if (octets) {
+        if (threadIdx.x < 64) fs.rot[threadIdx.x] = 0;
+        __syncthreads();
+    }
+    const int accept = k + (k >> 1) + 8;
+    int lo = 0, hi = kmax + 1;                              // count(lo) >= k (trivially), count(hi) = 0 < k
+    int g = (guess > 0 && guess <= kmax) ? guess : max(1, kmax - (2 << 23));
+    int step = 1 << 20;
+    bool have_lo = false, have_hi = false;
+    for (int it = 0; it < 64; ++it) {
+        int c;
+        if (!octets) {
+            c = __syncthreads_count(ti >= g);
+        } else {
+            int mine = 0;
+#pragma unroll
+            for (int j = 0; j < SEL_OCTETS; ++j) mine += (oi[j] >= g) ? 1 : 0;
+            mine = __reduce_add_sync(0xffffffffu, mine);
+            if (lane_id() == 0 && mine) atomicAdd(&fs.rot[it], mine);
+            __syncthreads();
+            c = *reinterpret_cast<volatile int*>(&fs.rot[it]);
+        }
+        MAB_STAT(7, 1);
+        if (c >= k) { lo = g; have_lo = true; if (c <= accept) break; }
+        else { hi = g; have_hi = true; }
+        if (hi - lo <= 1) break;
+        if (have_lo && have_hi) g = lo + ((hi - lo) >> 1);
+        else if (have_lo) { g = (int)min((int64_t)lo + step, (int64_t)hi - 1); step <<= 1; }
+        else { g = (int)max((int64_t)hi - step, (int64_t)1); step <<= 1; }
+    }
+    guess = lo;
+    return have_lo ? lo : 0;
+}
+
+// Exact selection of the k largest keys among the tile's elements.  On success (true) sm.sel_bm /
+// sm.sel_before hold the result, candidates flagged with bit 15 of cand_pos are the selected
+// ones, n_cand their number.  Uniform: every thread gets the same return value.
+__device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], const float (&omax)[SEL_OCTETS], int n, int k,
+                                            int& guess, SelectSmem& sm, FastSelSmem& fs, int& n_cand) {
+    const int t = threadIdx.x, lane = lane_id(), warp = warp_id();
+    float tmax = fmaxf(fmaxf(omax[0], omax[1]), fmaxf(omax[2], omax[3]));
+
+    // block maximum key
+    if (t == 0) fs.kmax = 0;
+    __syncthreads();
+    {
+        const int wm = __reduce_max_sync(0xffffffffu, __float_as_int(tmax));
+        if (lane == 0 && wm) atomicMax(&fs.kmax, wm);
+    }
+    __syncthreads();
+    const int kmax = fs.kmax;
+    if (kmax == 0 || kmax >= 0x7f800000) { MAB_STAT(1, 1); return false; }   // all zero, or non-finite values: slow path
+
+    const bool octets = k > FS_OCTET_LEVEL_K;
+    const int groups = octets ? (n + 7) / 8 : min(SEL_THREADS, (n + 7) / 8);
+    if (k > groups) { MAB_STAT(2, 1); return false; }
+    const int T_lo = fs_lower_bound(omax, tmax, k, octets, kmax, guess, fs);
+    if (T_lo <= 0) { MAB_STAT(3, 1); return false; }
+    const float T_lo_f = __int_as_float(T_lo);
+
+    // ---- compact the candidates --------------------------------------------------------------
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < SEL_OCTETS; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mine += (fabsf(a[j][e]) >= T_lo_f) ? 1 : 0;
+    int C;
+    int at = block_exclusive_scan(mine, sm.scan, C);
+    if (C > FS_CAND_CAP) { MAB_STAT(4, 1); return false; }   // uniform: C is a block-wide value
+    if (mine) {
+#pragma unroll
+        for (int j = 0; j < SEL_OCTETS; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (fabsf(a[j][e]) >= T_lo_f) {
+                    fs.cand_val[at] = a[j][e];
+                    fs.cand_pos[at] = (uint16_t)(((j * SEL_THREADS + t) << 3) | e);
+                    ++at;
+                }
+    }
+    n_cand = C;
+    MAB_STAT(8, C);
+
+    // ---- exact k-th key among the candidates: radix histogram levels ---------------------------
+    int r_lo = T_lo, r_hi = kmax, k_rem = k, R = C, sh = 31;
+    for (int level = 0; level < 5; ++level) {
+        const unsigned W1 = (unsigned)(r_hi - r_lo);          // width - 1
+        sh = W1 < 256 ? 0 : (32 - __clz(W1)) - 8;
+        if (t < 256) fs.hist[t] = 0;
+        __syncthreads();                                       // also orders the candidate writes above
+        for (int i = t; i < C; i += SEL_THREADS) {
+            const int key = fs_key(fs.cand_val[i]);
+            if (key >= r_lo && key <= r_hi) atomicAdd(&fs.hist[(key - r_lo) >> sh], 1);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // suffix sums from the top bin: lane l owns bins [8 l, 8 l + 8)
+            int h[8], s = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { h[i] = fs.hist[lane * 8 + i]; s += h[i]; }
+            int suf = s;                                       // inclusive suffix over lanes >= lane
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_down_sync(0xffffffffu, suf, o);
+                if (lane + o < 32) suf += v;
+            }
+            const unsigned ok = __ballot_sync(0xffffffffu, suf >= k_rem);
+            const int owner = 31 - __clz(ok);                  // highest lane whose suffix reaches k_rem (ok != 0: total >= k_rem)
+            if (lane == owner) {
+                int above = suf - s;                           // candidates in bins above this lane's
+                int b = 7;
+                while (above + h[b] < k_rem) { above += h[b]; --b; }
+                fs.ctrl[0] = lane * 8 + b;                     // bin holding the k_rem-th largest
+                fs.ctrl[1] = k_rem - above;                    // how many of its members are selected
+                fs.ctrl[2] = h[b];
+            }
+        }
+        __syncthreads();
+        const int b_star = fs.ctrl[0];
+        k_rem = fs.ctrl[1];
+        R = fs.ctrl[2];
+        const int n_lo = r_lo + (b_star << sh);
+        r_hi = (int)min((int64_t)r_hi, (int64_t)n_lo + ((int64_t)1 << sh) - 1);
+        r_lo = n_lo;
+        MAB_STAT(9, 1);
+        if (R <= 32 || sh == 0) break;
+    }
+    if (R > 32 && sh != 0) { MAB_STAT(5, 1); return false; } // cannot happen within 5 levels of 8 bits; stay safe
+
+    // ---- members of the final bin: rank them (<= 32) or treat them as ties of one key -------------
+    const bool by_rank = R <= 32;
+    if (t == 0) fs.n_member = 0;
+    sm.gt_bm[t] = 0u;
+    sm.tie_bm[t] = 0u;
+    __syncthreads();
+    for (int i = t; i < C; i += SEL_THREADS) {
+        const int key = fs_key(fs.cand_val[i]);
+        const uint32_t pos = fs.cand_pos[i];
+        if (key > r_hi) {
+            fs.cand_pos[i] = (uint16_t)(pos | 0x8000u);
+            atomicOr(&sm.gt_bm[pos >> 5], 1u << (pos & 31));
+        } else if (key >= r_lo) {
+            if (by_rank) fs.member[atomicAdd(&fs.n_member, 1)] = i;
+            else atomicOr(&sm.tie_bm[pos >> 5], 1u << (pos & 31));
+        }
+    }
+    __syncthreads();
+    int need_ties = 0;
+    if (by_rank) {
+        if (warp == 0) {
+            const int nm = fs.n_member;                        // == R
+            const int idx = lane < nm ? fs.member[lane] : -1;
+            const int key = idx >= 0 ? fs_key(fs.cand_val[idx]) : -1;
+            const int pos = idx >= 0 ? (int)fs.cand_pos[idx] : 0x7fffffff;
+            int rank = 0;
+            for (int o = 0; o < nm; ++o) {
+                const int ok = __shfl_sync(0xffffffffu, key, o), op = __shfl_sync(0xffffffffu, pos, o);
+                rank += (ok > key || (ok == key && op < pos)) ? 1 : 0;
+            }
+            if (idx >= 0 && rank < k_rem) {
+                fs.cand_pos[idx] = (uint16_t)(pos | 0x8000);
+                atomicOr(&sm.gt_bm[pos >> 5], 1u << (pos & 31));
+            }
+        }
+    } else {
+        need_ties = k_rem;                                     // r_lo == r_hi: every member has the k-th key
+    }
+    resolve_selection(need_ties, sm);                          // starts with a barrier
+    if (!by_rank) {
+        // flag the ties that made it
+        for (int i = t; i < C; i += SEL_THREADS) {
+            const uint32_t pos = fs.cand_pos[i];
+            if (!(pos & 0x8000u) && fs_key(fs.cand_val[i]) == r_lo && (sm.sel_bm[pos >> 5] >> (pos & 31)) & 1u)
+                fs.cand_pos[i] = (uint16_t)(pos | 0x8000u);
+        }
+        __syncthreads();
+    }
+    MAB_STAT(0, 1);
+    if (!by_rank) MAB_STAT(6, 1);
+    return true;
+}
+
+}  // namespace mab
