@@ -45,6 +45,11 @@ const char* mab_last_error(void);
  * No counterpart in the reference; it lets a benchmark state how many launches it timed. */
 int64_t mab_kernel_launch_count(void);
 
+/* 1 if a kernel of this library on the current device ever gave up a (bounded) wait for the copy
+ * engine and returned early, 0 if not, < 0 on failure.  Synchronises with the device.  A non-zero
+ * value means the step it happened in is incomplete.  No counterpart in the reference. */
+int mab_device_error(void);
+
 /* ---- device queries ------------------------------------------------------------------- */
 
 /* Replaces ista_daslab_cuda_tools.get_sm_count() (micro_adam.py:40).  < 0 on failure. */

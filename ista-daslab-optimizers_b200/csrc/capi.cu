@@ -126,14 +126,14 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
     auto key = [&](int i) { return tensors[i].grad_dtype * 2 + tensors[i].param_dtype; };
     std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return key(x) < key(y); });
 
-    struct Chunk { int first, count, units_a, units_b, grad_dtype, param_dtype, max_k; };
+    struct Chunk { int first, count, units_a, units_b, grad_dtype, param_dtype, max_k, max_dbs; };
     std::vector<Chunk> chunks;
     static thread_local std::vector<mab_tensor> staged;
     staged.resize(n);
     const int max_tensors = std::min(WIN_MAX_TENSORS, 512);
     const int64_t unit_cap = (int64_t)1 << 30;
     for (int pos = 0; pos < n;) {
-        Chunk c = {pos, 0, 0, 0, tensors[order[pos]].grad_dtype, tensors[order[pos]].param_dtype, 0};
+        Chunk c = {pos, 0, 0, 0, tensors[order[pos]].grad_dtype, tensors[order[pos]].param_dtype, 0, 0};
         int64_t ua = 0, ub = 0;
         while (pos < n && c.count < max_tensors && key(order[pos]) == c.grad_dtype * 2 + c.param_dtype) {
             mab_tensor& t = tensors[order[pos]];
@@ -147,6 +147,7 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
             staged[pos] = t;
             ua += na; ub += nb;
             c.max_k = std::max(c.max_k, std::max(t.k_block_size_many, t.k_block_size_few));
+            c.max_dbs = std::max(c.max_dbs, t.d_block_size);
             ++c.count; ++pos;
         }
         c.units_a = (int)ua; c.units_b = (int)ub;
@@ -157,7 +158,7 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
 
     if (what & RUN_A)
         for (const Chunk& c : chunks)
-            if (int rc = launch_ef_topk_quant(dev + c.first, c.count, c.units_a, c.grad_dtype, args->quant_block_size, s)) return rc;
+            if (int rc = launch_ef_topk_quant(dev + c.first, c.count, c.units_a, c.grad_dtype, args->quant_block_size, c.max_dbs, s)) return rc;
     if (what & RUN_B) {
         WindowArgs wa;
         if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,

@@ -11,12 +11,27 @@
 #include "select.cuh"
 #include "select_fast.cuh"
 #include "codec_fast.cuh"
+#include "async_copy.cuh"
 #include "fused.cuh"
 
 namespace mab {
 
 constexpr int A_MAX_TENSORS = 512;
 
+// 8 staged elements in shared memory (16-byte aligned) as floats.
+__device__ __forceinline__ void staged_octet(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void staged_octet(const uint16_t* p, float (&v)[8]) {
+    const uint4 a = reinterpret_cast<const uint4*>(p)[0];
+    v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
+    v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
+    v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
+    v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
+}
+
+// 8 elements of the gradient in global memory (read-only path) as floats.
 template <typename TG> struct GradOctet;
 template <> struct GradOctet<float> {
     __device__ __forceinline__ static void load(const float* p, float (&v)[8], bool vec, int n) {
@@ -44,73 +59,189 @@ template <> struct GradOctet<uint16_t> {
     }
 };
 
+// Set when a wait on the copy engine gave up (no launch spins for ever); read by mab_device_error().
+__device__ int g_copy_timeout;
+
+// Where a tile lives and whether the copy engine can stage it: whole octets and quantisation
+// blocks only, sources aligned for 16-byte bulk copies (4 bytes for the statistics).
+template <typename TG>
+struct TileRef {
+    const TG* g; const uint8_t* ef; const uint16_t* mn; const uint16_t* mx;   // first element / byte / statistic of the tile
+    int n, k; bool staged; int stat_skip;                                      // stat_skip: 0/1 entries copied before the tile's first
+};
+
+template <typename TG>
+__device__ __forceinline__ TileRef<TG> tile_ref(const mab_tensor& T, int blk, int qshift) {
+    TileRef<TG> r;
+    const int dbs = T.d_block_size;
+    const int64_t base = (int64_t)blk * dbs;
+    r.n = (int)min((int64_t)dbs, T.d - base);
+    r.k = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
+    r.g = reinterpret_cast<const TG*>(T.grad) + base;
+    r.ef = T.error + (base >> 1);
+    const int64_t qb0 = base >> qshift;
+    r.mn = T.min_vals + qb0;
+    r.mx = T.max_vals + qb0;
+    r.stat_skip = (int)(qb0 & 1);
+    r.staged = (r.n & 31) == 0 && (r.n & ((1 << qshift) - 1)) == 0 && aligned16(r.g) && aligned16(r.ef) &&
+               ((reinterpret_cast<uintptr_t>(T.min_vals) | reinterpret_cast<uintptr_t>(T.max_vals)) & 3) == 0;
+    return r;
+}
+
+// Shared-memory staging area of one tile, carved from the dynamic allocation.
+template <typename TG>
+struct Stage {
+    TG* g; uint32_t* ef; uint16_t* mn; uint16_t* mx;
+    __device__ Stage(unsigned char* raw, int stage_elems, int qshift) {
+        const int g_bytes = (stage_elems * (int)sizeof(TG) + 127) & ~127;
+        const int ef_bytes = ((stage_elems >> 1) + 127) & ~127;
+        const int st_bytes = ((((stage_elems >> qshift) + 4) * 2) + 15) & ~15;
+        g = reinterpret_cast<TG*>(raw);
+        ef = reinterpret_cast<uint32_t*>(raw + g_bytes);
+        mn = reinterpret_cast<uint16_t*>(raw + g_bytes + ef_bytes);
+        mx = reinterpret_cast<uint16_t*>(raw + g_bytes + ef_bytes + st_bytes);
+    }
+    static int bytes(int stage_elems, int qshift) {
+        const int g_bytes = (stage_elems * (int)sizeof(TG) + 127) & ~127;
+        const int ef_bytes = ((stage_elems >> 1) + 127) & ~127;
+        const int st_bytes = ((((stage_elems >> qshift) + 4) * 2) + 15) & ~15;
+        return g_bytes + ef_bytes + 2 * st_bytes;
+    }
+};
+
+// Starts the copies of a staged tile: thread 0 arms the barrier and issues the bulk copies of the
+// gradient and the codes in 16 KB pieces; the statistics (a few hundred bf16) go through cp.async.
+template <typename TG>
+__device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG>& st, uint64_t* bar, int qshift) {
+    if (threadIdx.x == 0) {
+        const uint32_t gb = (uint32_t)r.n * (uint32_t)sizeof(TG), eb = (uint32_t)r.n >> 1;
+        mbar_arrive_expect_tx(bar, gb + eb);
+        for (uint32_t off = 0; off < gb; off += 16384)
+            bulk_g2s(reinterpret_cast<unsigned char*>(st.g) + off, reinterpret_cast<const unsigned char*>(r.g) + off, min(16384u, gb - off), bar);
+        for (uint32_t off = 0; off < eb; off += 16384)
+            bulk_g2s(reinterpret_cast<unsigned char*>(st.ef) + off, r.ef + off, min(16384u, eb - off), bar);
+    }
+    const int words = (((r.n >> qshift) + r.stat_skip) + 1) >> 1;      // 4-byte words covering the tile's statistics
+    const uint32_t* mn_src = reinterpret_cast<const uint32_t*>(r.mn - r.stat_skip);
+    const uint32_t* mx_src = reinterpret_cast<const uint32_t*>(r.mx - r.stat_skip);
+    for (int i = threadIdx.x; i < words; i += SEL_THREADS) {
+        cp_async_4(reinterpret_cast<uint32_t*>(st.mn) + i, mn_src + i);
+        cp_async_4(reinterpret_cast<uint32_t*>(st.mx) + i, mx_src + i);
+    }
+    cp_async_commit();
+}
+
 template <typename TG>
 __global__ void __launch_bounds__(SEL_THREADS, 1)
-ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift) {
+ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
+    extern __shared__ __align__(128) unsigned char stage_raw[];
     __shared__ SelectSmem sm;
     __shared__ FastSelSmem fs;
     __shared__ int s_first[A_MAX_TENSORS + 1];
+    __shared__ __align__(8) uint64_t s_bar;
+    const Stage<TG> st(stage_raw, stage_elems, qshift);
     int guess = 0;                                  // lower bound found for the previous tile, as key bits
     for (int i = threadIdx.x; i < n_tensors; i += SEL_THREADS) s_first[i] = tensors[i].first_unit_a;
-    if (threadIdx.x == 0) s_first[n_tensors] = total_units;
+    if (threadIdx.x == 0) { s_first[n_tensors] = total_units; mbar_init(&s_bar, 1); }
     __syncthreads();
     const int oshift = qshift - 3;                  // octets per quantisation block, as a shift
     const int lanes_per_qb = 1 << oshift;
+    uint32_t parity = 0;
+
+    // prologue: start staging the first tile
+    bool cur_staged = false;
+    if ((int)blockIdx.x < total_units) {
+        const int ti = find_tensor(s_first, n_tensors, blockIdx.x);
+        const TileRef<TG> r = tile_ref<TG>(tensors[ti], blockIdx.x - s_first[ti], qshift);
+        cur_staged = r.staged && r.n <= stage_elems;
+        if (cur_staged) stage_issue(r, st, &s_bar, qshift);
+    }
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int ti = find_tensor(s_first, n_tensors, unit);
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
-        const int dbs = T.d_block_size, nfull = T.topk_full_blocks_count;
-        const int64_t base = (int64_t)blk * dbs;
-        const int n = (int)min((int64_t)dbs, T.d - base);
-        const int k = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
-        const TG* g = reinterpret_cast<const TG*>(T.grad) + base;
-        const uint8_t* ef_in = T.error + (base >> 1);
-        const uint16_t* mn_in = T.min_vals + (base >> qshift);     // statistics of the tile's first block
-        const uint16_t* mx_in = T.max_vals + (base >> qshift);
-        const bool vec_g = aligned16(g), vec_e = (reinterpret_cast<uintptr_t>(ef_in) & 3) == 0;
+        const TileRef<TG> tr = tile_ref<TG>(T, blk, qshift);
+        const int n = tr.n, k = tr.k;
+        const int64_t base = (int64_t)blk * T.d_block_size;
+        const bool vec_e = (reinterpret_cast<uintptr_t>(tr.ef) & 3) == 0;
 
+        MAB_TICK_DECL
         // ---- a = g + Qinv(e), rounded to the gradient's element type ------------------------
         float a[SEL_OCTETS][8];
         float omax[SEL_OCTETS];
+        if (cur_staged) {
+            cp_async_wait_all();
+            const bool ok = mbar_wait(&s_bar, parity);
+            parity ^= 1u;
+            if (__syncthreads_or(!ok)) {            // the copy engine never delivered: flag it and stop
+                if (threadIdx.x == 0) atomicExch(&g_copy_timeout, 1);
+                return;
+            }
+            const int n_oct = n >> 3;
+            const uint16_t* s_mn = st.mn + tr.stat_skip;
+            const uint16_t* s_mx = st.mx + tr.stat_skip;
 #pragma unroll
-        for (int j = 0; j < SEL_OCTETS; ++j) {
-            const int o = j * SEL_THREADS + (int)threadIdx.x;
-            const int cnt = n - o * 8;               // >= 8: full octet, 1..7: the tensor's last, <= 0: none
-            omax[j] = 0.0f;
-            if (cnt >= 8) {
-                const QParams q = qparams(mn_in[o >> oshift], mx_in[o >> oshift]);
-                uint32_t w;
-                if (vec_e) w = __ldg(reinterpret_cast<const uint32_t*>(ef_in + o * 4));
-                else w = ef_in[o * 4] | ((uint32_t)ef_in[o * 4 + 1] << 8) | ((uint32_t)ef_in[o * 4 + 2] << 16) | ((uint32_t)ef_in[o * 4 + 3] << 24);
-                float gv[8], x[8];
-                GradOctet<TG>::load(g + o * 8, gv, vec_g, 8);
-                decode_octet(w, q, x);
+            for (int j = 0; j < SEL_OCTETS; ++j) {
+                const int o = j * SEL_THREADS + (int)threadIdx.x;
+                omax[j] = 0.0f;
+                if (o < n_oct) {
+                    const QParams q = qparams(s_mn[o >> oshift], s_mx[o >> oshift]);
+                    float gv[8], x[8];
+                    staged_octet(st.g + o * 8, gv);
+                    decode_octet(st.ef[o], q, x);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    a[j][e] = Elem<TG>::round(__fadd_rn(gv[e], x[e]));
-                    omax[j] = fmaxf(omax[j], fabsf(a[j][e]));
+                    for (int e = 0; e < 8; ++e) {
+                        a[j][e] = Elem<TG>::round(__fadd_rn(gv[e], x[e]));
+                        omax[j] = fmaxf(omax[j], fabsf(a[j][e]));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[j][e] = 0.0f;
                 }
-            } else if (cnt > 0) {
-                const QParams q = qparams(mn_in[o >> oshift], mx_in[o >> oshift]);
-                uint32_t w = 0;
+            }
+        } else {
+            const bool vec_g = aligned16(tr.g);
 #pragma unroll
-                for (int b = 0; b < 4; ++b) if (2 * b < cnt) w |= (uint32_t)ef_in[o * 4 + b] << (8 * b);
-                float gv[8], x[8];
-                GradOctet<TG>::load(g + o * 8, gv, false, cnt);
-                decode_octet_exact(w, q, x);
+            for (int j = 0; j < SEL_OCTETS; ++j) {
+                const int o = j * SEL_THREADS + (int)threadIdx.x;
+                const int cnt = n - o * 8;               // >= 8: full octet, 1..7: the tensor's last, <= 0: none
+                omax[j] = 0.0f;
+                if (cnt > 0) {
+                    const QParams q = qparams(tr.mn[o >> oshift], tr.mx[o >> oshift]);
+                    uint32_t w = 0;
+                    if (vec_e && cnt >= 8) w = __ldg(reinterpret_cast<const uint32_t*>(tr.ef + o * 4));
+                    else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    a[j][e] = (e < cnt) ? Elem<TG>::round(__fadd_rn(gv[e], x[e])) : 0.0f;
-                    omax[j] = fmaxf(omax[j], fabsf(a[j][e]));
+                        for (int b = 0; b < 4; ++b) if (2 * b < cnt) w |= (uint32_t)tr.ef[o * 4 + b] << (8 * b);
+                    }
+                    float gv[8], x[8];
+                    GradOctet<TG>::load(tr.g + o * 8, gv, vec_g && cnt >= 8, cnt);
+                    decode_octet_exact(w, q, x);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        a[j][e] = (e < cnt) ? Elem<TG>::round(__fadd_rn(gv[e], x[e])) : 0.0f;
+                        omax[j] = fmaxf(omax[j], fabsf(a[j][e]));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a[j][e] = 0.0f;
                 }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) a[j][e] = 0.0f;
             }
         }
+        MAB_TICK(10);
+        // the staging area is free again: start on the tile this CTA handles next
+        __syncthreads();
+        cur_staged = false;
+        if (unit + (int)gridDim.x < total_units) {
+            const int nu = unit + gridDim.x;
+            const int nti = find_tensor(s_first, n_tensors, nu);
+            const TileRef<TG> nr = tile_ref<TG>(tensors[nti], nu - s_first[nti], qshift);
+            cur_staged = nr.staged && nr.n <= stage_elems;
+            if (cur_staged) stage_issue(nr, st, &s_bar, qshift);
+        }
 
+        MAB_TICK(11);
         // ---- exact top-k ---------------------------------------------------------------------
         const int64_t row_off = (int64_t)T.ring_index * T.k + (int64_t)blk * T.k_block_size_many;
         uint16_t* v_out = T.V + row_off;
@@ -122,6 +253,7 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
             publish_masks(a, T_key, sm);
             resolve_selection(need, sm);
         }
+        MAB_TICK(12);
         emit_indices(sm, T.I + row_off);
         if (fast) {
             // V[row] = bf16(a[I]) from the candidate list, in the order the bitmap defines
@@ -134,6 +266,7 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
             }
         }
 
+        MAB_TICK(13);
         // ---- a[I] = 0 (slow path: also V[row]); statistics; e = Q(a) ------------------------------
         uint8_t* ef_out = T.error + (base >> 1);
         uint16_t* mn_out = T.min_vals + (base >> qshift);
@@ -184,21 +317,36 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 }
             }
         }
+        MAB_TICK(14);
         __syncthreads();   // selection scratch is reused by the next unit
+        MAB_TICK(15);
     }
 }
 
 int units_a_of(const mab_tensor& t) { return t.topk_full_blocks_count + (t.k_block_size_few > 0 ? 1 : 0); }
 
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
-                         int qbs, cudaStream_t s) {
+                         int qbs, int max_dbs, cudaStream_t s) {
     const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count());
     int qshift = 0;
     while ((1 << qshift) < qbs) ++qshift;
-    if (grad_dtype == MAB_F32)
-        ef_topk_quant_kernel<float><<<grid, SEL_THREADS, 0, s>>>(dev_tensors, n_tensors, total_units, qshift);
-    else
-        ef_topk_quant_kernel<uint16_t><<<grid, SEL_THREADS, 0, s>>>(dev_tensors, n_tensors, total_units, qshift);
+    // stage whole tiles when they fit beside the kernel's static shared memory, else load directly
+    const int limit = device_max_optin_smem() - 48 * 1024;
+    if (grad_dtype == MAB_F32) {
+        int stage_elems = max_dbs;
+        if (Stage<float>::bytes(stage_elems, qshift) > limit) stage_elems = 0;
+        const int smem = stage_elems ? Stage<float>::bytes(stage_elems, qshift) : 0;
+        auto kern = ef_topk_quant_kernel<float>;
+        MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems);
+    } else {
+        int stage_elems = max_dbs;
+        if (Stage<uint16_t>::bytes(stage_elems, qshift) > limit) stage_elems = 0;
+        const int smem = stage_elems ? Stage<uint16_t>::bytes(stage_elems, qshift) : 0;
+        auto kern = ef_topk_quant_kernel<uint16_t>;
+        MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems);
+    }
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_kernel launch");
@@ -207,10 +355,17 @@ int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total
 
 }  // namespace mab
 
+extern "C" int mab_device_error(void) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, mab::g_copy_timeout, sizeof(v));
+    if (e != cudaSuccess) return mab::cuda_fail(e, "mab_device_error");
+    return v;
+}
+
 #ifdef MAB_STATS
-extern "C" int mab_debug_stats(unsigned long long* out16, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out16, mab::g_stats, sizeof(mab::g_stats));
-    if (e == cudaSuccess && reset) { unsigned long long z[16] = {0}; e = cudaMemcpyToSymbol(mab::g_stats, z, sizeof(z)); }
+extern "C" int mab_debug_stats(unsigned long long* out32, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out32, mab::g_stats, sizeof(mab::g_stats));
+    if (e == cudaSuccess && reset) { unsigned long long z[32] = {0}; e = cudaMemcpyToSymbol(mab::g_stats, z, sizeof(z)); }
     return e == cudaSuccess ? 0 : -3;
 }
 #endif

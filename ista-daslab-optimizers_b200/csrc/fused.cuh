@@ -26,7 +26,7 @@ int units_b_of(const mab_tensor& t);
 
 // ef_topk_quant.cu
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
-                         int qbs, cudaStream_t s);
+                         int qbs, int max_dbs, cudaStream_t s);
 int units_a_of(const mab_tensor& t);
 
 }  // namespace mab

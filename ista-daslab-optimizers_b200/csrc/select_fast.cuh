@@ -24,10 +24,15 @@ namespace mab {
 #ifdef MAB_STATS
 // Development-only tile statistics (compiled in with -DMAB_STATS): [0] fast tiles, [1..6] tiles sent
 // to the slow path by reason, [7] lower-bound probes, [8] candidates, [9] histogram levels.
-__device__ unsigned long long g_stats[16];
+__device__ unsigned long long g_stats[32];
 #define MAB_STAT(i, v) do { if (threadIdx.x == 0) atomicAdd(&g_stats[i], (unsigned long long)(v)); } while (0)
+// phase timer: adds the cycles since the previous mark to slot i (thread 0's clock)
+#define MAB_TICK(i) do { if (threadIdx.x == 0) { const long long _now = clock64(); atomicAdd(&g_stats[i], (unsigned long long)(_now - g_tick)); g_tick = _now; } } while (0)
+#define MAB_TICK_DECL long long g_tick = clock64();
 #else
 #define MAB_STAT(i, v) do { } while (0)
+#define MAB_TICK(i) do { } while (0)
+#define MAB_TICK_DECL
 #endif
 
 constexpr int FS_CAND_CAP = 4096;
@@ -93,6 +98,7 @@ __device__ __forceinline__ int fs_lower_bound(const float (&omax)[SEL_OCTETS], f
 // ones, n_cand their number.  Uniform: every thread gets the same return value.
 __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], const float (&omax)[SEL_OCTETS], int n, int k,
                                             int& guess, SelectSmem& sm, FastSelSmem& fs, int& n_cand) {
+    MAB_TICK_DECL
     const int t = threadIdx.x, lane = lane_id(), warp = warp_id();
     float tmax = fmaxf(fmaxf(omax[0], omax[1]), fmaxf(omax[2], omax[3]));
 
@@ -105,6 +111,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
     }
     __syncthreads();
     const int kmax = fs.kmax;
+    MAB_TICK(16);
     if (kmax == 0 || kmax >= 0x7f800000) { MAB_STAT(1, 1); return false; }   // all zero, or non-finite values: slow path
 
     const bool octets = k > FS_OCTET_LEVEL_K;
@@ -113,6 +120,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
     const int T_lo = fs_lower_bound(omax, tmax, k, octets, kmax, guess, fs);
     if (T_lo <= 0) { MAB_STAT(3, 1); return false; }
     const float T_lo_f = __int_as_float(T_lo);
+    MAB_TICK(17);
 
     // ---- compact the candidates --------------------------------------------------------------
     int mine = 0;
@@ -135,6 +143,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
                 }
     }
     n_cand = C;
+    MAB_TICK(18);
     MAB_STAT(8, C);
 
     // ---- exact k-th key among the candidates: radix histogram levels ---------------------------
@@ -181,6 +190,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
         MAB_STAT(9, 1);
         if (R <= 32 || sh == 0) break;
     }
+    MAB_TICK(19);
     if (R > 32 && sh != 0) { MAB_STAT(5, 1); return false; } // cannot happen within 5 levels of 8 bits; stay safe
 
     // ---- members of the final bin: rank them (<= 32) or treat them as ties of one key -------------
@@ -221,7 +231,9 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
     } else {
         need_ties = k_rem;                                     // r_lo == r_hi: every member has the k-th key
     }
+    MAB_TICK(20);
     resolve_selection(need_ties, sm);                          // starts with a barrier
+    MAB_TICK(21);
     if (!by_rank) {
         // flag the ties that made it
         for (int i = t; i < C; i += SEL_THREADS) {

@@ -55,6 +55,7 @@ class MabStepArgs(Structure):
 SIGNATURES = {
     'mab_last_error': (c_char_p, []),
     'mab_kernel_launch_count': (c_int64, []),
+    'mab_device_error': (c_int, []),
     'mab_get_sm_count': (c_int, []),
     'mab_get_max_floats_for_shared_memory_per_thread_block': (c_int, []),
     'mab_asymm_block_quant_inv': (c_int, [c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
@@ -123,6 +124,14 @@ def current_stream(device) -> int:
 
 def kernel_launch_count() -> int:
     return load().mab_kernel_launch_count()
+
+
+def device_error() -> int:
+    """1 if a kernel ever gave up waiting for the copy engine on the current device (synchronises)."""
+    v = load().mab_device_error()
+    if v < 0:
+        check(v, 'device_error')
+    return v
 
 
 def get_sm_count() -> int:

@@ -34,6 +34,17 @@ def test_step_matches_golden_and_oracle(name, use_fused, golden):
     check_trace(case, tr, ref.digests, ref.samples)
 
 
+def test_no_kernel_gave_up_a_wait():
+    """Runs a multi-block case (tiles staged by the copy engine) and checks the device error flag."""
+    from ista_daslab_optimizers_b200 import _native
+    case = cases.CASES['c1_fp32_1m']
+    ad = cases.CudaAdapter(case, case.params())
+    for t in range(2):
+        ad.step(case.grads(t))
+    torch.cuda.synchronize()
+    assert _native.device_error() == 0
+
+
 def test_fused_path_is_taken_when_supported():
     case = cases.CASES['bf16_wd']
     ad = cases.CudaAdapter(case, case.params())
