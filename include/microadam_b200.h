@@ -169,6 +169,32 @@ int mab_fused_ef_topk_quant(mab_tensor* tensors, int n_tensors, const mab_step_a
 int mab_fused_window_adam_update(mab_tensor* tensors, int n_tensors, const mab_step_args* args,
                                  void* workspace, int64_t workspace_bytes, void* stream);
 
+/* Most tensors one call of mab_fused_step_static accepts. */
+#define MAB_STATIC_MAX_TENSORS 1024
+
+/* mab_fused_step for callers that have no device buffer to offer as workspace.  (It has no
+ * counterpart in the reference, whose native calls take one tensor at a time and need no table.)
+ *
+ * Who needs it: a trainer that gives all of HBM to one arena at start-up (a fixed memory plan, a
+ * pooling allocator that has already claimed the device) has nothing left that cudaMalloc could
+ * return, and a host that reaches this library through a foreign-function interface may be able to
+ * pass only the buffers its own runtime tracks (parameters, gradients, optimizer state) and not
+ * create a new one.  For them the table of tensor descriptors that the two kernels read lives in
+ * a fixed array inside the library instead: MAB_STATIC_MAX_TENSORS * sizeof(mab_tensor) bytes
+ * (136 KiB) of device memory per GPU, held by every GPU that loads the library until the process
+ * exits.  The call allocates nothing, on the device or on the host.
+ *
+ * Same arguments, results and errors as mab_fused_step, minus the workspace, with these differences:
+ *  - n_tensors > MAB_STATIC_MAX_TENSORS fails with MAB_ERR_LIMIT (split the step into several calls);
+ *  - tensors are processed in the order given; consecutive tensors with the same (grad, param) element
+ *    types share a kernel launch, so keep equal types together;
+ *  - the first call on a device looks up the array's device address (once per device, with that device
+ *    current); make that first call outside any stream capture;
+ *  - all calls on a device share the one array.  Calls on the same stream are ordered and safe; two
+ *    calls whose kernels can overlap on the GPU (different streams without an event between them)
+ *    race on it.  Nothing in the array has to start at zero: each call overwrites what it uses. */
+int mab_fused_step_static(mab_tensor* tensors, int n_tensors, const mab_step_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -185,3 +185,94 @@ extern "C" int mab_fused_window_adam_update(mab_tensor* tensors, int n_tensors, 
                                             int64_t workspace_bytes, void* stream) {
     return fused_run(tensors, n_tensors, args, workspace, workspace_bytes, stream, RUN_B);
 }
+
+// ---- fused step whose descriptor table lives inside the library --------------------------------
+//
+// For callers that cannot hand over a device workspace (see the header).  The table is a file-scope
+// device array; in host code its name is only a handle, so its device address is looked up once
+// per device with cudaGetSymbolAddress and that pointer is what the copy and the kernels receive.
+
+static __device__ __align__(256) unsigned char g_static_table[MAB_STATIC_MAX_TENSORS * sizeof(mab_tensor)];
+
+static int static_table_address(void** out) {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {};          // one device address per GPU; racing first calls store the same value
+    int dev = -1;
+    MAB_CUDA_TRY(cudaGetDevice(&dev));
+    MAB_REQUIRE(dev >= 0 && dev < kMaxDevices, MAB_ERR_LIMIT, "mab_fused_step_static: device ordinal %d beyond %d", dev, kMaxDevices);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        MAB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_table));
+        MAB_REQUIRE(p != nullptr, MAB_ERR_CUDA, "mab_fused_step_static: no device address for the descriptor table");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return MAB_OK;
+}
+
+// End (exclusive) of the run of tensors starting at `first` that one launch can take: same element
+// types, at most 512 tensors, unit counts within the kernels' 32-bit prefix.  Fills the library-owned
+// fields of those tensors and reports the run's totals.
+static int static_run_end(mab_tensor* tensors, int n, int first, int* units_a, int* units_b, int* max_k, int* max_dbs) {
+    const int gd = tensors[first].grad_dtype, pd = tensors[first].param_dtype;
+    const int64_t unit_cap = (int64_t)1 << 30;
+    int64_t ua = 0, ub = 0;
+    int i = first, mk = 0, md = 0;
+    while (i < n && i - first < WIN_MAX_TENSORS && tensors[i].grad_dtype == gd && tensors[i].param_dtype == pd) {
+        mab_tensor& t = tensors[i];
+        const int64_t na = units_a_of(t), nb = units_b_of(t);
+        if (i > first && (ua + na > unit_cap || ub + nb > unit_cap)) break;
+        t.decay_f32 = (float)(1.0 - t.lr * t.weight_decay);
+        t.neg_lr_f32 = (float)(-t.lr);
+        t.first_unit_a = (int32_t)ua;
+        t.first_unit_b = (int32_t)ub;
+        ua += na; ub += nb;
+        mk = std::max(mk, std::max(t.k_block_size_many, t.k_block_size_few));
+        md = std::max(md, t.d_block_size);
+        ++i;
+    }
+    *units_a = (int)ua; *units_b = (int)ub; *max_k = mk; *max_dbs = md;
+    return i;
+}
+
+extern "C" int mab_fused_step_static(mab_tensor* tensors, int n, const mab_step_args* args, void* stream) {
+    MAB_REQUIRE(n >= 0, MAB_ERR_BAD_ARG, "mab_fused_step_static: n_tensors=%d", n);
+    MAB_REQUIRE(n <= MAB_STATIC_MAX_TENSORS, MAB_ERR_LIMIT,
+                "mab_fused_step_static: %d tensors in one call, the built-in table holds %d; split the step into several calls",
+                n, MAB_STATIC_MAX_TENSORS);
+    if (n == 0) return MAB_OK;
+    MAB_REQUIRE(tensors && args, MAB_ERR_BAD_ARG, "mab_fused_step_static: null argument");
+    MAB_REQUIRE(args->steps >= 1, MAB_ERR_BAD_ARG, "mab_fused_step_static: steps=%lld", (long long)args->steps);
+    for (int i = 0; i < n; ++i) {
+        const char* why = fused_obstacle(&tensors[i], args);
+        MAB_REQUIRE(why == nullptr, MAB_ERR_UNSUPPORTED, "mab_fused_step_static: tensor %d: %s", i, why);
+        MAB_REQUIRE(units_a_of(tensors[i]) <= ((int64_t)1 << 30) && units_b_of(tensors[i]) <= ((int64_t)1 << 30), MAB_ERR_LIMIT,
+                    "mab_fused_step_static: tensor %d has too many blocks", i);
+    }
+    if (device_sm_count() < 0) return MAB_ERR_CUDA;
+    void* table = nullptr;
+    if (int rc = static_table_address(&table)) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    WindowArgs wa;
+    if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
+                                  args->quant_block_size)) return rc;
+
+    // first pass: fill the library-owned fields of every run, then ship the table
+    int ua, ub, mk, md;
+    for (int first = 0; first < n;) first = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
+    MAB_CUDA_TRY(cudaMemcpyAsync(table, tensors, (size_t)n * sizeof(mab_tensor), cudaMemcpyHostToDevice, s));
+    const mab_tensor* dev = reinterpret_cast<const mab_tensor*>(table);
+    // kernel A over every run, then kernel B over every run (the runs are recomputed, not stored)
+    for (int first = 0; first < n;) {
+        const int end = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
+        if (int rc = launch_ef_topk_quant(dev + first, end - first, ua, tensors[first].grad_dtype, args->quant_block_size, md, s)) return rc;
+        first = end;
+    }
+    for (int first = 0; first < n;) {
+        const int end = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
+        const int max_entries = (int)std::min<int64_t>((int64_t)wa.rows * mk, INT32_MAX);
+        if (int rc = launch_window_step(dev + first, end - first, ua, ub, max_entries, tensors[first].param_dtype, wa, s)) return rc;
+        first = end;
+    }
+    return MAB_OK;
+}

@@ -18,6 +18,7 @@ MAB_OK = 0
 MAB_F32, MAB_BF16 = 0, 1
 MAB_K2D, MAB_D2K = 0, 1
 MAB_MAX_WINDOW = 128
+MAB_STATIC_MAX_TENSORS = 1024
 
 _DTYPE_CODE = {torch.float32: MAB_F32, torch.bfloat16: MAB_BF16}
 
@@ -71,6 +72,7 @@ SIGNATURES = {
     'mab_fused_step': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),
     'mab_fused_ef_topk_quant': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),
     'mab_fused_window_adam_update': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),
+    'mab_fused_step_static': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p]),
 }
 
 _lib = None
