@@ -26,18 +26,17 @@ __device__ __forceinline__ float magic_byte(uint32_t v) {
 // x[e] = Qinv(code_e) = RN(RN(code * u) + mn).  With F = 2^23 + code (exact), fma(F, u, -2^23 u)
 // rounds the exact value code * u once, which is RN(code * u); valid while 2^23 * |u| does not
 // overflow and u >= +0 (a negative u would turn the +0 of code 0 into -0); the caller checks both.
+// Two elements per instruction: the packed f32x2 forms round each component like the scalar ones.
 __device__ __forceinline__ void decode_octet_fast(uint32_t w, const QParams& q, float (&x)[8]) {
     uint32_t hi, lo;
     split_nibbles(w, hi, lo);
     const float nb = -(8388608.0f * q.u);
-    x[0] = __fadd_rn(__fmaf_rn(magic_byte<0>(hi), q.u, nb), q.mn);
-    x[1] = __fadd_rn(__fmaf_rn(magic_byte<0>(lo), q.u, nb), q.mn);
-    x[2] = __fadd_rn(__fmaf_rn(magic_byte<1>(hi), q.u, nb), q.mn);
-    x[3] = __fadd_rn(__fmaf_rn(magic_byte<1>(lo), q.u, nb), q.mn);
-    x[4] = __fadd_rn(__fmaf_rn(magic_byte<2>(hi), q.u, nb), q.mn);
-    x[5] = __fadd_rn(__fmaf_rn(magic_byte<2>(lo), q.u, nb), q.mn);
-    x[6] = __fadd_rn(__fmaf_rn(magic_byte<3>(hi), q.u, nb), q.mn);
-    x[7] = __fadd_rn(__fmaf_rn(magic_byte<3>(lo), q.u, nb), q.mn);
+    const float2 u2 = make_float2(q.u, q.u), nb2 = make_float2(nb, nb), mn2 = make_float2(q.mn, q.mn);
+    float2 p;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<0>(hi), magic_byte<0>(lo)), u2, nb2), mn2); x[0] = p.x; x[1] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<1>(hi), magic_byte<1>(lo)), u2, nb2), mn2); x[2] = p.x; x[3] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<2>(hi), magic_byte<2>(lo)), u2, nb2), mn2); x[4] = p.x; x[5] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<3>(hi), magic_byte<3>(lo)), u2, nb2), mn2); x[6] = p.x; x[7] = p.y;
 }
 
 __device__ __forceinline__ void decode_octet_exact(uint32_t w, const QParams& q, float (&x)[8]) {
@@ -62,32 +61,56 @@ __device__ __forceinline__ uint32_t encode_octet_exact(const float (&r)[8], cons
 
 // Codes of a full octet.  s~ = (r - mn) * (1/u) + 0.5 differs from the defining
 // s = RN(RN((r - mn) / u) + 0.5) by less than 2^-17 for |s| <= 16.5, so floor(s~) = floor(s)
-// unless s~ lies within 2^-16 of an integer; in that (rare) case, and for u outside
-// [2^-100, 2^100] (zero, subnormal, infinite), the octet is redone with the exact definition.
+// unless s~ lies within 2^-16 of an integer; those (rare) elements, and every element when u is
+// outside [2^-100, 2^100] (zero, subnormal, infinite), are coded with the exact definition.
 // The clamp to [0.25, 15.5] keeps floor() in 0..15 and maps every out-of-range s to the code the
 // definition's clamp gives it.
 __device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QParams& q) {
     if (!(q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX)) return encode_octet_exact(r, q, 8);
     const float r0 = __frcp_rn(q.u);
     const float MAGIC = 12582912.0f;              // 1.5 * 2^23: low mantissa bits of x + MAGIC hold round-down(x)
+    const float2 nmn2 = make_float2(-q.mn, -q.mn), r02 = make_float2(r0, r0), half2v = make_float2(0.5f, 0.5f);
+    const float2 mg2 = make_float2(MAGIC, MAGIC), nmg2 = make_float2(-MAGIC, -MAGIC), neg1 = make_float2(-1.0f, -1.0f);
+    const float2 nhalf2 = make_float2(-0.5f, -0.5f);
     float f[8];
-    bool unsafe = false;
+    unsigned unsafe = 0;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        float s = __fmaf_rn(__fsub_rn(r[e], q.mn), r0, 0.5f);
-        s = fminf(fmaxf(s, 0.25f), 15.5f);
-        const float fl = __fadd_rd(s, MAGIC) - MAGIC;       // floor(s), exact
-        const float frac = s - fl;                           // exact, in [0, 1)
-        unsafe |= fabsf(frac - 0.5f) > 0.5f - 1.52587890625e-5f;
-        f[e] = fl;
+    for (int b = 0; b < 4; ++b) {
+        float2 s = __ffma2_rn(__fadd2_rn(make_float2(r[2 * b], r[2 * b + 1]), nmn2), r02, half2v);   // r - mn == r + (-mn)
+        s.x = fminf(fmaxf(s.x, 0.25f), 15.5f);
+        s.y = fminf(fmaxf(s.y, 0.25f), 15.5f);
+        const float2 fl = __fadd2_rn(__fadd2_rd(s, mg2), nmg2);     // floor(s), exact
+        const float2 d = __fadd2_rn(__ffma2_rn(fl, neg1, s), nhalf2); // (s - floor(s)) - 0.5, exact
+        unsafe |= (fabsf(d.x) > 0.5f - 1.52587890625e-5f) ? (1u << (2 * b)) : 0u;
+        unsafe |= (fabsf(d.y) > 0.5f - 1.52587890625e-5f) ? (2u << (2 * b)) : 0u;
+        f[2 * b] = fl.x; f[2 * b + 1] = fl.y;
     }
-    if (unsafe) return encode_octet_exact(r, q, 8);
+    if (unsafe) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if (unsafe & (1u << e)) f[e] = static_cast<float>(qcode_exact(r[e], q));
+    }
     // byte b = 16 * code(2b) + code(2b+1), built in float and read from the low mantissa byte
     const uint32_t b0 = __float_as_uint(__fmaf_rn(f[0], 16.0f, f[1]) + 8388608.0f);
     const uint32_t b1 = __float_as_uint(__fmaf_rn(f[2], 16.0f, f[3]) + 8388608.0f);
     const uint32_t b2 = __float_as_uint(__fmaf_rn(f[4], 16.0f, f[5]) + 8388608.0f);
     const uint32_t b3 = __float_as_uint(__fmaf_rn(f[6], 16.0f, f[7]) + 8388608.0f);
     return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
+
+// min and max of 8 values with the 3-input min / max of sm_100.
+__device__ __forceinline__ float min3(float a, float b, float c) { float d; asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+__device__ __forceinline__ void octet_min_max(const float (&v)[8], float& lo, float& hi) {
+    lo = fminf(min3(v[0], v[1], v[2]), min3(min3(v[3], v[4], v[5]), v[6], v[7]));
+    hi = fmaxf(max3(v[0], v[1], v[2]), max3(max3(v[3], v[4], v[5]), v[6], v[7]));
+}
+
+// Two floats -> two bf16 (round to nearest even) in one conversion; low half = first value.
+__device__ __forceinline__ uint32_t pack_bf16x2_rne(float a, float b) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+    return d;
 }
 
 }  // namespace mab

@@ -18,6 +18,23 @@ namespace mab {
 
 constexpr int A_MAX_TENSORS = 512;
 
+// a = round_to_grad_dtype(g + x) for an octet.
+__device__ __forceinline__ void add_round(const float (&g)[8], const float (&x)[8], float (&a)[8], const float*) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float2 s = __fadd2_rn(make_float2(g[2 * b], g[2 * b + 1]), make_float2(x[2 * b], x[2 * b + 1]));
+        a[2 * b] = s.x; a[2 * b + 1] = s.y;
+    }
+}
+__device__ __forceinline__ void add_round(const float (&g)[8], const float (&x)[8], float (&a)[8], const uint16_t*) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const float2 s = __fadd2_rn(make_float2(g[2 * b], g[2 * b + 1]), make_float2(x[2 * b], x[2 * b + 1]));
+        const uint32_t w = pack_bf16x2_rne(s.x, s.y);
+        a[2 * b] = __uint_as_float(w << 16); a[2 * b + 1] = __uint_as_float(w & 0xFFFF0000u);
+    }
+}
+
 // 8 staged elements in shared memory (16-byte aligned) as floats.
 __device__ __forceinline__ void staged_octet(const float* p, float (&v)[8]) {
     const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
@@ -109,17 +126,15 @@ struct Stage {
     }
 };
 
-// Starts the copies of a staged tile: thread 0 arms the barrier and issues the bulk copies of the
-// gradient and the codes in 16 KB pieces; the statistics (a few hundred bf16) go through cp.async.
+// Starts the copies of a staged tile: one thread arms the barrier and issues the bulk copies of the
+// gradient and the codes (one copy each); the statistics (a few hundred bf16) go through cp.async.
 template <typename TG>
 __device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG>& st, uint64_t* bar, int qshift) {
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == SEL_THREADS - 32) {           // first lane of the last warp: warp 0 has serial work of its own
         const uint32_t gb = (uint32_t)r.n * (uint32_t)sizeof(TG), eb = (uint32_t)r.n >> 1;
         mbar_arrive_expect_tx(bar, gb + eb);
-        for (uint32_t off = 0; off < gb; off += 16384)
-            bulk_g2s(reinterpret_cast<unsigned char*>(st.g) + off, reinterpret_cast<const unsigned char*>(r.g) + off, min(16384u, gb - off), bar);
-        for (uint32_t off = 0; off < eb; off += 16384)
-            bulk_g2s(reinterpret_cast<unsigned char*>(st.ef) + off, r.ef + off, min(16384u, eb - off), bar);
+        bulk_g2s(st.g, r.g, gb, bar);
+        bulk_g2s(st.ef, r.ef, eb, bar);
     }
     const int words = (((r.n >> qshift) + r.stat_skip) + 1) >> 1;      // 4-byte words covering the tile's statistics
     const uint32_t* mn_src = reinterpret_cast<const uint32_t*>(r.mn - r.stat_skip);
@@ -190,11 +205,9 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                     float gv[8], x[8];
                     staged_octet(st.g + o * 8, gv);
                     decode_octet(st.ef[o], q, x);
+                    add_round(gv, x, a[j], static_cast<const TG*>(nullptr));
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        a[j][e] = Elem<TG>::round(__fadd_rn(gv[e], x[e]));
-                        omax[j] = fmaxf(omax[j], fabsf(a[j][e]));
-                    }
+                    for (int e = 0; e < 8; ++e) omax[j] = fmaxf(omax[j], fabsf(a[j][e]));
                 } else {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) a[j][e] = 0.0f;
@@ -278,8 +291,10 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
             const int cnt = n - o * 8;
             const uint32_t sel = sel_bytes[o];
             if (fast) {
+#ifndef MAB_X_SKIP_ZERO
 #pragma unroll
                 for (int e = 0; e < 8; ++e) a[j][e] = (sel & (1u << e)) ? 0.0f : a[j][e];
+#endif
             } else if (sel) {
                 const int word = o >> 2;
                 int p = sm.sel_before[word] + __popc(sm.sel_bm[word] & ((1u << (8 * (o & 3))) - 1u));
@@ -289,22 +304,28 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
             }
             float lo = INFINITY, hi = -INFINITY;
             if (cnt >= 8) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) { lo = fminf(lo, a[j][e]); hi = fmaxf(hi, a[j][e]); }
+                octet_min_max(a[j], lo, hi);
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) if (e < cnt) { lo = fminf(lo, a[j][e]); hi = fmaxf(hi, a[j][e]); }
             }
+#ifndef MAB_X_SKIP_SHUFFLE
             for (int off = 1; off < lanes_per_qb; off <<= 1) {
                 lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
                 hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
             }
+#endif
             if (cnt > 0) {
-                const uint16_t mn_b = f32_to_bf16_bits_rne(lo), mx_b = f32_to_bf16_bits_rne(hi);
+                const uint32_t st_b = pack_bf16x2_rne(lo, hi);
+                const uint16_t mn_b = (uint16_t)(st_b & 0xFFFFu), mx_b = (uint16_t)(st_b >> 16);
                 if ((o & (lanes_per_qb - 1)) == 0) { mn_out[o >> oshift] = mn_b; mx_out[o >> oshift] = mx_b; }
                 const QParams q2 = qparams(mn_b, mx_b);
                 if (cnt >= 8) {
+#ifdef MAB_X_SKIP_ENCODE
+                    const uint32_t w = __float_as_uint(a[j][0] + q2.u);
+#else
                     const uint32_t w = encode_octet(a[j], q2);
+#endif
                     if (vec_e) *reinterpret_cast<uint32_t*>(ef_out + o * 4) = w;
                     else {
 #pragma unroll

@@ -85,15 +85,18 @@ __device__ __forceinline__ void publish_masks(const float (&key)[SEL_OCTETS][8],
 __device__ __forceinline__ void resolve_selection(int need_ties, SelectSmem& sm) {
     __syncthreads();
     const int w = threadIdx.x;
-    uint32_t tw = sm.tie_bm[w];
     const uint32_t gw = sm.gt_bm[w];
     int total;
-    const int ties_before = block_exclusive_scan(__popc(tw), sm.scan, total);
-    int keep = need_ties - ties_before;
-    if (keep <= 0) tw = 0;
-    else while (__popc(tw) > keep) tw &= ~(0x80000000u >> __clz(tw));   // drop the highest position
-    const uint32_t sel = gw | tw;
-    __syncthreads();
+    uint32_t sel = gw;
+    if (need_ties > 0) {                                    // uniform: no tie scan when no tie is needed
+        uint32_t tw = sm.tie_bm[w];
+        const int ties_before = block_exclusive_scan(__popc(tw), sm.scan, total);
+        int keep = need_ties - ties_before;
+        if (keep <= 0) tw = 0;
+        else while (__popc(tw) > keep) tw &= ~(0x80000000u >> __clz(tw));   // drop the highest position
+        sel |= tw;
+        __syncthreads();
+    }
     const int before = block_exclusive_scan(__popc(sel), sm.scan, total);
     sm.sel_bm[w] = sel;
     sm.sel_before[w] = before;

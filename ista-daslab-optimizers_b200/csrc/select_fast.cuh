@@ -213,19 +213,19 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
     __syncthreads();
     int need_ties = 0;
     if (by_rank) {
-        if (warp == 0) {
-            const int nm = fs.n_member;                        // == R
+        // member w is ranked by warp w: lane l holds member l, one ballot counts who beats member w
+        const int nm = fs.n_member;                            // == R <= 32
+        if (warp < nm) {
+            const int mine_idx = fs.member[warp];
+            const int my_key = fs_key(fs.cand_val[mine_idx]);
+            const int my_pos = (int)(fs.cand_pos[mine_idx] & 0x7FFFu);   // other warps may set the flag bit meanwhile
             const int idx = lane < nm ? fs.member[lane] : -1;
             const int key = idx >= 0 ? fs_key(fs.cand_val[idx]) : -1;
-            const int pos = idx >= 0 ? (int)fs.cand_pos[idx] : 0x7fffffff;
-            int rank = 0;
-            for (int o = 0; o < nm; ++o) {
-                const int ok = __shfl_sync(0xffffffffu, key, o), op = __shfl_sync(0xffffffffu, pos, o);
-                rank += (ok > key || (ok == key && op < pos)) ? 1 : 0;
-            }
-            if (idx >= 0 && rank < k_rem) {
-                fs.cand_pos[idx] = (uint16_t)(pos | 0x8000);
-                atomicOr(&sm.gt_bm[pos >> 5], 1u << (pos & 31));
+            const int pos = idx >= 0 ? (int)(fs.cand_pos[idx] & 0x7FFFu) : 0x7fffffff;
+            const unsigned beats = __ballot_sync(0xffffffffu, key > my_key || (key == my_key && pos < my_pos));
+            if (lane == 0 && __popc(beats) < k_rem) {
+                fs.cand_pos[mine_idx] = (uint16_t)(my_pos | 0x8000);
+                atomicOr(&sm.gt_bm[my_pos >> 5], 1u << (my_pos & 31));
             }
         }
     } else {

@@ -12,7 +12,7 @@ from ctypes import POINTER, Structure, c_char_p, c_double, c_float, c_int, c_int
 import torch
 
 LIB_NAME = 'libmicroadam_b200.so'
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'lib', LIB_NAME)
+LIB_PATH = os.environ.get('MICROADAM_B200_LIB') or os.path.join(os.path.dirname(os.path.abspath(__file__)), 'lib', LIB_NAME)
 
 MAB_OK = 0
 MAB_F32, MAB_BF16 = 0, 1
