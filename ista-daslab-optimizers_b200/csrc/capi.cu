@@ -164,8 +164,7 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
         if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
                                       args->quant_block_size)) return rc;
         for (const Chunk& c : chunks) {
-            const int max_entries = (int)std::min<int64_t>((int64_t)wa.rows * c.max_k, INT32_MAX);
-            if (int rc = launch_window_step(dev + c.first, c.count, c.units_a, c.units_b, max_entries, c.param_dtype, wa, s)) return rc;
+            if (int rc = launch_window_step(dev + c.first, c.count, c.units_a, c.units_b, c.max_k, c.param_dtype, wa, s)) return rc;
         }
     }
     return MAB_OK;
@@ -270,8 +269,7 @@ extern "C" int mab_fused_step_static(mab_tensor* tensors, int n, const mab_step_
     }
     for (int first = 0; first < n;) {
         const int end = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
-        const int max_entries = (int)std::min<int64_t>((int64_t)wa.rows * mk, INT32_MAX);
-        if (int rc = launch_window_step(dev + first, end - first, ua, ub, max_entries, tensors[first].param_dtype, wa, s)) return rc;
+        if (int rc = launch_window_step(dev + first, end - first, ua, ub, mk, tensors[first].param_dtype, wa, s)) return rc;
         first = end;
     }
     return MAB_OK;

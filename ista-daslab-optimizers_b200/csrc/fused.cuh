@@ -20,7 +20,7 @@ __device__ __forceinline__ int find_tensor(const int* first, int n, int unit) {
 
 // window_adam.cu
 int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double beta2, double eps, float alpha, int qbs);
-int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_entries,
+int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_k,
                        int param_dtype, const WindowArgs& a, cudaStream_t s);
 int units_b_of(const mab_tensor& t);
 

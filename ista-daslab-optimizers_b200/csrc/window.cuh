@@ -26,6 +26,7 @@ constexpr int WIN_MAX_TENSORS = 512;  // tensors per launch (their unit prefix s
 
 struct WindowArgs {
     int   rows;                       // valid window rows: min(steps, m)
+    int   m;                          // allocated window rows
     float w1[MAB_MAX_WINDOW];         // beta1^age(r) * (1 - beta1), indexed by row
     float w2[MAB_MAX_WINDOW];
     float bc1, bc2, eps;              // 1 - beta1^steps, 1 - beta2^steps

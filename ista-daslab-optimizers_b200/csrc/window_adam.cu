@@ -18,6 +18,16 @@
 
 namespace mab {
 
+#ifdef MAB_STATS
+// Development-only phase timers of the tile kernel (cycles of thread 0, summed over tiles); [15] = tiles.
+__device__ unsigned long long g_stats_b[16];
+#define MAB_BTICK(i) do { if (threadIdx.x == 0) { const long long _now = clock64(); atomicAdd(&g_stats_b[i], (unsigned long long)(_now - b_tick)); b_tick = _now; } } while (0)
+#define MAB_BTICK_DECL long long b_tick = clock64();
+#else
+#define MAB_BTICK(i) do { } while (0)
+#define MAB_BTICK_DECL
+#endif
+
 enum : int { MODE_WRITE_UPDATE = 0, MODE_STEP = 1 };
 
 // 8 consecutive elements of a buffer as floats; vector access when `full`, else element-wise
@@ -59,10 +69,10 @@ template <> struct Octet<uint16_t> {
     __device__ __forceinline__ static void store(uint16_t* p, const float (&v)[8], bool full, int n) {
         if (full) {
             uint4 a;
-            a.x = f32_to_bf16_bits_rne(v[0]) | ((uint32_t)f32_to_bf16_bits_rne(v[1]) << 16);
-            a.y = f32_to_bf16_bits_rne(v[2]) | ((uint32_t)f32_to_bf16_bits_rne(v[3]) << 16);
-            a.z = f32_to_bf16_bits_rne(v[4]) | ((uint32_t)f32_to_bf16_bits_rne(v[5]) << 16);
-            a.w = f32_to_bf16_bits_rne(v[6]) | ((uint32_t)f32_to_bf16_bits_rne(v[7]) << 16);
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(a.x) : "f"(v[1]), "f"(v[0]));
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(a.y) : "f"(v[3]), "f"(v[2]));
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(a.z) : "f"(v[5]), "f"(v[4]));
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(a.w) : "f"(v[7]), "f"(v[6]));
             reinterpret_cast<uint4*>(p)[0] = a;
         } else {
 #pragma unroll
@@ -71,16 +81,88 @@ template <> struct Octet<uint16_t> {
     }
 };
 
+// Two floats -> two bf16 (round to nearest even) in one conversion; low half = first value.
+__device__ __forceinline__ uint32_t cvt_bf16x2_rne(float a, float b) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+    return d;
+}
+
+// p <- round_p(round_p(p * decay) - lr * u) for 8 values, two per instruction (packed f32x2
+// operations round each component like the scalar ones).
+template <typename TP>
+__device__ __forceinline__ void update_octet(float (&pv)[8], const float (&u)[8], bool do_decay, float2 decay2, float2 neg_lr2) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float2 x = make_float2(pv[2 * b], pv[2 * b + 1]);
+        if (do_decay) {
+            x = __fmul2_rn(x, decay2);
+            if (sizeof(TP) == 2) {                       // the decayed value is stored as bf16 before the update reads it
+                const uint32_t w = cvt_bf16x2_rne(x.x, x.y);
+                x = make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+            }
+        }
+        x = __ffma2_rn(neg_lr2, make_float2(u[2 * b], u[2 * b + 1]), x);
+        pv[2 * b] = x.x; pv[2 * b + 1] = x.y;
+    }
+}
+
+// An octet as loaded (16-byte vectors), unpacked to floats only when it is used.
+template <typename T> struct RawOctet;
+template <> struct RawOctet<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = reinterpret_cast<const float4*>(p)[0]; b = reinterpret_cast<const float4*>(p)[1]; }
+    __device__ __forceinline__ void unpack(float (&v)[8]) const {
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct RawOctet<uint16_t> {
+    uint4 a;
+    __device__ __forceinline__ void load(const uint16_t* p) { a = reinterpret_cast<const uint4*>(p)[0]; }
+    __device__ __forceinline__ void unpack(float (&v)[8]) const {
+        v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
+    }
+};
+
+// Where the streaming loop gets the update of octet o (8 consecutive elements of the range) from.
+struct DenseU {                 // a dense float array in shared memory, 16-byte aligned
+    const float* u;
+    __device__ __forceinline__ void load(int o, float (&v)[8]) const {
+        const float4 a = reinterpret_cast<const float4*>(u + o * 8)[0], b = reinterpret_cast<const float4*>(u + o * 8)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+struct SparseU {                // touched positions as a bitmap, their updates compact in slot order
+    const uint32_t* bitmap;     // bit i of the range set <=> position i touched
+    const uint16_t* prefix;     // touched positions in lower bitmap words
+    const float2* mv;           // .x = update of the slot
+    __device__ __forceinline__ void load(int o, float (&v)[8]) const {
+        const uint32_t word = bitmap[o >> 2];
+        const uint32_t sh = 8u * (o & 3);
+        const uint32_t byte = (word >> sh) & 0xFFu;
+        int slot = prefix[o >> 2] + __popc(word & ((1u << sh) - 1u));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const bool on = (byte >> e) & 1u;
+            v[e] = on ? mv[slot].x : 0.0f;
+            slot += on ? 1 : 0;
+        }
+    }
+};
+
 __device__ __forceinline__ float round_as(float v, bool bf16) {
     return bf16 ? bf16_bits_to_f32(f32_to_bf16_bits_rne(v)) : v;
 }
 
-// Streams tensor elements [e0, e0 + len) against the dense update u[0..len) in shared memory
-// (already rounded to the gradient's element type).  e0 is a multiple of 8 (and of
-// quant_block_size when alpha > 0).  NT threads, all of them must call.
-template <typename TP, int MODE, int NT>
-__device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowArgs& a, const float* __restrict__ u_s,
-                                             int64_t e0, int len) {
+// Streams tensor elements [e0, e0 + len) against their updates (already rounded to the gradient's
+// element type), which `src` delivers octet by octet.  e0 is a multiple of 8 (and of
+// quant_block_size when alpha > 0).  NT threads, all of them must call.  ALPHA selects the
+// alpha > 0 form at compile time (it needs many more registers).
+template <typename TP, int MODE, int NT, bool ALPHA, typename USrc>
+__device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowArgs& a, const USrc& src, int64_t e0, int len) {
     TP* p = reinterpret_cast<TP*>(T.param) + e0;
     const bool vec = aligned16(p);                        // octets stay 16-byte aligned from here
     const int n_oct = (len + 7) >> 3;
@@ -88,39 +170,50 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
         for (int o = threadIdx.x; o < n_oct; o += NT) {
             const int n = min(8, len - o * 8);
             float u[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) u[e] = u_s[o * 8 + e];
+            src.load(o, u);
             Octet<TP>::store(p + o * 8, u, vec && n == 8, n);
         }
         return;
     }
     const float decay = T.decay_f32, neg_lr = T.neg_lr_f32;
     const bool do_decay = T.weight_decay > 0.0;
-    if (a.alpha == 0.0f) {
-        // two octets per thread and iteration so that two parameter loads are in flight
-        for (int o = threadIdx.x; o < n_oct; o += 2 * NT) {
-            const int o2 = o + NT;
-            const int n1 = min(8, len - o * 8);
-            const int n2 = (o2 < n_oct) ? min(8, len - o2 * 8) : 0;
-            float pv1[8], pv2[8];
-            Octet<TP>::load(p + o * 8, pv1, vec && n1 == 8, n1);
-            if (n2 > 0) Octet<TP>::load(p + o2 * 8, pv2, vec && n2 == 8, n2);
+    if (!ALPHA) {
+        const float2 decay2 = make_float2(decay, decay), neg_lr2 = make_float2(neg_lr, neg_lr);
+        constexpr int B = (sizeof(TP) == 2) ? 4 : 2;          // octets per thread and batch
+        const int full_oct = vec ? (len >> 3) : 0;           // octets that can move as 16-byte vectors
+        const int nbatch = (full_oct + B * NT - 1) / (B * NT);
+        // software pipeline: the loads of batch i + 1 are in flight while batch i is computed and stored
+        RawOctet<TP> cur[B], nxt[B];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float x = pv1[e];
-                if (do_decay) x = Elem<TP>::round(__fmul_rn(x, decay));
-                pv1[e] = fmaf(neg_lr, u_s[o * 8 + e], x);
+        for (int i = 0; i < B; ++i) { const int o = threadIdx.x + i * NT; if (o < full_oct) cur[i].load(p + o * 8); }
+        for (int bi = 0; bi < nbatch; ++bi) {
+            const int o0 = bi * B * NT + threadIdx.x;
+            if (bi + 1 < nbatch) {
+#pragma unroll
+                for (int i = 0; i < B; ++i) { const int o = o0 + (B + i) * NT; if (o < full_oct) nxt[i].load(p + o * 8); }
             }
-            Octet<TP>::store(p + o * 8, pv1, vec && n1 == 8, n1);
-            if (n2 > 0) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    float x = pv2[e];
-                    if (do_decay) x = Elem<TP>::round(__fmul_rn(x, decay));
-                    pv2[e] = fmaf(neg_lr, u_s[o2 * 8 + e], x);
+            for (int i = 0; i < B; ++i) {
+                const int o = o0 + i * NT;
+                if (o < full_oct) {
+                    float pv[8], u[8];
+                    cur[i].unpack(pv);
+                    src.load(o, u);
+                    update_octet<TP>(pv, u, do_decay, decay2, neg_lr2);
+                    Octet<TP>::store(p + o * 8, pv, true, 8);
                 }
-                Octet<TP>::store(p + o2 * 8, pv2, vec && n2 == 8, n2);
             }
+#pragma unroll
+            for (int i = 0; i < B; ++i) cur[i] = nxt[i];
+        }
+        // the ragged rest (a misaligned tensor, or the last, short octet): element-wise
+        for (int o = full_oct + threadIdx.x; o < n_oct; o += NT) {
+            const int n = min(8, len - o * 8);
+            float pv[8], u[8];
+            Octet<TP>::load(p + o * 8, pv, false, n);
+            src.load(o, u);
+            update_octet<TP>(pv, u, do_decay, decay2, neg_lr2);
+            Octet<TP>::store(p + o * 8, pv, false, n);
         }
         return;
     }
@@ -141,13 +234,14 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
             const uint8_t* ef = T.error + (ge >> 1);
 #pragma unroll
             for (int b = 0; b < 4; ++b) if (2 * b < n) codes |= (uint32_t)ef[b] << (8 * b);
-            float pv[8];
+            float pv[8], uo[8];
             Octet<TP>::load(p + o * 8, pv, vec && n == 8, n);
+            src.load(o, uo);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const uint32_t code = (codes >> (8 * (e >> 1) + ((e & 1) ? 0 : 4))) & 0xFu;
                 const float x1 = qinv(code, q);
-                const float u = round_as(__fadd_rn(u_s[o * 8 + e], __fmul_rn(a.alpha, x1)), g_bf16);
+                const float u = round_as(__fadd_rn(uo[e], __fmul_rn(a.alpha, x1)), g_bf16);
                 float x = pv[e];
                 if (do_decay) x = Elem<TP>::round(__fmul_rn(x, decay));
                 pv[e] = fmaf(neg_lr, u, x);
@@ -180,14 +274,16 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
 // ------------------------------------------------------------------------------------ tile kernel
 
 constexpr int WT_THREADS = 256;
-constexpr int WT_CHUNK = 3712;            // positions per streaming chunk: 29 * 128
 constexpr int WT_WORDS = 1024;            // bitmap words (32768 positions)
 constexpr int WT_MAX_ENTRIES = 16384;     // window entries of one block the compact arrays may hold
 
-__host__ __device__ constexpr int wt_smem_bytes(int entries) {
-    const int e = (entries + 3) & ~3;
-    const int staging = e > WT_CHUNK ? 4 * e : 4 * WT_CHUNK;
-    return 8 * e + staging + 4 * WT_WORDS + 2 * WT_WORDS;
+// Bytes one row's slice of I (or V) occupies in the raw staging area: the slice is copied from the
+// 16-byte boundary below its first element, in whole 16-byte pieces.
+__host__ __device__ constexpr int wt_row_stride(int max_k) { return ((max_k * 2 + 30) + 15) & ~15; }
+
+__host__ __device__ constexpr int wt_smem_bytes(int rows, int max_k) {
+    const int e = (rows * max_k + 3) & ~3;
+    return 8 * e + rows * 2 * wt_row_stride(max_k) + 4 * WT_WORDS + 2 * WT_WORDS;
 }
 
 // Fast (not correctly rounded) form of m_hat / (sqrt(v_hat) + eps): the update is specified to
@@ -198,19 +294,47 @@ __device__ __forceinline__ float adam_update_fast(float m, float v, float inv_bc
     return __fdividef(m * inv_bc1, s + eps);
 }
 
-template <typename TP, int MODE>
+// Asks L2 for the 128-byte lines of [base, base + bytes), the block's threads sharing the lines.
+template <int NT>
+__device__ __forceinline__ void prefetch_l2(uintptr_t base, int64_t bytes) {
+    const uintptr_t first = base & ~(uintptr_t)127;
+    const int lines = (int)((base + bytes - first + 127) >> 7);
+    for (int i = threadIdx.x; i < lines; i += NT)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(first + ((uintptr_t)i << 7)));
+}
+
+// Prefetches what the tile kernel will read of one unit: the block's parameters and its slices of
+// the valid window rows.
+template <typename TP, int NT>
+__device__ __forceinline__ void prefetch_unit(const mab_tensor& T, int blk, int rows) {
+    const int dbs = T.d_block_size;
+    const int64_t blk_base = (int64_t)blk * dbs;
+    const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
+    const int kcnt = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
+    prefetch_l2<NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
+    const int64_t koff = (int64_t)blk * T.k_block_size_many;
+    for (int r = 0; r < rows; ++r) {
+        prefetch_l2<NT>(reinterpret_cast<uintptr_t>(T.I + koff + (int64_t)r * T.k), 2 * kcnt);
+        prefetch_l2<NT>(reinterpret_cast<uintptr_t>(T.V + koff + (int64_t)r * T.k), 2 * kcnt);
+    }
+}
+
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src_gmem) : "memory");
+}
+
+template <typename TP, int MODE, bool ALPHA>
 __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
-                                                 int max_entries, const WindowArgs& a) {
+                                                 int max_k, const WindowArgs& a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_first[WIN_MAX_TENSORS + 1];
     __shared__ int s_scan[36];
-    const int ecap = (max_entries + 3) & ~3;
-    float* m_acc = reinterpret_cast<float*>(smem_raw);
-    float* v_acc = m_acc + ecap;
-    uint32_t* ent = reinterpret_cast<uint32_t*>(v_acc + ecap);          // (bf16 value << 16) | position, later | slot
-    float* dense = reinterpret_cast<float*>(ent);                        // aliases ent once the entries are consumed
-    const int staging_words = max(ecap, WT_CHUNK);
-    uint32_t* bitmap = ent + staging_words;
+    const int rows = a.rows;
+    const int ecap = (rows * max_k + 3) & ~3;
+    const int rstride = wt_row_stride(max_k);
+    float2* mv = reinterpret_cast<float2*>(smem_raw);                        // (first moment | update, second moment) per slot
+    unsigned char* raw = reinterpret_cast<unsigned char*>(mv + ecap);       // rows x {I slice, V slice}, rstride bytes each
+    uint32_t* bitmap = reinterpret_cast<uint32_t*>(raw + rows * 2 * rstride);
     uint16_t* prefix = reinterpret_cast<uint16_t*>(bitmap + WT_WORDS);
     const int t = threadIdx.x;
 
@@ -218,36 +342,72 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     if (t == 0) s_first[n_tensors] = total_units;
     __syncthreads();
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
+    const int chunks_per_row = rstride >> 4;
+    if (MODE == MODE_STEP && (int)blockIdx.x < total_units) {
+        const int ti = find_tensor(s_first, n_tensors, blockIdx.x);
+        prefetch_unit<TP, WT_THREADS>(tensors[ti], blockIdx.x - s_first[ti], rows);
+    }
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int ti = find_tensor(s_first, n_tensors, unit);
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
+        if (MODE == MODE_STEP && unit + (int)gridDim.x < total_units) {     // the unit after this one: into L2 while this one runs
+            const int nu = unit + gridDim.x;
+            const int nti = find_tensor(s_first, n_tensors, nu);
+            prefetch_unit<TP, WT_THREADS>(tensors[nti], nu - s_first[nti], rows);
+        }
         const int dbs = T.d_block_size, nfull = T.topk_full_blocks_count;
         const int64_t blk_base = (int64_t)blk * dbs;
         const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
         const int64_t koff = (int64_t)blk * T.k_block_size_many;
-        const int16_t* __restrict__ I_blk = T.I + koff;
-        const uint16_t* __restrict__ V_blk = T.V + koff;
         const int64_t pitch = T.k;
-        const int rows = a.rows;
+        const uintptr_t I_blk = reinterpret_cast<uintptr_t>(T.I + koff), V_blk = reinterpret_cast<uintptr_t>(T.V + koff);
+        const uintptr_t I_lo = reinterpret_cast<uintptr_t>(T.I), I_hi = reinterpret_cast<uintptr_t>(T.I + (int64_t)a.m * pitch);
+        const uintptr_t V_lo = reinterpret_cast<uintptr_t>(T.V), V_hi = reinterpret_cast<uintptr_t>(T.V + (int64_t)a.m * pitch);
         const int E = rows * kcnt;
+        const float inv_kcnt = 1.0f / (float)kcnt;
         const bool g_bf16 = (T.grad_dtype == MAB_BF16);
 
-        // 1. stage the window entries, clear the bitmap and the compact moments
-        for (int r = 0; r < rows; ++r)
-            for (int j = t; j < kcnt; j += WT_THREADS)
-                ent[r * kcnt + j] = ((uint32_t)V_blk[r * pitch + j] << 16) | (uint32_t)(uint16_t)I_blk[r * pitch + j];
+        MAB_BTICK_DECL
+        // 1. stage the window entries: every row's slice of I and of V is copied asynchronously in
+        //    16-byte pieces from the 16-byte boundary below its first element; meanwhile clear the
+        //    bitmap and the compact moments
+        for (int idx = t; idx < rows * 2 * chunks_per_row; idx += WT_THREADS) {
+            const int c = idx % chunks_per_row, ra = idx / chunks_per_row;       // ra = 2 * row + array
+            const int r = ra >> 1;
+            const bool isV = ra & 1;
+            const uintptr_t seg = (isV ? V_blk : I_blk) + (uintptr_t)r * pitch * 2;
+            const uintptr_t src = (seg & ~(uintptr_t)15) + 16u * c;
+            if (src < seg + 2u * kcnt) {
+                unsigned char* dst = raw + ra * rstride + 16 * c;
+                const uintptr_t lo = isV ? V_lo : I_lo, hi = isV ? V_hi : I_hi;
+                if (src >= lo && src + 16 <= hi) cp_async_16(dst, reinterpret_cast<const void*>(src));
+                else                                             // a piece that sticks out of the array: element by element
+                    for (int b = 0; b < 16; b += 2)
+                        if (src + b >= lo && src + b + 2 <= hi)
+                            *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
         for (int i = t; i < WT_WORDS; i += WT_THREADS) bitmap[i] = 0u;
-        for (int i = t; i < E; i += WT_THREADS) { m_acc[i] = 0.0f; v_acc[i] = 0.0f; }
+        for (int i = t; i < E; i += WT_THREADS) mv[i] = make_float2(0.0f, 0.0f);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
+        MAB_BTICK(0);
+        // entry i = (row r, column j): its position sits at raw + 2r * rstride + (address of the row's slice & 15) + 2j
+        auto pos_ptr = [&](int i) -> uint16_t* {
+            const int r = (int)(((float)i + 0.5f) * inv_kcnt), j = i - r * kcnt;
+            return reinterpret_cast<uint16_t*>(raw + (2 * r) * rstride + ((I_blk + (uintptr_t)r * pitch * 2) & 15)) + j;
+        };
         // 2. mark touched positions
         for (int i = t; i < E; i += WT_THREADS) {
-            const uint32_t pos = ent[i] & 0xFFFFu;
+            const uint32_t pos = *pos_ptr(i);
             atomicOr(&bitmap[pos >> 5], 1u << (pos & 31));
         }
         __syncthreads();
+        MAB_BTICK(1);
         // 3. number them: prefix[w] = touched positions in words below w
         int cnt[WT_WORDS / WT_THREADS], local = 0;
 #pragma unroll
@@ -257,70 +417,68 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
 #pragma unroll
         for (int i = 0; i < WT_WORDS / WT_THREADS; ++i) { prefix[t * (WT_WORDS / WT_THREADS) + i] = (uint16_t)run; run += cnt[i]; }
         __syncthreads();
-        // 4. replace positions by slots, then accumulate row after row
+        MAB_BTICK(2);
+        // 4. positions -> slots (in place), then accumulate row after row
         for (int i = t; i < E; i += WT_THREADS) {
-            const uint32_t e = ent[i];
-            const uint32_t pos = e & 0xFFFFu;
-            const uint32_t slot = prefix[pos >> 5] + __popc(bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u));
-            ent[i] = (e & 0xFFFF0000u) | slot;
+            uint16_t* pp = pos_ptr(i);
+            const uint32_t pos = *pp;
+            *pp = (uint16_t)(prefix[pos >> 5] + __popc(bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u)));
         }
         __syncthreads();
+        MAB_BTICK(3);
         for (int r = 0; r < rows; ++r) {
+            const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(raw + (2 * r) * rstride + ((I_blk + (uintptr_t)r * pitch * 2) & 15));
+            const uint16_t* val_r = reinterpret_cast<const uint16_t*>(raw + (2 * r + 1) * rstride + ((V_blk + (uintptr_t)r * pitch * 2) & 15));
             const float w1 = a.w1[r], w2 = a.w2[r];
             for (int j = t; j < kcnt; j += WT_THREADS) {
-                const uint32_t e = ent[r * kcnt + j];
-                const int slot = e & 0xFFFFu;
-                const float val = __uint_as_float(e & 0xFFFF0000u);
-                m_acc[slot] = __fadd_rn(m_acc[slot], __fmul_rn(val, w1));
-                v_acc[slot] = __fadd_rn(v_acc[slot], __fmul_rn(__fmul_rn(val, val), w2));
+                const int slot = slot_r[j];
+                const float val = bf16_bits_to_f32(val_r[j]);
+                float2 acc = mv[slot];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
+                mv[slot] = acc;
             }
             __syncthreads();
         }
+        MAB_BTICK(4);
         // 5. moments -> update (rounded to the gradient's element type), slot by slot
-        for (int s = t; s < touched; s += WT_THREADS)
-            m_acc[s] = round_as(adam_update_fast(m_acc[s], v_acc[s], inv_bc1, inv_bc2, a.eps), g_bf16);
-        // 6. stream the block in chunks against a dense copy of the update
-        for (int c0 = 0; c0 < n_blk; c0 += WT_CHUNK) {
-            const int len = min(WT_CHUNK, n_blk - c0);
-            __syncthreads();                                   // ent / dense free, updates final
-            for (int i = t; i < WT_CHUNK / 4; i += WT_THREADS) reinterpret_cast<float4*>(dense)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            __syncthreads();
-            const int w0 = c0 >> 5, nw = (len + 31) >> 5;
-            for (int w = t; w < nw; w += WT_THREADS) {
-                uint32_t bits = bitmap[w0 + w];
-                int slot = prefix[w0 + w];
-                while (bits) {
-                    const int b = __ffs(bits) - 1;
-                    bits &= bits - 1;
-                    dense[w * 32 + b] = m_acc[slot++];
-                }
-            }
-            __syncthreads();
-            stream_range<TP, MODE, WT_THREADS>(T, a, dense, blk_base + c0, len);
+        for (int s = t; s < touched; s += WT_THREADS) {
+            const float2 acc = mv[s];
+            mv[s].x = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
         }
+        __syncthreads();
+        MAB_BTICK(5);
+        // 6. stream the whole block; each octet finds its updates through the bitmap
+        const SparseU src{bitmap, prefix, mv};
+        stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk);
+        MAB_BTICK(7);
         __syncthreads();                                       // everything is reused by the next unit
+        MAB_BTICK(8);
+#ifdef MAB_STATS
+        if (threadIdx.x == 0) atomicAdd(&g_stats_b[15], 1ull);
+#endif
     }
 }
 
-template <typename TP, int MODE>
+template <typename TP, int MODE, bool ALPHA>
 __global__ void __launch_bounds__(WT_THREADS)
-window_tile_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int max_entries,
+window_tile_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int max_k,
                    const __grid_constant__ WindowArgs a) {
-    window_tile_body<TP, MODE>(tensors, n_tensors, total_units, max_entries, a);
+    window_tile_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, max_k, a);
 }
 
 // Single tensor whose descriptor travels as a kernel argument (operator-level entry point).
-template <typename TP, int MODE>
+template <typename TP, int MODE, bool ALPHA>
 __global__ void __launch_bounds__(WT_THREADS)
-window_tile_single_kernel(const __grid_constant__ mab_tensor t, int total_units, int max_entries,
+window_tile_single_kernel(const __grid_constant__ mab_tensor t, int total_units, int max_k,
                           const __grid_constant__ WindowArgs a) {
-    window_tile_body<TP, MODE>(&t, 1, total_units, max_entries, a);
+    window_tile_body<TP, MODE, ALPHA>(&t, 1, total_units, max_k, a);
 }
 
 // ------------------------------------------------------------------------------------ wide kernel
 
 // TP: element type of `param` (MODE_STEP) or of the output buffer held in `param` (MODE_WRITE_UPDATE).
-template <typename TP, int MODE>
+template <typename TP, int MODE, bool ALPHA>
 __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  const WindowArgs& a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -350,53 +508,53 @@ __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ 
             for (int i = threadIdx.x; i < len; i += WIN_THREADS) sm.m_acc[i] = round_as(sm.m_acc[i], true);
             __syncthreads();
         }
-        stream_range<TP, MODE, WIN_THREADS>(T, a, sm.m_acc, blk_base + s0, len);
+        stream_range<TP, MODE, WIN_THREADS, ALPHA>(T, a, DenseU{sm.m_acc}, blk_base + s0, len);
         __syncthreads();   // shared accumulators are reused by the next unit
     }
 }
 
-template <typename TP, int MODE>
+template <typename TP, int MODE, bool ALPHA>
 __global__ void __launch_bounds__(WIN_THREADS)
 window_wide_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, const __grid_constant__ WindowArgs a) {
-    window_wide_body<TP, MODE>(tensors, n_tensors, total_units, a);
+    window_wide_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, a);
 }
 
-template <typename TP, int MODE>
+template <typename TP, int MODE, bool ALPHA>
 __global__ void __launch_bounds__(WIN_THREADS)
 window_wide_single_kernel(const __grid_constant__ mab_tensor t, int total_units, const __grid_constant__ WindowArgs a) {
-    window_wide_body<TP, MODE>(&t, 1, total_units, a);
+    window_wide_body<TP, MODE, ALPHA>(&t, 1, total_units, a);
 }
 
 // ------------------------------------------------------------------------------------ launch
 
 // `single` != nullptr: one tensor passed by value; else n_tensors descriptors in device memory.
-// units_tile / units_wide are the unit counts of the two variants; max_entries = rows * largest
-// k_block_size of the launch decides which one runs.
-template <typename TP, int MODE>
-static int launch_window(const mab_tensor* dev_tensors, const mab_tensor* single, int n_tensors, int units_tile,
-                         int units_wide, int max_entries, const WindowArgs& a, cudaStream_t s) {
+// units_tile / units_wide are the unit counts of the two variants; rows * max_k (the largest
+// k_block_size of the launch) decides which one runs.
+template <typename TP, int MODE, bool ALPHA>
+static int launch_window_impl(const mab_tensor* dev_tensors, const mab_tensor* single, int n_tensors, int units_tile,
+                              int units_wide, int max_k, const WindowArgs& a, cudaStream_t s) {
     const int sms = device_sm_count();
-    if (max_entries <= WT_MAX_ENTRIES) {
-        const int smem = wt_smem_bytes(max_entries);
-        const int per_sm = std::max(1, std::min(8, (227 * 1024) / (smem + 2048)));
+    if ((int64_t)a.rows * max_k <= WT_MAX_ENTRIES) {
+        const int smem = wt_smem_bytes(a.rows, max_k);
+        const int per_sm = std::max(1, std::min(8, (227 * 1024) / (smem + 3072)));
         const int grid = (int)std::min<int64_t>(units_tile, (int64_t)sms * per_sm);
         if (single) {
-            auto kern = window_tile_single_kernel<TP, MODE>;
+            auto kern = window_tile_single_kernel<TP, MODE, ALPHA>;
             MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            kern<<<grid, WT_THREADS, smem, s>>>(*single, units_tile, max_entries, a);
+            kern<<<grid, WT_THREADS, smem, s>>>(*single, units_tile, max_k, a);
         } else {
-            auto kern = window_tile_kernel<TP, MODE>;
+            auto kern = window_tile_kernel<TP, MODE, ALPHA>;
             MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            kern<<<grid, WT_THREADS, smem, s>>>(dev_tensors, n_tensors, units_tile, max_entries, a);
+            kern<<<grid, WT_THREADS, smem, s>>>(dev_tensors, n_tensors, units_tile, max_k, a);
         }
     } else {
         const int grid = (int)std::min<int64_t>(units_wide, (int64_t)sms * 2);
         if (single) {
-            auto kern = window_wide_single_kernel<TP, MODE>;
+            auto kern = window_wide_single_kernel<TP, MODE, ALPHA>;
             MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WIN_SMEM_BYTES));
             kern<<<grid, WIN_THREADS, WIN_SMEM_BYTES, s>>>(*single, units_wide, a);
         } else {
-            auto kern = window_wide_kernel<TP, MODE>;
+            auto kern = window_wide_kernel<TP, MODE, ALPHA>;
             MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WIN_SMEM_BYTES));
             kern<<<grid, WIN_THREADS, WIN_SMEM_BYTES, s>>>(dev_tensors, n_tensors, units_wide, a);
         }
@@ -407,10 +565,22 @@ static int launch_window(const mab_tensor* dev_tensors, const mab_tensor* single
     return MAB_OK;
 }
 
+// `single` != nullptr: one tensor passed by value; else n_tensors descriptors in device memory.
+// units_tile / units_wide are the unit counts of the two variants; rows * max_k (the largest
+// k_block_size of the launch) decides which one runs.
+template <typename TP, int MODE>
+static int launch_window(const mab_tensor* dev_tensors, const mab_tensor* single, int n_tensors, int units_tile,
+                         int units_wide, int max_k, const WindowArgs& a, cudaStream_t s) {
+    if (MODE == MODE_STEP && a.alpha != 0.0f)
+        return launch_window_impl<TP, MODE, true>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
+    return launch_window_impl<TP, MODE, false>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
+}
+
 int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double beta2, double eps, float alpha, int qbs) {
     MAB_REQUIRE(steps >= 1, MAB_ERR_BAD_ARG, "steps must be >= 1 (got %lld)", (long long)steps);
     MAB_REQUIRE(m >= 1 && m <= MAB_MAX_WINDOW, MAB_ERR_LIMIT, "m=%d outside [1, %d]", m, MAB_MAX_WINDOW);
     a.rows = (int)std::min<int64_t>(steps, m);
+    a.m = m;
     for (int r = 0; r < MAB_MAX_WINDOW; ++r) { a.w1[r] = 0.f; a.w2[r] = 0.f; }
     for (int r = 0; r < a.rows; ++r) {
         const int64_t age = ((steps - 1) - r) % m;
@@ -427,11 +597,11 @@ int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double b
     return MAB_OK;
 }
 
-int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_entries,
+int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_k,
                        int param_dtype, const WindowArgs& a, cudaStream_t s) {
     if (param_dtype == MAB_F32)
-        return launch_window<float, MODE_STEP>(dev_tensors, nullptr, n_tensors, units_tile, units_wide, max_entries, a, s);
-    return launch_window<uint16_t, MODE_STEP>(dev_tensors, nullptr, n_tensors, units_tile, units_wide, max_entries, a, s);
+        return launch_window<float, MODE_STEP>(dev_tensors, nullptr, n_tensors, units_tile, units_wide, max_k, a, s);
+    return launch_window<uint16_t, MODE_STEP>(dev_tensors, nullptr, n_tensors, units_tile, units_wide, max_k, a, s);
 }
 
 int units_b_of(const mab_tensor& t) {
@@ -443,6 +613,14 @@ int units_b_of(const mab_tensor& t) {
 }  // namespace mab
 
 using namespace mab;
+
+#ifdef MAB_STATS
+extern "C" int mab_debug_stats_b(unsigned long long* out16, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out16, mab::g_stats_b, sizeof(mab::g_stats_b));
+    if (e == cudaSuccess && reset) { unsigned long long z[16] = {0}; e = cudaMemcpyToSymbol(mab::g_stats_b, z, sizeof(z)); }
+    return e == cudaSuccess ? 0 : -3;
+}
+#endif
 
 extern "C" int mab_compute_microadam_update(int blocks, int threads, int carveout, int64_t steps, double beta1, double beta2,
                                             double eps, int64_t dbs, int64_t kbs, int64_t d, int64_t m, int64_t k,
@@ -473,9 +651,8 @@ extern "C" int mab_compute_microadam_update(int blocks, int threads, int carveou
     const int units_wide = units_b_of(t);
     const int units_tile = t.topk_full_blocks_count + (t.k_block_size_few > 0 ? 1 : 0);
     if (units_tile == 0) return MAB_OK;
-    const int64_t max_entries = (int64_t)a.rows * std::max(t.k_block_size_many, t.k_block_size_few);
+    const int max_k = std::max(t.k_block_size_many, t.k_block_size_few);
     cudaStream_t s = (cudaStream_t)stream;
-    const int me = (int)std::min<int64_t>(max_entries, INT32_MAX);
-    if (out_dtype == MAB_F32) return launch_window<float, MODE_WRITE_UPDATE>(nullptr, &t, 1, units_tile, units_wide, me, a, s);
-    return launch_window<uint16_t, MODE_WRITE_UPDATE>(nullptr, &t, 1, units_tile, units_wide, me, a, s);
+    if (out_dtype == MAB_F32) return launch_window<float, MODE_WRITE_UPDATE>(nullptr, &t, 1, units_tile, units_wide, max_k, a, s);
+    return launch_window<uint16_t, MODE_WRITE_UPDATE>(nullptr, &t, 1, units_tile, units_wide, max_k, a, s);
 }

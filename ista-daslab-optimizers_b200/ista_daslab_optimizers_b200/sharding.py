@@ -123,51 +123,56 @@ class ShardedMicroAdam(MicroAdam):
     def _slice_of(self, p):
         return self._my_slice.get(id(p))
 
-    # ---------------------------------------------------------------------------- exchange
-    def _build_gather_views(self):
-        """Per rank, the flat views it owns; views adjacent in memory (parameters that are slices
-        of one flat buffer) are merged, so that a flat model needs one piece per rank."""
-        per_rank: List[List[torch.Tensor]] = [[] for _ in range(self.world_size)]
-        last: List[Optional[Tuple[int, int, int, torch.dtype]]] = [None] * self.world_size   # storage ptr, begin, end, dtype
-        for pc in self.plan:
-            p = self._all_params[pc.index]
-            if not p.is_contiguous():
-                raise RuntimeError('sharded parameters must be contiguous')
-            es = p.element_size()
-            sp = p.untyped_storage().data_ptr()
-            begin = p.data_ptr() + pc.lo * es
-            end = p.data_ptr() + pc.hi * es
-            prev = last[pc.rank]
-            if prev is not None and prev[0] == sp and prev[2] == begin and prev[3] == p.dtype:
-                begin = prev[1]
-                per_rank[pc.rank].pop()
-            n = (end - begin) // es
-            view = torch.empty(0, dtype=p.dtype, device=p.device).set_(p.untyped_storage(), (begin - sp) // es, (n,))
-            per_rank[pc.rank].append(view)
-            last[pc.rank] = (sp, begin, end, p.dtype)
-        return per_rank
-
     def _after_update(self):
         if not self.gather:
             return
         if self._gather_views is None:
-            self._gather_views = self._build_gather_views()
-        views = self._gather_views
-        group = self.process_group
-        counts = {len(v) for v in views}
-        self.last_gather_bytes = sum(v.numel() * v.element_size() for r, vs in enumerate(views) if r != self.rank for v in vs)
-        backend = dist.get_backend(group)
-        if counts == {1} and backend == 'nccl' and len({v[0].dtype for v in views}) == 1:
-            # one piece per rank (flat model): a single all-gather with unequal pieces, in place
-            dist.all_gather([v[0] for v in views], views[self.rank][0], group=group)
-            return
-        works = []
-        for r, vs in enumerate(views):
-            src = dist.get_global_rank(group, r) if group is not None else r
-            for v in vs:
-                works.append(dist.broadcast(v, src=src, group=group, async_op=True))
-        for w in works:
-            w.wait()
+            self._gather_views = build_gather_views(self.plan, self._all_params, self.world_size)
+        self.last_gather_bytes = exchange_pieces(self._gather_views, self.rank, self.process_group)
+
+
+def build_gather_views(plan: Sequence[Piece], params: Sequence[torch.Tensor], world_size: int) -> List[List[torch.Tensor]]:
+    """Per rank, flat views of the parameter ranges it owns.  Views adjacent in memory (parameters
+    that are slices of one flat buffer) are merged, so that a flat model needs one view per rank."""
+    per_rank: List[List[torch.Tensor]] = [[] for _ in range(world_size)]
+    last: List[Optional[Tuple[int, int, int, torch.dtype]]] = [None] * world_size   # storage ptr, begin, end, dtype
+    for pc in plan:
+        p = params[pc.index]
+        if not p.is_contiguous():
+            raise RuntimeError('sharded parameters must be contiguous')
+        es = p.element_size()
+        storage = p.untyped_storage()
+        sp = storage.data_ptr()
+        begin = p.data_ptr() + pc.lo * es
+        end = p.data_ptr() + pc.hi * es
+        prev = last[pc.rank]
+        if prev is not None and prev[0] == sp and prev[2] == begin and prev[3] == p.dtype:
+            begin = prev[1]
+            per_rank[pc.rank].pop()
+        n = (end - begin) // es
+        view = torch.empty(0, dtype=p.dtype, device=p.device).set_(storage, (begin - sp) // es, (n,))
+        per_rank[pc.rank].append(view)
+        last[pc.rank] = (sp, begin, end, p.dtype)
+    return per_rank
+
+
+def exchange_pieces(views: List[List[torch.Tensor]], rank: int, group=None) -> int:
+    """Every rank sends the ranges it owns (views[rank]) to all others, in place.  One all-gather with
+    unequal pieces when every rank owns exactly one view (NCCL); one broadcast per view otherwise.
+    Returns the bytes this rank received."""
+    received = sum(v.numel() * v.element_size() for r, vs in enumerate(views) if r != rank for v in vs)
+    backend = dist.get_backend(group)
+    if {len(v) for v in views} == {1} and backend == 'nccl' and len({v[0].dtype for v in views}) == 1:
+        dist.all_gather([v[0] for v in views], views[rank][0], group=group)
+        return received
+    works = []
+    for r, vs in enumerate(views):
+        src = dist.get_global_rank(group, r) if group is not None else r
+        for v in vs:
+            works.append(dist.broadcast(v, src=src, group=group, async_op=True))
+    for w in works:
+        w.wait()
+    return received
 
 
 def flatten_parameters(params: Sequence[torch.nn.Parameter]) -> torch.Tensor:

@@ -1,0 +1,50 @@
+"""A sharded step equals the unsharded step bit for bit (each rank's shard run in turn on one GPU)."""
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(t):
+    return t.detach().cpu().contiguous().view(torch.uint8) if t.dtype != torch.uint8 else t.detach().cpu()
+
+
+@pytest.mark.parametrize('world', [2, 3])
+@pytest.mark.parametrize('name', ['bf16_wd', 'mixed_fp32_alpha'])
+def test_sharded_equals_unsharded(name, world):
+    from ista_daslab_optimizers_b200.sharding import ShardedMicroAdam
+    case = cases.CASES[name]
+    full = cases.CudaAdapter(case, case.params())
+    kw = dict(m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init, alpha=case.alpha, betas=case.betas,
+              weight_decay=case.weight_decay, eps=case.eps, d_block_size=case.d_block_size)
+    ranks = []
+    for r in range(world):
+        params = [torch.nn.Parameter(p.cuda()) for p in case.params()]
+        ranks.append((params, ShardedMicroAdam(params, rank=r, world_size=world, gather=False, **kw)))
+    plan = ranks[0][1].plan
+    assert {pc.rank for pc in plan} == set(range(world))
+    qbs, m = case.qbs, case.m
+    for t in range(4):
+        grads = case.grads(t)
+        full.step(grads)
+        for params, opt in ranks:
+            for p, g in zip(params, grads):
+                p.grad = g.cuda()
+            opt.step()
+        for pc in plan:
+            params, opt = ranks[pc.rank]
+            su, sr = full.state(pc.index), opt.state[params[pc.index]]
+            dbs, k_many = su['d_block_size'], su['k_block_size_many']
+            assert sr['d'] == pc.hi - pc.lo
+            row = (su['index'] - 1) % m
+            c0 = (pc.lo // dbs) * k_many
+            assert torch.equal(su['I'][row, c0:c0 + sr['k']], sr['I'][row])
+            assert torch.equal(bits(su['V'][row, c0:c0 + sr['k']]), bits(sr['V'][row]))
+            assert torch.equal(su['error'][pc.lo // 2:(pc.hi + 1) // 2], sr['error'])
+            used = (sr['d'] + qbs - 1) // qbs
+            q0 = pc.lo // qbs
+            assert torch.equal(bits(su['min_vals'][q0:q0 + used]), bits(sr['min_vals'][:used]))
+            assert torch.equal(bits(su['max_vals'][q0:q0 + used]), bits(sr['max_vals'][:used]))
+            assert torch.equal(bits(full.param(pc.index).view(-1)[pc.lo:pc.hi]), bits(params[pc.index].data.view(-1)[pc.lo:pc.hi]))
