@@ -329,6 +329,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int s_first[WIN_MAX_TENSORS + 1];
     __shared__ int s_scan[36];
+    __shared__ int s_pos_off[MAB_MAX_WINDOW], s_val_off[MAB_MAX_WINDOW];   // byte offsets of each row's first position / value in raw
     const int rows = a.rows;
     const int ecap = (rows * max_k + 3) & ~3;
     const int rstride = wt_row_stride(max_k);
@@ -374,20 +375,28 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         // 1. stage the window entries: every row's slice of I and of V is copied asynchronously in
         //    16-byte pieces from the 16-byte boundary below its first element; meanwhile clear the
         //    bitmap and the compact moments
-        for (int idx = t; idx < rows * 2 * chunks_per_row; idx += WT_THREADS) {
-            const int c = idx % chunks_per_row, ra = idx / chunks_per_row;       // ra = 2 * row + array
+        if (t < rows) {
+            s_pos_off[t] = (2 * t) * rstride + (int)((I_blk + (uintptr_t)t * pitch * 2) & 15);
+            s_val_off[t] = (2 * t + 1) * rstride + (int)((V_blk + (uintptr_t)t * pitch * 2) & 15);
+        }
+        for (int ra = t >> 6; ra < rows * 2; ra += WT_THREADS >> 6) {               // ra = 2 * row + array; 64 threads per slice
             const int r = ra >> 1;
             const bool isV = ra & 1;
             const uintptr_t seg = (isV ? V_blk : I_blk) + (uintptr_t)r * pitch * 2;
-            const uintptr_t src = (seg & ~(uintptr_t)15) + 16u * c;
-            if (src < seg + 2u * kcnt) {
-                unsigned char* dst = raw + ra * rstride + 16 * c;
-                const uintptr_t lo = isV ? V_lo : I_lo, hi = isV ? V_hi : I_hi;
-                if (src >= lo && src + 16 <= hi) cp_async_16(dst, reinterpret_cast<const void*>(src));
-                else                                             // a piece that sticks out of the array: element by element
-                    for (int b = 0; b < 16; b += 2)
-                        if (src + b >= lo && src + b + 2 <= hi)
-                            *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
+            const uintptr_t seg_end = seg + 2u * kcnt;
+            const uintptr_t first = seg & ~(uintptr_t)15;
+            const uintptr_t lo = isV ? V_lo : I_lo, hi = isV ? V_hi : I_hi;
+            unsigned char* dst_row = raw + ra * rstride;
+            for (int c = t & 63; c < chunks_per_row; c += 64) {
+                const uintptr_t src = first + 16u * c;
+                if (src < seg_end) {
+                    unsigned char* dst = dst_row + 16 * c;
+                    if (src >= lo && src + 16 <= hi) cp_async_16(dst, reinterpret_cast<const void*>(src));
+                    else                                         // a piece that sticks out of the array: element by element
+                        for (int b = 0; b < 16; b += 2)
+                            if (src + b >= lo && src + b + 2 <= hi)
+                                *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
+                }
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -399,7 +408,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         // entry i = (row r, column j): its position sits at raw + 2r * rstride + (address of the row's slice & 15) + 2j
         auto pos_ptr = [&](int i) -> uint16_t* {
             const int r = (int)(((float)i + 0.5f) * inv_kcnt), j = i - r * kcnt;
-            return reinterpret_cast<uint16_t*>(raw + (2 * r) * rstride + ((I_blk + (uintptr_t)r * pitch * 2) & 15)) + j;
+            return reinterpret_cast<uint16_t*>(raw + s_pos_off[r]) + j;
         };
         // 2. mark touched positions
         for (int i = t; i < E; i += WT_THREADS) {
@@ -427,8 +436,8 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         __syncthreads();
         MAB_BTICK(3);
         for (int r = 0; r < rows; ++r) {
-            const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(raw + (2 * r) * rstride + ((I_blk + (uintptr_t)r * pitch * 2) & 15));
-            const uint16_t* val_r = reinterpret_cast<const uint16_t*>(raw + (2 * r + 1) * rstride + ((V_blk + (uintptr_t)r * pitch * 2) & 15));
+            const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(raw + s_pos_off[r]);
+            const uint16_t* val_r = reinterpret_cast<const uint16_t*>(raw + s_val_off[r]);
             const float w1 = a.w1[r], w2 = a.w2[r];
             for (int j = t; j < kcnt; j += WT_THREADS) {
                 const int slot = slot_r[j];
