@@ -113,4 +113,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rne(float a, float b) {
     return d;
 }
 
+// Lane-wise maximum of two packed bf16 pairs.
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 }  // namespace mab

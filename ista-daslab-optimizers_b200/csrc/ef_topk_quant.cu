@@ -118,7 +118,7 @@ struct Stage {
         mn = reinterpret_cast<uint16_t*>(raw + g_bytes + ef_bytes);
         mx = reinterpret_cast<uint16_t*>(raw + g_bytes + ef_bytes + st_bytes);
     }
-    static int bytes(int stage_elems, int qshift) {
+    __host__ __device__ static int bytes(int stage_elems, int qshift) {
         const int g_bytes = (stage_elems * (int)sizeof(TG) + 127) & ~127;
         const int ef_bytes = ((stage_elems >> 1) + 127) & ~127;
         const int st_bytes = ((((stage_elems >> qshift) + 4) * 2) + 15) & ~15;
@@ -149,9 +149,9 @@ __device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG
 template <typename TG>
 __global__ void __launch_bounds__(SEL_THREADS, 1)
 ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
-    extern __shared__ __align__(128) unsigned char stage_raw[];
-    __shared__ SelectSmem sm;
-    __shared__ FastSelSmem fs;
+    extern __shared__ __align__(128) unsigned char stage_raw[];      // [staging area | SelectSmem | FastSelSmem]
+    SelectSmem& sm = *reinterpret_cast<SelectSmem*>(stage_raw + Stage<TG>::bytes(stage_elems, qshift));
+    FastSelSmem& fs = *reinterpret_cast<FastSelSmem*>(stage_raw + Stage<TG>::bytes(stage_elems, qshift) + sizeof(SelectSmem));
     __shared__ int s_first[A_MAX_TENSORS + 1];
     __shared__ __align__(8) uint64_t s_bar;
     const Stage<TG> st(stage_raw, stage_elems, qshift);
@@ -259,7 +259,9 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
         const int64_t row_off = (int64_t)T.ring_index * T.k + (int64_t)blk * T.k_block_size_many;
         uint16_t* v_out = T.V + row_off;
         int n_cand = 0;
-        const bool fast = fast_select(a, omax, n, k, guess, sm, fs, n_cand);
+        int oct_slot[SEL_OCTETS];
+        bool compact_octets;
+        const bool fast = fast_select(a, omax, n, k, guess, sm, fs, n_cand, oct_slot, compact_octets, sizeof(TG) == 2 ? 16 : 0);
         if (!fast) {
             int need;
             const int T_key = block_kth_key_bisect(a, k, sm, need);
@@ -290,11 +292,16 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
             const int o = j * SEL_THREADS + (int)threadIdx.x;
             const int cnt = n - o * 8;
             const uint32_t sel = sel_bytes[o];
-            if (fast) {
-#ifndef MAB_X_SKIP_ZERO
+            if (fast && compact_octets) {
+                if (oct_slot[j] >= 0) {                   // the copy already has the selected elements zeroed
+                    const float4 lo4 = reinterpret_cast<const float4*>(fs.oct_val[oct_slot[j]])[0];
+                    const float4 hi4 = reinterpret_cast<const float4*>(fs.oct_val[oct_slot[j]])[1];
+                    a[j][0] = lo4.x; a[j][1] = lo4.y; a[j][2] = lo4.z; a[j][3] = lo4.w;
+                    a[j][4] = hi4.x; a[j][5] = hi4.y; a[j][6] = hi4.z; a[j][7] = hi4.w;
+                }
+            } else if (fast) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) a[j][e] = (sel & (1u << e)) ? 0.0f : a[j][e];
-#endif
             } else if (sel) {
                 const int word = o >> 2;
                 int p = sm.sel_before[word] + __popc(sm.sel_bm[word] & ((1u << (8 * (o & 3))) - 1u));
@@ -309,23 +316,16 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
 #pragma unroll
                 for (int e = 0; e < 8; ++e) if (e < cnt) { lo = fminf(lo, a[j][e]); hi = fmaxf(hi, a[j][e]); }
             }
-#ifndef MAB_X_SKIP_SHUFFLE
-            for (int off = 1; off < lanes_per_qb; off <<= 1) {
-                lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-                hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-            }
-#endif
+            // bf16 rounding is monotone and odd, so the block statistics are the lane-wise maximum of the
+            // rounded (-min, max) pairs: one packed value and one packed max per shuffle step
+            uint32_t st_b = pack_bf16x2_rne(-lo, hi);
+            for (int off = 1; off < lanes_per_qb; off <<= 1) st_b = max_bf16x2(st_b, __shfl_xor_sync(0xffffffffu, st_b, off));
             if (cnt > 0) {
-                const uint32_t st_b = pack_bf16x2_rne(lo, hi);
-                const uint16_t mn_b = (uint16_t)(st_b & 0xFFFFu), mx_b = (uint16_t)(st_b >> 16);
+                const uint16_t mn_b = (uint16_t)((st_b & 0xFFFFu) ^ 0x8000u), mx_b = (uint16_t)(st_b >> 16);
                 if ((o & (lanes_per_qb - 1)) == 0) { mn_out[o >> oshift] = mn_b; mx_out[o >> oshift] = mx_b; }
                 const QParams q2 = qparams(mn_b, mx_b);
                 if (cnt >= 8) {
-#ifdef MAB_X_SKIP_ENCODE
-                    const uint32_t w = __float_as_uint(a[j][0] + q2.u);
-#else
                     const uint32_t w = encode_octet(a[j], q2);
-#endif
                     if (vec_e) *reinterpret_cast<uint32_t*>(ef_out + o * 4) = w;
                     else {
 #pragma unroll
@@ -352,18 +352,19 @@ int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total
     int qshift = 0;
     while ((1 << qshift) < qbs) ++qshift;
     // stage whole tiles when they fit beside the kernel's static shared memory, else load directly
-    const int limit = device_max_optin_smem() - 48 * 1024;
+    const int scratch = (int)(sizeof(SelectSmem) + sizeof(FastSelSmem));
+    const int limit = device_max_optin_smem() - 4 * 1024 - scratch;
     if (grad_dtype == MAB_F32) {
         int stage_elems = max_dbs;
         if (Stage<float>::bytes(stage_elems, qshift) > limit) stage_elems = 0;
-        const int smem = stage_elems ? Stage<float>::bytes(stage_elems, qshift) : 0;
+        const int smem = Stage<float>::bytes(stage_elems, qshift) + scratch;
         auto kern = ef_topk_quant_kernel<float>;
         MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems);
     } else {
         int stage_elems = max_dbs;
         if (Stage<uint16_t>::bytes(stage_elems, qshift) > limit) stage_elems = 0;
-        const int smem = stage_elems ? Stage<uint16_t>::bytes(stage_elems, qshift) : 0;
+        const int smem = Stage<uint16_t>::bytes(stage_elems, qshift) + scratch;
         auto kern = ef_topk_quant_kernel<uint16_t>;
         MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems);

@@ -36,11 +36,17 @@ __device__ unsigned long long g_stats[32];
 #endif
 
 constexpr int FS_CAND_CAP = 4096;
+constexpr int FS_OCT_CAP = 1024;          // octets holding a candidate that the compact copy can take
 constexpr int FS_OCTET_LEVEL_K = 384;     // above this k the bound is searched on octet maxima
 
-struct FastSelSmem {
+struct __align__(16) FastSelSmem {
+    float    oct_val[FS_OCT_CAP][8];      // compact copy of the octets that hold a candidate (k <= FS_OCTET_LEVEL_K)
     float    cand_val[FS_CAND_CAP];       // signed value
     uint16_t cand_pos[FS_CAND_CAP];       // position in the tile; bit 15 set once selected
+    uint16_t cand_ref[FS_CAND_CAP];       // 8 * (index in oct_val) + element, when the compact copy is in use
+    uint16_t oct_id[FS_OCT_CAP];          // tile octet of each compact octet
+    int      wcount[SEL_OCTETS * 32];      // candidate octets per (octet row, warp), then their exclusive prefix
+    int      n_oct;
     int      hist[256];
     int      member[32];                  // candidate indices of the members of the final bin
     int      rot[64];                     // rotating counters of the octet-level probes
@@ -96,12 +102,25 @@ __device__ __forceinline__ int fs_lower_bound(const float (&omax)[SEL_OCTETS], f
 // Exact selection of the k largest keys among the tile's elements.  On success (true) sm.sel_bm /
 // sm.sel_before hold the result, candidates flagged with bit 15 of cand_pos are the selected
 // ones, n_cand their number.  Uniform: every thread gets the same return value.
+//
+// For small k the candidates are gathered in two steps that keep the per-element work off the
+// 1024-thread path: octets whose maximum reaches the bound (about one in eight) are copied to a
+// compact array in shared memory, one warp-aggregated atomic per warp and octet row, and the
+// per-element test then runs over that array only.  In that case `oct_slot[j]` tells the owner of
+// octet j where its copy is (-1: none), and on return the selected elements of the copies are
+// already zero: the owner reloads its octets from there instead of testing selection bits.
+// key_zero_bits = number of low key bits that are always zero (16 when the values are bf16): a
+// histogram bin no wider than that holds a single key value, so its members are exact ties.
 __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], const float (&omax)[SEL_OCTETS], int n, int k,
-                                            int& guess, SelectSmem& sm, FastSelSmem& fs, int& n_cand) {
+                                            int& guess, SelectSmem& sm, FastSelSmem& fs, int& n_cand,
+                                            int (&oct_slot)[SEL_OCTETS], bool& compact_octets, int key_zero_bits) {
     MAB_TICK_DECL
     const int t = threadIdx.x, lane = lane_id(), warp = warp_id();
     float tmax = fmaxf(fmaxf(omax[0], omax[1]), fmaxf(omax[2], omax[3]));
 
+    compact_octets = false;
+#pragma unroll
+    for (int j = 0; j < SEL_OCTETS; ++j) oct_slot[j] = -1;
     // block maximum key
     if (t == 0) fs.kmax = 0;
     __syncthreads();
@@ -123,25 +142,93 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
     MAB_TICK(17);
 
     // ---- compact the candidates --------------------------------------------------------------
-    int mine = 0;
+    int C = 0;
+    bool by_octets = !octets;                                  // small k: through the compact octet copy
+    if (by_octets) {
+        // slots of the compact copy: (octet row, warp) segments in a fixed order, lanes in order inside
+        unsigned ball[SEL_OCTETS];
 #pragma unroll
-    for (int j = 0; j < SEL_OCTETS; ++j)
+        for (int j = 0; j < SEL_OCTETS; ++j) {
+            ball[j] = __ballot_sync(0xffffffffu, omax[j] >= T_lo_f);
+            if (lane == 0) fs.wcount[j * 32 + warp] = __popc(ball[j]);
+        }
+        __syncthreads();
+        if (warp == 0) {
+            int c[SEL_OCTETS], sum = 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) mine += (fabsf(a[j][e]) >= T_lo_f) ? 1 : 0;
-    int C;
-    int at = block_exclusive_scan(mine, sm.scan, C);
-    if (C > FS_CAND_CAP) { MAB_STAT(4, 1); return false; }   // uniform: C is a block-wide value
-    if (mine) {
+            for (int i = 0; i < SEL_OCTETS; ++i) { c[i] = fs.wcount[lane * SEL_OCTETS + i]; sum += c[i]; }
+            int inc = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += v; }
+            int run = inc - sum;
+#pragma unroll
+            for (int i = 0; i < SEL_OCTETS; ++i) { fs.wcount[lane * SEL_OCTETS + i] = run; run += c[i]; }
+            if (lane == 31) fs.n_oct = inc;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < SEL_OCTETS; ++j) {
+            if ((ball[j] >> lane) & 1u) {
+                const int slot = fs.wcount[j * 32 + warp] + __popc(ball[j] & ((1u << lane) - 1u));
+                if (slot < FS_OCT_CAP) {
+                    reinterpret_cast<float4*>(fs.oct_val[slot])[0] = make_float4(a[j][0], a[j][1], a[j][2], a[j][3]);
+                    reinterpret_cast<float4*>(fs.oct_val[slot])[1] = make_float4(a[j][4], a[j][5], a[j][6], a[j][7]);
+                    fs.oct_id[slot] = (uint16_t)(j * SEL_THREADS + t);
+                    oct_slot[j] = slot;
+                }
+            }
+        }
+        __syncthreads();
+        const int n_oct = fs.n_oct;
+        if (n_oct > FS_OCT_CAP) {                              // uniform: too clustered for the copy, use the registers
+            by_octets = false;
+#pragma unroll
+            for (int j = 0; j < SEL_OCTETS; ++j) oct_slot[j] = -1;
+        } else {
+            // one compact octet per thread (FS_OCT_CAP <= SEL_THREADS); read once to count, once to copy
+            int mine = 0;
+            if (t < n_oct) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) mine += (fabsf(fs.oct_val[t][e]) >= T_lo_f) ? 1 : 0;
+            }
+            int at = block_exclusive_scan(mine, sm.scan, C);
+            if (C > FS_CAND_CAP) { MAB_STAT(4, 1); return false; }
+            if (mine) {
+                const uint32_t o = fs.oct_id[t];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float ve = fs.oct_val[t][e];
+                    if (fabsf(ve) >= T_lo_f) {
+                        fs.cand_val[at] = ve;
+                        fs.cand_pos[at] = (uint16_t)((o << 3) | e);
+                        fs.cand_ref[at] = (uint16_t)((t << 3) | e);
+                        ++at;
+                    }
+                }
+            }
+        }
+    }
+    if (!by_octets) {
+        int mine = 0;
 #pragma unroll
         for (int j = 0; j < SEL_OCTETS; ++j)
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-                if (fabsf(a[j][e]) >= T_lo_f) {
-                    fs.cand_val[at] = a[j][e];
-                    fs.cand_pos[at] = (uint16_t)(((j * SEL_THREADS + t) << 3) | e);
-                    ++at;
-                }
+            for (int e = 0; e < 8; ++e) mine += (fabsf(a[j][e]) >= T_lo_f) ? 1 : 0;
+        int at = block_exclusive_scan(mine, sm.scan, C);
+        if (C > FS_CAND_CAP) { MAB_STAT(4, 1); return false; }   // uniform: C is a block-wide value
+        if (mine) {
+#pragma unroll
+            for (int j = 0; j < SEL_OCTETS; ++j)
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    if (fabsf(a[j][e]) >= T_lo_f) {
+                        fs.cand_val[at] = a[j][e];
+                        fs.cand_pos[at] = (uint16_t)(((j * SEL_THREADS + t) << 3) | e);
+                        ++at;
+                    }
+        }
     }
+    compact_octets = by_octets;
     n_cand = C;
     MAB_TICK(18);
     MAB_STAT(8, C);
@@ -188,10 +275,10 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
         r_hi = (int)min((int64_t)r_hi, (int64_t)n_lo + ((int64_t)1 << sh) - 1);
         r_lo = n_lo;
         MAB_STAT(9, 1);
-        if (R <= 32 || sh == 0) break;
+        if (R <= 32 || sh <= key_zero_bits) break;
     }
     MAB_TICK(19);
-    if (R > 32 && sh != 0) { MAB_STAT(5, 1); return false; } // cannot happen within 5 levels of 8 bits; stay safe
+    if (R > 32 && sh > key_zero_bits) { MAB_STAT(5, 1); return false; } // cannot happen within 5 levels of 8 bits; stay safe
 
     // ---- members of the final bin: rank them (<= 32) or treat them as ties of one key -------------
     const bool by_rank = R <= 32;
@@ -229,7 +316,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
             }
         }
     } else {
-        need_ties = k_rem;                                     // r_lo == r_hi: every member has the k-th key
+        need_ties = k_rem;                                     // the bin holds one key value: every member has the k-th key
     }
     MAB_TICK(20);
     resolve_selection(need_ties, sm);                          // starts with a barrier
@@ -238,9 +325,16 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
         // flag the ties that made it
         for (int i = t; i < C; i += SEL_THREADS) {
             const uint32_t pos = fs.cand_pos[i];
-            if (!(pos & 0x8000u) && fs_key(fs.cand_val[i]) == r_lo && (sm.sel_bm[pos >> 5] >> (pos & 31)) & 1u)
+            const int key = fs_key(fs.cand_val[i]);
+            if (!(pos & 0x8000u) && key >= r_lo && key <= r_hi && (sm.sel_bm[pos >> 5] >> (pos & 31)) & 1u)
                 fs.cand_pos[i] = (uint16_t)(pos | 0x8000u);
         }
+        __syncthreads();
+    }
+    if (by_octets) {
+        // the residual of the copied octets: selected elements become 0 (their values stay in cand_val)
+        for (int i = t; i < C; i += SEL_THREADS)
+            if (fs.cand_pos[i] & 0x8000u) { const uint32_t ref = fs.cand_ref[i]; fs.oct_val[ref >> 3][ref & 7] = 0.0f; }
         __syncthreads();
     }
     MAB_STAT(0, 1);
