@@ -157,13 +157,24 @@ def build_gather_views(plan: Sequence[Piece], params: Sequence[torch.Tensor], wo
 
 
 def exchange_pieces(views: List[List[torch.Tensor]], rank: int, group=None) -> int:
-    """Every rank sends the ranges it owns (views[rank]) to all others, in place.  One all-gather with
-    unequal pieces when every rank owns exactly one view (NCCL); one broadcast per view otherwise.
-    Returns the bytes this rank received."""
+    """Every rank sends the ranges it owns (views[rank]) to all others, in place: an all-gather with
+    unequal pieces.  NCCL: grouped point-to-point sends and receives; other backends: one broadcast
+    per view.  Returns the bytes this rank received."""
     received = sum(v.numel() * v.element_size() for r, vs in enumerate(views) if r != rank for v in vs)
     backend = dist.get_backend(group)
-    if {len(v) for v in views} == {1} and backend == 'nccl' and len({v[0].dtype for v in views}) == 1:
-        dist.all_gather([v[0] for v in views], views[rank][0], group=group)
+    if backend == 'nccl':
+        # every rank sends its views to every peer and receives theirs in place, as one NCCL group: all
+        # NVLink ports of every GPU are busy in both directions, whatever the sizes of the pieces
+        world = len(views)
+        ops = []
+        for peer in range(world):
+            if peer == rank:
+                continue
+            dst = dist.get_global_rank(group, peer) if group is not None else peer
+            ops += [dist.P2POp(dist.isend, v, dst, group) for v in views[rank]]
+            ops += [dist.P2POp(dist.irecv, v, dst, group) for v in views[peer]]
+        for w in dist.batch_isend_irecv(ops) if ops else []:
+            w.wait()
         return received
     works = []
     for r, vs in enumerate(views):
