@@ -36,8 +36,8 @@ UNIT = 'Gparams/s'
 # DRAM bytes per parameter and launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum)
 # on a smaller case of the same kernel and scaled by the parameter count; see profiles/.  None = not captured.
 NCU_TRAFFIC_BYTES_PER_PARAM = {
-    ('ef_topk_quant', 'bf16'): None, ('window_adam', 'bf16'): None,
-    ('ef_topk_quant', 'f32'): None, ('window_adam', 'f32'): None,
+    ('ef_topk_quant', 'bf16'): 3.04, ('window_adam', 'bf16'): 4.41,
+    ('ef_topk_quant', 'f32'): 5.02, ('window_adam', 'f32'): 9.52,
 }
 
 
@@ -49,6 +49,12 @@ def workload_spec(name: str):
     if name == 'gpt2_flat':
         return dict(shapes=[(124439808,)], dtype=torch.float32, weight_decay=0.0, grad_sigma=1e-3,
                     label='one fp32 flat parameter of 124,439,808 elements (BASELINE config 2)')
+    if name.startswith('flat_'):
+        # flat_<bf16|f32>_<numel>: one flat tensor, for ncu captures on a case a few times larger than L2
+        _, dt, numel = name.split('_')
+        dtype = torch.bfloat16 if dt == 'bf16' else torch.float32
+        return dict(shapes=[(int(numel),)], dtype=dtype, weight_decay=0.1 if dtype == torch.bfloat16 else 0.0,
+                    grad_sigma=1e-4 if dtype == torch.bfloat16 else 1e-3, label=f'one flat {dt} parameter of {int(numel)} elements')
     raise SystemExit(f'unknown workload {name}')
 
 
@@ -204,7 +210,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=10)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='llama3_8b', choices=['llama3_8b', 'gpt2_flat'])
+    ap.add_argument('--workload', default='llama3_8b', help='llama3_8b | gpt2_flat | flat_<bf16|f32>_<numel>')
     ap.add_argument('--grad-sets', type=int, default=2, help='distinct pre-generated gradient sets cycled over the steps')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -285,7 +291,7 @@ def main():
     if world > 1:
         mine = [(offsets[pc.index] + pc.lo, offsets[pc.index] + pc.hi) for pc in opt.plan if pc.rank == opt.rank]
         my_lo, my_hi = min(a for a, _ in mine), max(b for _, b in mine)
-    e2e_steps = max(1, min(args.e2e_steps, steps))
+    e2e_steps = max(0, min(args.e2e_steps, steps))
     gflat = grad_sets[0][0]
     try:
         host = torch.empty(my_hi - my_lo, dtype=spec['dtype'], pin_memory=True)
@@ -300,7 +306,7 @@ def main():
     barrier()
     t0 = time.perf_counter()
     checksum = 0.0
-    for t in range(e2e_steps):
+    for t in range(max(1, e2e_steps) if e2e_steps else 0):
         if not chunked:
             gflat[my_lo:my_hi].copy_(host, non_blocking=True)
         else:
@@ -313,7 +319,7 @@ def main():
     e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    e2e_value = n_params * e2e_steps / e2e_s.item() / 1e9
+    e2e_value = n_params * e2e_steps / e2e_s.item() / 1e9 if e2e_steps else None
 
     if rank != 0:
         if world > 1:

@@ -120,4 +120,10 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
     return d;
 }
 
+__device__ __forceinline__ uint32_t min_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 }  // namespace mab

@@ -348,6 +348,10 @@ int units_a_of(const mab_tensor& t) { return t.topk_full_blocks_count + (t.k_blo
 
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
                          int qbs, int max_dbs, cudaStream_t s) {
+    if (grad_dtype == MAB_BF16) {          // bf16 tiles are small enough for two shared-memory resident CTAs per SM
+        const int rc = launch_ef_topk_quant_bf16(dev_tensors, n_tensors, total_units, qbs, max_dbs, s);
+        if (rc <= 0) return rc;
+    }
     const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count());
     int qshift = 0;
     while ((1 << qshift) < qbs) ++qshift;
@@ -381,7 +385,9 @@ extern "C" int mab_device_error(void) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, mab::g_copy_timeout, sizeof(v));
     if (e != cudaSuccess) return mab::cuda_fail(e, "mab_device_error");
-    return v;
+    int v2 = 0;
+    if (int rc = mab::read_copy_timeout_bf16(&v2)) return rc;
+    return (v | v2) ? 1 : 0;
 }
 
 #ifdef MAB_STATS

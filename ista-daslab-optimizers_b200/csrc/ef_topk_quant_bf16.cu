@@ -1,0 +1,530 @@
+// Kernel A for bf16 gradients: the tile lives in shared memory, two CTAs per SM.
+//
+// A bf16 tile (29 056 values) is 58 KB, so two tiles fit one SM.  The tile is staged by the bulk
+// copy engine, turned into a = g + Qinv(e) in place, searched, zeroed at the selected positions and
+// re-quantised, all in shared memory; registers hold nothing across phases, so a CTA needs only 512
+// threads with 64 registers and two CTAs run per SM: one tile's barrier-bound selection overlaps the
+// other tile's arithmetic.  A thread owns whole quantisation blocks (64 consecutive values for
+// quant_block_size 64), so block statistics need no shuffles and the decode / encode constants are
+// computed once per block instead of once per 8 values.
+//
+// Results are bit-identical to the register-resident kernel in ef_topk_quant.cu (same arithmetic,
+// same tie rule); that kernel keeps serving fp32 gradients, whose 116 KB tiles allow one CTA per SM.
+#include "common.cuh"
+#include "select.cuh"
+#include "codec_fast.cuh"
+#include "async_copy.cuh"
+#include "fused.cuh"
+
+namespace mab {
+
+constexpr int S_NT = 512;
+constexpr int S_WPT = SEL_WORDS / S_NT;     // bitmap words per thread
+constexpr int S_CAND_CAP = 2048;
+constexpr int S_OCT_CAP = 1024;
+constexpr int S_MAX_TENSORS = 512;
+
+// Set when a wait on the copy engine gave up; read through mab_device_error() together with the other kernel's flag.
+__device__ int g_copy_timeout_bf16;
+
+struct __align__(16) SmemSel {
+    uint32_t gt_bm[SEL_WORDS], tie_bm[SEL_WORDS], sel_bm[SEL_WORDS];
+    int      sel_before[SEL_WORDS];
+    float    cand_val[S_CAND_CAP];
+    uint16_t cand_pos[S_CAND_CAP];       // position in the tile; bit 15 set once selected
+    uint16_t oct_list[S_OCT_CAP];        // octets that hold a candidate
+    int      hist[256];
+    int      member[32];
+    int      rot[64];
+    int      counters[40];
+    int      ctrl[8];
+    int      scan[36];
+    int      n_member, kmax;
+};
+
+struct BfStage {
+    uint16_t* tile; uint32_t* ef; uint16_t* mn; uint16_t* mx;
+    __host__ __device__ static int tile_bytes(int elems) { return (elems * 2 + 127) & ~127; }
+    __host__ __device__ static int ef_bytes(int elems) { return ((elems >> 1) + 127) & ~127; }
+    __host__ __device__ static int st_bytes(int elems, int qshift) { return ((((elems >> qshift) + 4) * 2) + 15) & ~15; }
+    __host__ __device__ static int bytes(int elems, int qshift) { return tile_bytes(elems) + ef_bytes(elems) + 2 * st_bytes(elems, qshift); }
+    __device__ BfStage(unsigned char* raw, int elems, int qshift) {
+        tile = reinterpret_cast<uint16_t*>(raw);
+        ef = reinterpret_cast<uint32_t*>(raw + tile_bytes(elems));
+        mn = reinterpret_cast<uint16_t*>(raw + tile_bytes(elems) + ef_bytes(elems));
+        mx = reinterpret_cast<uint16_t*>(raw + tile_bytes(elems) + ef_bytes(elems) + st_bytes(elems, qshift));
+    }
+};
+
+__device__ __forceinline__ void unpack8(const uint4& a, float (&v)[8]) {
+    v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
+    v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
+    v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
+    v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
+}
+
+__device__ __forceinline__ int key_of_bits(uint16_t b) { return (int)(b & 0x7FFFu) << 16; }   // |value| as float key bits
+
+// Number of tile elements with key >= thr (key bits), every thread of the CTA calling.
+__device__ __forceinline__ int tile_count_ge(const uint16_t* tile, int n_oct, int thr, int* counter) {
+    const float thr_f = __int_as_float(thr);
+    int c = 0;
+    for (int o = threadIdx.x; o < n_oct; o += S_NT) {
+        float v[8];
+        unpack8(reinterpret_cast<const uint4*>(tile)[o], v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) c += (fabsf(v[e]) >= thr_f) ? 1 : 0;
+    }
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (lane_id() == 0 && c) atomicAdd(counter, c);
+    __syncthreads();
+    return *reinterpret_cast<volatile int*>(counter);
+}
+
+// From gt_bm / tie_bm: sel_bm = gt | (the need_ties lowest tie positions), sel_before = prefix popcount.
+// Every thread owns S_WPT consecutive bitmap words.  Starts and ends with a barrier.
+__device__ __forceinline__ void resolve_selection_smem(int need_ties, SmemSel& ss) {
+    __syncthreads();
+    const int w0 = threadIdx.x * S_WPT;
+    uint32_t sel[S_WPT];
+    int total;
+#pragma unroll
+    for (int i = 0; i < S_WPT; ++i) sel[i] = ss.gt_bm[w0 + i];
+    if (need_ties > 0) {
+        uint32_t tw[S_WPT];
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < S_WPT; ++i) { tw[i] = ss.tie_bm[w0 + i]; cnt += __popc(tw[i]); }
+        int before = block_exclusive_scan(cnt, ss.scan, total);
+#pragma unroll
+        for (int i = 0; i < S_WPT; ++i) {
+            const int keep = need_ties - before;
+            before += __popc(tw[i]);
+            if (keep <= 0) tw[i] = 0;
+            else while (__popc(tw[i]) > keep) tw[i] &= ~(0x80000000u >> __clz(tw[i]));
+            sel[i] |= tw[i];
+        }
+        __syncthreads();
+    }
+    int cnt = 0;
+#pragma unroll
+    for (int i = 0; i < S_WPT; ++i) cnt += __popc(sel[i]);
+    int before = block_exclusive_scan(cnt, ss.scan, total);
+#pragma unroll
+    for (int i = 0; i < S_WPT; ++i) { ss.sel_bm[w0 + i] = sel[i]; ss.sel_before[w0 + i] = before; before += __popc(sel[i]); }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(S_NT, 2)
+ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];       // [staging: tile | codes | statistics][SmemSel]
+    __shared__ int s_first[S_MAX_TENSORS + 1];
+    __shared__ __align__(8) uint64_t s_bar;
+    const BfStage st(smem_raw, stage_elems, qshift);
+    SmemSel& ss = *reinterpret_cast<SmemSel*>(smem_raw + BfStage::bytes(stage_elems, qshift));
+    const int t = threadIdx.x, lane = lane_id(), warp = warp_id();
+    for (int i = t; i < n_tensors; i += S_NT) s_first[i] = tensors[i].first_unit_a;
+    if (t == 0) { s_first[n_tensors] = total_units; mbar_init(&s_bar, 1); }
+    __syncthreads();
+    const int cshift = qshift - 3;              // octets per quantisation block, as a shift
+    const int cpq = 1 << cshift;
+    uint32_t parity = 0;
+    int guess = 0;
+
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+        const int ti = find_tensor(s_first, n_tensors, unit);
+        const mab_tensor& T = tensors[ti];
+        const int blk = unit - s_first[ti];
+        const int dbs = T.d_block_size;
+        const int64_t base = (int64_t)blk * dbs;
+        const int n = (int)min((int64_t)dbs, T.d - base);
+        const int k = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
+        const uint16_t* g = reinterpret_cast<const uint16_t*>(T.grad) + base;
+        const uint8_t* ef_g = T.error + (base >> 1);
+        const int64_t qb0 = base >> qshift;
+        const int n_oct = (n + 7) >> 3, n_qb = (n + (1 << qshift) - 1) >> qshift;
+        const int skip = (int)(qb0 & 1);
+        const bool staged = (n & 31) == 0 && (n & ((1 << qshift) - 1)) == 0 && aligned16(g) && aligned16(ef_g) &&
+                            ((reinterpret_cast<uintptr_t>(T.min_vals) | reinterpret_cast<uintptr_t>(T.max_vals)) & 3) == 0;
+
+        // ---- bring the tile in -------------------------------------------------------------------
+        if (staged) {
+            if (t == 0) {
+                mbar_arrive_expect_tx(&s_bar, (uint32_t)n * 2u + ((uint32_t)n >> 1));
+                bulk_g2s(st.tile, g, (uint32_t)n * 2u, &s_bar);
+                bulk_g2s(st.ef, ef_g, (uint32_t)n >> 1, &s_bar);
+            }
+            const int words = ((n_qb + skip) + 1) >> 1;
+            const uint32_t* mn_src = reinterpret_cast<const uint32_t*>(T.min_vals + qb0 - skip);
+            const uint32_t* mx_src = reinterpret_cast<const uint32_t*>(T.max_vals + qb0 - skip);
+            for (int i = t; i < words; i += S_NT) {
+                cp_async_4(reinterpret_cast<uint32_t*>(st.mn) + i, mn_src + i);
+                cp_async_4(reinterpret_cast<uint32_t*>(st.mx) + i, mx_src + i);
+            }
+            cp_async_commit();
+            cp_async_wait_all();
+            const bool ok = mbar_wait(&s_bar, parity);
+            parity ^= 1u;
+            if (__syncthreads_or(!ok)) {
+                if (t == 0) atomicExch(&g_copy_timeout_bf16, 1);
+                return;
+            }
+        } else {
+            // ragged tile (a tensor's last block, or unaligned buffers): plain loads, zero padded to whole octets
+            for (int i = t; i < n_oct * 8; i += S_NT) st.tile[i] = (i < n) ? g[i] : (uint16_t)0;
+            for (int i = t; i < n_oct; i += S_NT) {
+                uint32_t w = 0;
+                for (int b = 0; b < 4; ++b) if ((i * 8 + 2 * b) < n) w |= (uint32_t)ef_g[i * 4 + b] << (8 * b);
+                st.ef[i] = w;
+            }
+            for (int i = t; i < n_qb; i += S_NT) { st.mn[i + skip] = T.min_vals[qb0 + i]; st.mx[i + skip] = T.max_vals[qb0 + i]; }
+            __syncthreads();
+        }
+        const uint16_t* s_mn = st.mn + skip;
+        const uint16_t* s_mx = st.mx + skip;
+        uint4* tile4 = reinterpret_cast<uint4*>(st.tile);
+
+        // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
+        // register slot i of a thread: block t + (i >> cshift) * S_NT, chunk (i + lane) mod cpq of that block
+        float omax[8];
+        {
+            QParams q = {0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                omax[i] = 0.0f;
+                const int b = t + (i >> cshift) * S_NT;
+                if (b < n_qb) {
+                    if ((i & (cpq - 1)) == 0) q = qparams(s_mn[b], s_mx[b]);
+                    const int o = (b << cshift) + ((i + lane) & (cpq - 1));
+                    if (o < n_oct) {
+                        float gv[8], x[8];
+                        unpack8(tile4[o], gv);
+                        decode_octet(st.ef[o], q, x);
+                        uint4 out;
+                        uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+                        float m = 0.0f;
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            const float2 s = __fadd2_rn(make_float2(gv[2 * p], gv[2 * p + 1]), make_float2(x[2 * p], x[2 * p + 1]));
+                            uint32_t w = pack_bf16x2_rne(s.x, s.y);
+                            const int e0 = o * 8 + 2 * p;                      // padding of a ragged tile stays zero
+                            if (e0 + 1 >= n) w = (e0 >= n) ? 0u : (w & 0xFFFFu);
+                            ow[p] = w;
+                            m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
+                        }
+                        tile4[o] = out;
+                        omax[i] = m;
+                    }
+                }
+            }
+        }
+
+        // ---- exact top-k ---------------------------------------------------------------------------
+        if (t == 0) ss.kmax = 0;
+        if (t < 64) ss.rot[t] = 0;
+        __syncthreads();
+        {
+            float tm = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tm = fmaxf(tm, omax[i]);
+            const int wm = __reduce_max_sync(0xffffffffu, __float_as_int(tm));
+            if (lane == 0 && wm) atomicMax(&ss.kmax, wm);
+        }
+        __syncthreads();
+        const int kmax = ss.kmax;
+        bool done = false;
+        int C = 0;
+        if (kmax == 0) {
+            // every key is zero: the k lowest positions win the ties
+            for (int w = t; w < SEL_WORDS; w += S_NT) {
+                const int lo = w * 32;
+                ss.gt_bm[w] = (lo + 32 <= k) ? 0xFFFFFFFFu : (lo < k ? ((1u << (k - lo)) - 1u) : 0u);
+                ss.tie_bm[w] = 0u;
+            }
+            resolve_selection_smem(0, ss);
+            done = true;
+            C = -1;                                          // values (all zero) are taken from the tile below
+        }
+        if (!done && kmax < 0x7f800000 && k <= n_oct) {
+            // lower bound of the k-th key on octet maxima: at least k octets reach it, at most ~1.5 k
+            const int accept = k + (k >> 1) + 8;
+            int lo = 0, hi = kmax + 1, step = 1 << 20;
+            int gq = (guess > 0 && guess <= kmax) ? guess : max(1, kmax - (2 << 23));
+            bool have_lo = false, have_hi = false;
+            for (int it = 0; it < 64; ++it) {
+                int mine = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mine += (__float_as_int(omax[i]) >= gq) ? 1 : 0;
+                mine = __reduce_add_sync(0xffffffffu, mine);
+                if (lane == 0 && mine) atomicAdd(&ss.rot[it], mine);
+                __syncthreads();
+                const int c = *reinterpret_cast<volatile int*>(&ss.rot[it]);
+                if (c >= k) { lo = gq; have_lo = true; if (c <= accept) break; }
+                else { hi = gq; have_hi = true; }
+                if (hi - lo <= 1) break;
+                if (have_lo && have_hi) gq = lo + ((hi - lo) >> 1);
+                else if (have_lo) { gq = (int)min((int64_t)lo + step, (int64_t)hi - 1); step <<= 1; }
+                else { gq = (int)max((int64_t)hi - step, (int64_t)1); step <<= 1; }
+            }
+            guess = lo;
+            const int T_lo = have_lo ? lo : 0;
+            if (T_lo > 0) {
+                const float T_lo_f = __int_as_float(T_lo);
+                // candidate octets -> list
+                int mine = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mine += (omax[i] >= T_lo_f) ? 1 : 0;
+                int n_list;
+                int at = block_exclusive_scan(mine, ss.scan, n_list);
+                if (n_list <= S_OCT_CAP) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (omax[i] >= T_lo_f)
+                            ss.oct_list[at++] = (uint16_t)(((t + (i >> cshift) * S_NT) << cshift) + ((i + lane) & (cpq - 1)));
+                    __syncthreads();
+                    // candidates of the listed octets (up to two octets per thread)
+                    mine = 0;
+                    for (int i = t; i < n_list; i += S_NT) {
+                        float v[8];
+                        unpack8(tile4[ss.oct_list[i]], v);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) mine += (fabsf(v[e]) >= T_lo_f) ? 1 : 0;
+                    }
+                    at = block_exclusive_scan(mine, ss.scan, C);
+                    if (C <= S_CAND_CAP) {
+                        for (int i = t; i < n_list; i += S_NT) {
+                            const uint32_t o = ss.oct_list[i];
+                            float v[8];
+                            unpack8(tile4[o], v);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (fabsf(v[e]) >= T_lo_f) { ss.cand_val[at] = v[e]; ss.cand_pos[at] = (uint16_t)((o << 3) | e); ++at; }
+                        }
+                        // radix histogram levels over [T_lo, kmax]; bf16 keys: a bin of <= 2^16 key bits is one value
+                        int r_lo = T_lo, r_hi = kmax, k_rem = k, R = C, sh = 31;
+                        for (int level = 0; level < 5; ++level) {
+                            const unsigned W1 = (unsigned)(r_hi - r_lo);
+                            sh = W1 < 256 ? 0 : (32 - __clz(W1)) - 8;
+                            if (t < 256) ss.hist[t] = 0;
+                            __syncthreads();
+                            for (int i = t; i < C; i += S_NT) {
+                                const int key = __float_as_int(fabsf(ss.cand_val[i]));
+                                if (key >= r_lo && key <= r_hi) atomicAdd(&ss.hist[(key - r_lo) >> sh], 1);
+                            }
+                            __syncthreads();
+                            if (warp == 0) {
+                                int h[8], s = 0;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) { h[i] = ss.hist[lane * 8 + i]; s += h[i]; }
+                                int suf = s;
+#pragma unroll
+                                for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_down_sync(0xffffffffu, suf, o); if (lane + o < 32) suf += v; }
+                                const unsigned okm = __ballot_sync(0xffffffffu, suf >= k_rem);
+                                const int owner = 31 - __clz(okm);
+                                if (lane == owner) {
+                                    int above = suf - s, b = 7;
+#pragma unroll
+                                    for (int i = 7; i >= 0; --i) if (b == i && above + h[i] < k_rem) { above += h[i]; b = i - 1; }
+                                    int hb = 0;
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) if (i == b) hb = h[i];
+                                    ss.ctrl[0] = lane * 8 + b; ss.ctrl[1] = k_rem - above; ss.ctrl[2] = hb;
+                                }
+                            }
+                            __syncthreads();
+                            const int b_star = ss.ctrl[0];
+                            k_rem = ss.ctrl[1];
+                            R = ss.ctrl[2];
+                            const int n_lo = r_lo + (b_star << sh);
+                            r_hi = (int)min((int64_t)r_hi, (int64_t)n_lo + ((int64_t)1 << sh) - 1);
+                            r_lo = n_lo;
+                            if (R <= 32 || sh <= 16) break;
+                        }
+                        if (R <= 32 || sh <= 16) {
+                            const bool by_rank = R <= 32;
+                            if (t == 0) ss.n_member = 0;
+                            for (int w = t; w < SEL_WORDS; w += S_NT) { ss.gt_bm[w] = 0u; ss.tie_bm[w] = 0u; }
+                            __syncthreads();
+                            for (int i = t; i < C; i += S_NT) {
+                                const int key = __float_as_int(fabsf(ss.cand_val[i]));
+                                const uint32_t pos = ss.cand_pos[i];
+                                if (key > r_hi) { ss.cand_pos[i] = (uint16_t)(pos | 0x8000u); atomicOr(&ss.gt_bm[pos >> 5], 1u << (pos & 31)); }
+                                else if (key >= r_lo) {
+                                    if (by_rank) ss.member[atomicAdd(&ss.n_member, 1)] = i;
+                                    else atomicOr(&ss.tie_bm[pos >> 5], 1u << (pos & 31));
+                                }
+                            }
+                            __syncthreads();
+                            int need_ties = 0;
+                            if (by_rank) {
+                                const int nm = ss.n_member;
+                                for (int mw = warp; mw < nm; mw += S_NT / 32) {   // member mw against all members, one ballot
+                                    const int mi = ss.member[mw];
+                                    const int my_key = __float_as_int(fabsf(ss.cand_val[mi]));
+                                    const int my_pos = (int)(ss.cand_pos[mi] & 0x7FFFu);
+                                    const int idx = lane < nm ? ss.member[lane] : -1;
+                                    const int key = idx >= 0 ? __float_as_int(fabsf(ss.cand_val[idx])) : -1;
+                                    const int pos = idx >= 0 ? (int)(ss.cand_pos[idx] & 0x7FFFu) : 0x7fffffff;
+                                    const unsigned beats = __ballot_sync(0xffffffffu, key > my_key || (key == my_key && pos < my_pos));
+                                    if (lane == 0 && __popc(beats) < k_rem) {
+                                        ss.cand_pos[mi] = (uint16_t)(my_pos | 0x8000);
+                                        atomicOr(&ss.gt_bm[my_pos >> 5], 1u << (my_pos & 31));
+                                    }
+                                }
+                            } else {
+                                need_ties = k_rem;
+                            }
+                            resolve_selection_smem(need_ties, ss);
+                            if (!by_rank) {
+                                for (int i = t; i < C; i += S_NT) {
+                                    const uint32_t pos = ss.cand_pos[i];
+                                    const int key = __float_as_int(fabsf(ss.cand_val[i]));
+                                    if (!(pos & 0x8000u) && key >= r_lo && key <= r_hi && ((ss.sel_bm[pos >> 5] >> (pos & 31)) & 1u))
+                                        ss.cand_pos[i] = (uint16_t)(pos | 0x8000u);
+                                }
+                                __syncthreads();
+                            }
+                            done = true;
+                        }
+                    }
+                }
+            }
+        }
+        const int64_t row_off = (int64_t)T.ring_index * T.k + (int64_t)blk * T.k_block_size_many;
+        int16_t* i_out = T.I + row_off;
+        uint16_t* v_out = T.V + row_off;
+        if (!done) {
+            // general path: bisection on the key bits over the tile in shared memory (data-independent cost)
+            C = -1;
+            done = true;
+            if (t < 40) ss.counters[t] = 0;
+            __syncthreads();
+            int Tk = 0;
+            for (int bit = 30; bit >= 16; --bit) {          // bf16 keys have 16 zero bits below
+                const int cand = Tk | (1 << bit);
+                if (tile_count_ge(st.tile, n_oct, cand, &ss.counters[bit]) >= k) Tk = cand;
+            }
+            const int n_gt = tile_count_ge(st.tile, n_oct, Tk + 0x10000, &ss.counters[32]);
+            const int need = k - n_gt;
+            const float Tf = __int_as_float(Tk);
+            uint8_t* gtb = reinterpret_cast<uint8_t*>(ss.gt_bm);
+            uint8_t* tieb = reinterpret_cast<uint8_t*>(ss.tie_bm);
+            for (int o = t; o < SEL_WORDS * 4; o += S_NT) {
+                uint32_t gm = 0, tm = 0;
+                if (o < n_oct) {
+                    float v[8];
+                    unpack8(tile4[o], v);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const bool valid = o * 8 + e < n;     // padding never competes, whatever the threshold
+                        gm |= (valid && fabsf(v[e]) > Tf) ? (1u << e) : 0u;
+                        tm |= (valid && fabsf(v[e]) == Tf) ? (1u << e) : 0u;
+                    }
+                }
+                gtb[o] = (uint8_t)gm; tieb[o] = (uint8_t)tm;
+            }
+            resolve_selection_smem(need, ss);
+        }
+
+        // ---- I[row], V[row]; selected positions become 0 in the tile ------------------------------------
+        {
+            const int w0 = t * S_WPT;
+#pragma unroll
+            for (int i = 0; i < S_WPT; ++i) {
+                uint32_t sel = ss.sel_bm[w0 + i];
+                int p = ss.sel_before[w0 + i];
+                while (sel) { const int b = __ffs(sel) - 1; sel &= sel - 1; i_out[p++] = (int16_t)((w0 + i) * 32 + b); }
+            }
+        }
+        if (C >= 0) {
+            for (int i = t; i < C; i += S_NT) {
+                const uint32_t pos = ss.cand_pos[i];
+                if (pos & 0x8000u) {
+                    const uint32_t q = pos & 0x7FFFu, w = q >> 5;
+                    v_out[ss.sel_before[w] + __popc(ss.sel_bm[w] & ((1u << (q & 31)) - 1u))] = (uint16_t)(__float_as_uint(ss.cand_val[i]) >> 16);
+                    st.tile[q] = 0;
+                }
+            }
+        } else {
+            const int w0 = t * S_WPT;
+#pragma unroll
+            for (int i = 0; i < S_WPT; ++i) {
+                uint32_t sel = ss.sel_bm[w0 + i];
+                int p = ss.sel_before[w0 + i];
+                while (sel) { const int b = __ffs(sel) - 1; sel &= sel - 1; const int q = (w0 + i) * 32 + b; v_out[p++] = st.tile[q]; st.tile[q] = 0; }
+            }
+        }
+        __syncthreads();
+
+        // ---- statistics and codes of the residual, one thread per quantisation block --------------------
+        uint16_t* mn_out = T.min_vals + qb0;
+        uint16_t* mx_out = T.max_vals + qb0;
+        for (int b = t; b < n_qb; b += S_NT) {
+            uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;  // running packed max (from -inf) and min (from +inf)
+            const int o_first = b << cshift;
+            for (int c = 0; c < cpq; ++c) {
+                const int o = o_first + ((c + lane) & (cpq - 1));
+                if (o < n_oct) {
+                    const uint4 v = tile4[o];
+                    const int cnt = n - o * 8;
+                    if (cnt >= 8) {
+                        hi2 = max_bf16x2(max_bf16x2(hi2, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
+                        lo2 = min_bf16x2(min_bf16x2(lo2, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
+                    } else {                                   // the tensor's last, short octet: valid elements only
+                        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                        for (int e = 0; e < cnt; ++e) {
+                            const uint32_t x = (w[e >> 1] >> (16 * (e & 1))) & 0xFFFFu;
+                            hi2 = max_bf16x2(hi2, x | (x << 16));
+                            lo2 = min_bf16x2(lo2, x | (x << 16));
+                        }
+                    }
+                }
+            }
+            hi2 = max_bf16x2(hi2, hi2 >> 16 | hi2 << 16);
+            lo2 = min_bf16x2(lo2, lo2 >> 16 | lo2 << 16);
+            const uint16_t mn_b = (uint16_t)(lo2 & 0xFFFFu), mx_b = (uint16_t)(hi2 & 0xFFFFu);
+            mn_out[b] = mn_b; mx_out[b] = mx_b;
+            const QParams q2 = qparams(mn_b, mx_b);
+            for (int c = 0; c < cpq; ++c) {
+                const int o = o_first + ((c + lane) & (cpq - 1));
+                if (o < n_oct) {
+                    float r[8];
+                    unpack8(tile4[o], r);
+                    const int cnt = n - o * 8;
+                    st.ef[o] = cnt >= 8 ? encode_octet(r, q2) : encode_octet_exact(r, q2, cnt);
+                }
+            }
+        }
+        __syncthreads();
+        // codes out: whole words coalesced, the ragged end byte by byte
+        uint8_t* ef_out = T.error + (base >> 1);
+        const int full_words = ((reinterpret_cast<uintptr_t>(ef_out) & 3) == 0) ? (n >> 3) : 0;
+        for (int i = t; i < full_words; i += S_NT) reinterpret_cast<uint32_t*>(ef_out)[i] = st.ef[i];
+        for (int i = full_words + t; i < n_oct; i += S_NT) {
+            const uint32_t w = st.ef[i];
+            for (int b = 0; b < 4; ++b) if (i * 8 + 2 * b < n) ef_out[i * 4 + b] = (uint8_t)(w >> (8 * b));
+        }
+        __syncthreads();                                     // the staging area is overwritten by the next tile
+    }
+}
+
+int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s) {
+    int qshift = 0;
+    while ((1 << qshift) < qbs) ++qshift;
+    const int smem = BfStage::bytes(max_dbs, qshift) + (int)sizeof(SmemSel);
+    if (2 * (smem + 3 * 1024) > device_max_optin_smem() + 1024) return 1;       // two CTAs per SM do not fit: caller uses the other kernel
+    const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count() * 2);
+    MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    ef_topk_quant_bf16_kernel<<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_bf16_kernel launch");
+    return MAB_OK;
+}
+
+int read_copy_timeout_bf16(int* out) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_copy_timeout_bf16, sizeof(int));
+    return e == cudaSuccess ? MAB_OK : cuda_fail(e, "mab_device_error");
+}
+
+}  // namespace mab

@@ -29,4 +29,8 @@ int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total
                          int qbs, int max_dbs, cudaStream_t s);
 int units_a_of(const mab_tensor& t);
 
+// ef_topk_quant_bf16.cu: returns 1 (without launching) when two CTAs of its shared memory do not fit an SM
+int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s);
+int read_copy_timeout_bf16(int* out);
+
 }  // namespace mab
