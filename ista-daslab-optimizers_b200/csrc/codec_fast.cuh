@@ -64,7 +64,10 @@ __device__ __forceinline__ uint32_t encode_octet_exact(const float (&r)[8], cons
 // unless s~ lies within 2^-16 of an integer; those (rare) elements, and every element when u is
 // outside [2^-100, 2^100] (zero, subnormal, infinite), are coded with the exact definition.
 // The clamp to [0.25, 15.5] keeps floor() in 0..15 and maps every out-of-range s to the code the
-// definition's clamp gives it.
+// definition's clamp gives it.  CLAMP = false is for callers whose statistics are the exact
+// minimum and maximum of the values (bf16 data: no rounding of the statistics), where
+// 0 <= r - mn <= mx - mn makes s~ fall in [0.5, 15.5 + 2^-18] by itself.
+template <bool CLAMP = true>
 __device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QParams& q) {
     if (!(q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX)) return encode_octet_exact(r, q, 8);
     const float r0 = __frcp_rn(q.u);
@@ -72,23 +75,25 @@ __device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QPar
     const float2 nmn2 = make_float2(-q.mn, -q.mn), r02 = make_float2(r0, r0), half2v = make_float2(0.5f, 0.5f);
     const float2 mg2 = make_float2(MAGIC, MAGIC), nmg2 = make_float2(-MAGIC, -MAGIC), neg1 = make_float2(-1.0f, -1.0f);
     const float2 nhalf2 = make_float2(-0.5f, -0.5f);
-    float f[8];
-    unsigned unsafe = 0;
+    float f[8], d[8];
+    float worst = 0.0f;                            // largest |frac(s~) - 0.5| of the octet
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
         float2 s = __ffma2_rn(__fadd2_rn(make_float2(r[2 * b], r[2 * b + 1]), nmn2), r02, half2v);   // r - mn == r + (-mn)
-        s.x = fminf(fmaxf(s.x, 0.25f), 15.5f);
-        s.y = fminf(fmaxf(s.y, 0.25f), 15.5f);
-        const float2 fl = __fadd2_rn(__fadd2_rd(s, mg2), nmg2);     // floor(s), exact
-        const float2 d = __fadd2_rn(__ffma2_rn(fl, neg1, s), nhalf2); // (s - floor(s)) - 0.5, exact
-        unsafe |= (fabsf(d.x) > 0.5f - 1.52587890625e-5f) ? (1u << (2 * b)) : 0u;
-        unsafe |= (fabsf(d.y) > 0.5f - 1.52587890625e-5f) ? (2u << (2 * b)) : 0u;
+        if (CLAMP) {
+            s.x = fminf(fmaxf(s.x, 0.25f), 15.5f);
+            s.y = fminf(fmaxf(s.y, 0.25f), 15.5f);
+        }
+        const float2 fl = __fadd2_rn(__fadd2_rd(s, mg2), nmg2);         // floor(s), exact
+        const float2 dd = __fadd2_rn(__ffma2_rn(fl, neg1, s), nhalf2);   // (s - floor(s)) - 0.5, exact
+        worst = fmaxf(worst, fmaxf(fabsf(dd.x), fabsf(dd.y)));
         f[2 * b] = fl.x; f[2 * b + 1] = fl.y;
+        d[2 * b] = dd.x; d[2 * b + 1] = dd.y;
     }
-    if (unsafe) {
+    if (worst > 0.5f - 1.52587890625e-5f) {
 #pragma unroll
         for (int e = 0; e < 8; ++e)
-            if (unsafe & (1u << e)) f[e] = static_cast<float>(qcode_exact(r[e], q));
+            if (fabsf(d[e]) > 0.5f - 1.52587890625e-5f) f[e] = static_cast<float>(qcode_exact(r[e], q));
     }
     // byte b = 16 * code(2b) + code(2b+1), built in float and read from the low mantissa byte
     const uint32_t b0 = __float_as_uint(__fmaf_rn(f[0], 16.0f, f[1]) + 8388608.0f);
@@ -112,6 +117,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rne(float a, float b) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
     return d;
 }
+
+// |x| of two packed bf16 values.
+__device__ __forceinline__ uint32_t abs_bf16x2(uint32_t a) { return a & 0x7FFF7FFFu; }
 
 // Lane-wise maximum of two packed bf16 pairs.
 __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {

@@ -325,7 +325,7 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 if ((o & (lanes_per_qb - 1)) == 0) { mn_out[o >> oshift] = mn_b; mx_out[o >> oshift] = mx_b; }
                 const QParams q2 = qparams(mn_b, mx_b);
                 if (cnt >= 8) {
-                    const uint32_t w = encode_octet(a[j], q2);
+                    const uint32_t w = encode_octet<true>(a[j], q2);
                     if (vec_e) *reinterpret_cast<uint32_t*>(ef_out + o * 4) = w;
                     else {
 #pragma unroll

@@ -24,6 +24,15 @@ constexpr int S_CAND_CAP = 2048;
 constexpr int S_OCT_CAP = 1024;
 constexpr int S_MAX_TENSORS = 512;
 
+#ifdef MAB_STATS
+__device__ unsigned long long g_stats_c[16];
+#define MAB_CTICK(i) do { if (threadIdx.x == 0) { const long long _now = clock64(); atomicAdd(&g_stats_c[i], (unsigned long long)(_now - c_tick)); c_tick = _now; } } while (0)
+#define MAB_CTICK_DECL long long c_tick = clock64();
+#else
+#define MAB_CTICK(i) do { } while (0)
+#define MAB_CTICK_DECL
+#endif
+
 // Set when a wait on the copy engine gave up; read through mab_device_error() together with the other kernel's flag.
 __device__ int g_copy_timeout_bf16;
 
@@ -147,6 +156,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         const bool staged = (n & 31) == 0 && (n & ((1 << qshift) - 1)) == 0 && aligned16(g) && aligned16(ef_g) &&
                             ((reinterpret_cast<uintptr_t>(T.min_vals) | reinterpret_cast<uintptr_t>(T.max_vals)) & 3) == 0;
 
+        MAB_CTICK_DECL
         // ---- bring the tile in -------------------------------------------------------------------
         if (staged) {
             if (t == 0) {
@@ -180,6 +190,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             for (int i = t; i < n_qb; i += S_NT) { st.mn[i + skip] = T.min_vals[qb0 + i]; st.mx[i + skip] = T.max_vals[qb0 + i]; }
             __syncthreads();
         }
+        MAB_CTICK(0);
         const uint16_t* s_mn = st.mn + skip;
         const uint16_t* s_mx = st.mx + skip;
         uint4* tile4 = reinterpret_cast<uint4*>(st.tile);
@@ -202,16 +213,19 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                         decode_octet(st.ef[o], q, x);
                         uint4 out;
                         uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
-                        float m = 0.0f;
+                        uint32_t m2 = 0u;                                     // packed running max of |a|
 #pragma unroll
                         for (int p = 0; p < 4; ++p) {
                             const float2 s = __fadd2_rn(make_float2(gv[2 * p], gv[2 * p + 1]), make_float2(x[2 * p], x[2 * p + 1]));
                             uint32_t w = pack_bf16x2_rne(s.x, s.y);
-                            const int e0 = o * 8 + 2 * p;                      // padding of a ragged tile stays zero
-                            if (e0 + 1 >= n) w = (e0 >= n) ? 0u : (w & 0xFFFFu);
+                            if (!staged) {                                    // padding of a ragged tile stays zero
+                                const int e0 = o * 8 + 2 * p;
+                                if (e0 + 1 >= n) w = (e0 >= n) ? 0u : (w & 0xFFFFu);
+                            }
                             ow[p] = w;
-                            m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
+                            m2 = max_bf16x2(m2, abs_bf16x2(w));
                         }
+                        const float m = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u));
                         tile4[o] = out;
                         omax[i] = m;
                     }
@@ -219,6 +233,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             }
         }
 
+        MAB_CTICK(1);
         // ---- exact top-k ---------------------------------------------------------------------------
         if (t == 0) ss.kmax = 0;
         if (t < 64) ss.rot[t] = 0;
@@ -390,6 +405,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 }
             }
         }
+        MAB_CTICK(2);
         const int64_t row_off = (int64_t)T.ring_index * T.k + (int64_t)blk * T.k_block_size_many;
         int16_t* i_out = T.I + row_off;
         uint16_t* v_out = T.V + row_off;
@@ -426,6 +442,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             resolve_selection_smem(need, ss);
         }
 
+        MAB_CTICK(3);
         // ---- I[row], V[row]; selected positions become 0 in the tile ------------------------------------
         {
             const int w0 = t * S_WPT;
@@ -456,6 +473,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         }
         __syncthreads();
 
+        MAB_CTICK(4);
         // ---- statistics and codes of the residual, one thread per quantisation block --------------------
         uint16_t* mn_out = T.min_vals + qb0;
         uint16_t* mx_out = T.max_vals + qb0;
@@ -491,11 +509,13 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                     float r[8];
                     unpack8(tile4[o], r);
                     const int cnt = n - o * 8;
-                    st.ef[o] = cnt >= 8 ? encode_octet(r, q2) : encode_octet_exact(r, q2, cnt);
+                    // bf16 values: the statistics are their exact minimum and maximum, no clamp needed
+                    st.ef[o] = cnt >= 8 ? encode_octet<false>(r, q2) : encode_octet_exact(r, q2, cnt);
                 }
             }
         }
         __syncthreads();
+        MAB_CTICK(5);
         // codes out: whole words coalesced, the ragged end byte by byte
         uint8_t* ef_out = T.error + (base >> 1);
         const int full_words = ((reinterpret_cast<uintptr_t>(ef_out) & 3) == 0) ? (n >> 3) : 0;
@@ -505,6 +525,10 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             for (int b = 0; b < 4; ++b) if (i * 8 + 2 * b < n) ef_out[i * 4 + b] = (uint8_t)(w >> (8 * b));
         }
         __syncthreads();                                     // the staging area is overwritten by the next tile
+        MAB_CTICK(6);
+#ifdef MAB_STATS
+        if (threadIdx.x == 0) atomicAdd(&g_stats_c[15], 1ull);
+#endif
     }
 }
 
@@ -521,6 +545,16 @@ int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int 
     if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_bf16_kernel launch");
     return MAB_OK;
 }
+
+#ifdef MAB_STATS
+}  // namespace mab
+extern "C" int mab_debug_stats_c(unsigned long long* out16, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out16, mab::g_stats_c, sizeof(mab::g_stats_c));
+    if (e == cudaSuccess && reset) { unsigned long long z[16] = {0}; e = cudaMemcpyToSymbol(mab::g_stats_c, z, sizeof(z)); }
+    return e == cudaSuccess ? 0 : -3;
+}
+namespace mab {
+#endif
 
 int read_copy_timeout_bf16(int* out) {
     cudaError_t e = cudaMemcpyFromSymbol(out, g_copy_timeout_bf16, sizeof(int));
