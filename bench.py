@@ -277,9 +277,11 @@ def main():
     launches = _native.kernel_launch_count() - launches0
     elapsed_ms = start.elapsed_time(end)
     events, opt.kernel_events = opt.kernel_events, None
-    t_a = sum(ev[0].elapsed_time(ev[1]) for ev in events) / len(events)
-    t_b = sum(ev[1].elapsed_time(ev[2]) for ev in events) / len(events)
-    t_gather = sum(ev[2].elapsed_time(ev[3]) for ev in events) / len(events) if len(events[0]) > 3 else 0.0
+    calls = [ev for ev in events if isinstance(ev, list)]            # one per fused call (several per step when overlapped)
+    t_a = sum(ev[0].elapsed_time(ev[1]) for ev in calls) / steps
+    t_b = sum(ev[1].elapsed_time(ev[2]) for ev in calls) / steps
+    # exchange time that is not hidden behind the kernels: step time minus kernel time
+    t_gather = max(0.0, elapsed_ms / steps - t_a - t_b) if world > 1 else 0.0
     stats = torch.tensor([elapsed_ms, t_a, t_b, t_gather], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
@@ -354,7 +356,7 @@ def main():
                      'frac_of_8tbs_nominal': dom['achieved_gbs'] / 8000.0},
         'kernels': kernels,
         'step_hbm': {'achieved_gbs': step_gbs, 'frac': step_gbs / peak, 'frac_of_8tbs_nominal': step_gbs / 8000.0,
-                     'algorithmic_bytes_per_param': ba + bb, 'kernel_ms': t_a + t_b, 'allgather_ms': t_gather},
+                     'algorithmic_bytes_per_param': ba + bb, 'kernel_ms': t_a + t_b, 'exposed_exchange_ms': t_gather},
         'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': 4, 'steps': e2e_steps,
                 'checksum': checksum},
         'gpu_launches': launches,

@@ -87,7 +87,7 @@ class MicroAdam(torch.optim.Optimizer):
 
         self._entries: List[_Entry] = []
         self._entries_key: Optional[tuple] = None
-        self._descs = None
+        self._descs = {}          # descriptor arrays of the fused step, one per group of entries
         self._workspace: Optional[torch.Tensor] = None
         # set to a list to have every fused step append [start, between the two kernels, end] CUDA events
         self.kernel_events: Optional[list] = None
@@ -197,7 +197,7 @@ class MicroAdam(torch.optim.Optimizer):
             entries.append(_Entry(p, st, lo, hi, gi))
         self._entries = entries
         self._entries_key = key
-        self._descs = None
+        self._descs = {}
         if self.use_fused and entries:
             args = self._step_args()
             for e in entries:
@@ -235,14 +235,16 @@ class MicroAdam(torch.optim.Optimizer):
         d.lr = float(group['lr'])                                                                      # micro_adam.py:121
         d.weight_decay = float(group.get('weight_decay', self.weight_decay))                           # micro_adam.py:122
 
-    def _fused_step(self, entries: List[_Entry]):
+    def _fused_step(self, entries: List[_Entry], group_key=0):
+        """One fused step over `entries`; `group_key` names the group so that its descriptor array is reused."""
         lib = N.load()
         n = len(entries)
-        if self._descs is None or len(self._descs) != n:
-            self._descs = (N.MabTensor * n)()
-            for d, e in zip(self._descs, entries):
+        descs = self._descs.get(group_key)
+        if descs is None or len(descs) != n:
+            descs = self._descs[group_key] = (N.MabTensor * n)()
+            for d, e in zip(descs, entries):
                 self._fill_static(d, e)
-        for d, e in zip(self._descs, entries):
+        for d, e in zip(descs, entries):
             self._fill_dynamic(d, e)
             e.st['index'] = (e.st['index'] + 1) % self.m                                               # micro_adam.py:211
         device = entries[0].p.device
@@ -254,15 +256,15 @@ class MicroAdam(torch.optim.Optimizer):
         with torch.cuda.device(device):
             stream = N.current_stream(device)
             if self.kernel_events is None:
-                N.check(lib.mab_fused_step(self._descs, n, ctypes.byref(args), ws, ws_bytes, stream), 'mab_fused_step')
+                N.check(lib.mab_fused_step(descs, n, ctypes.byref(args), ws, ws_bytes, stream), 'mab_fused_step')
             else:
                 # the same two kernels through their own entry points, with CUDA events between them
                 ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
                 ev[0].record()
-                N.check(lib.mab_fused_ef_topk_quant(self._descs, n, ctypes.byref(args), ws, ws_bytes, stream),
+                N.check(lib.mab_fused_ef_topk_quant(descs, n, ctypes.byref(args), ws, ws_bytes, stream),
                         'mab_fused_ef_topk_quant')
                 ev[1].record()
-                N.check(lib.mab_fused_window_adam_update(self._descs, n, ctypes.byref(args), ws, ws_bytes, stream),
+                N.check(lib.mab_fused_window_adam_update(descs, n, ctypes.byref(args), ws, ws_bytes, stream),
                         'mab_fused_window_adam_update')
                 ev[2].record()
                 self.kernel_events.append(ev)

@@ -100,7 +100,7 @@ class ShardedMicroAdam(MicroAdam):
 
     def __init__(self, params, m, lr, quant_block_size, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0,
                  eps=1e-8, *, process_group=None, rank: Optional[int] = None, world_size: Optional[int] = None,
-                 gather: bool = True, **kw):
+                 gather: bool = True, overlap_chunks: int = 6, **kw):
         super().__init__(params, m, lr, quant_block_size, k_init, alpha, betas, weight_decay, eps, **kw)
         self.process_group = process_group
         if rank is None or world_size is None:
@@ -119,6 +119,10 @@ class ShardedMicroAdam(MicroAdam):
                 self._my_slice[id(self._all_params[pc.index])] = (pc.lo, pc.hi)
         self._gather_views = None
         self.last_gather_bytes = 0
+        # the step runs in this many groups of pieces; a group's parameters travel while the next group is computed
+        self.overlap_chunks = max(1, int(overlap_chunks))
+        self._chunks = None
+        self._comm_stream = None
 
     def _slice_of(self, p):
         return self._my_slice.get(id(p))
@@ -129,6 +133,65 @@ class ShardedMicroAdam(MicroAdam):
         if self._gather_views is None:
             self._gather_views = build_gather_views(self.plan, self._all_params, self.world_size)
         self.last_gather_bytes = exchange_pieces(self._gather_views, self.rank, self.process_group)
+
+    # ---------------------------------------------------------------------------- overlapped step
+    def _chunk_plan(self):
+        """Every rank's pieces cut into `overlap_chunks` consecutive groups of about equal size (the same
+        cut on every rank, computed from the plan alone), with the exchange views of each group."""
+        if self._chunks is None:
+            per_rank = [[pc for pc in self.plan if pc.rank == r] for r in range(self.world_size)]
+            groups = [[[] for _ in range(self.world_size)] for _ in range(self.overlap_chunks)]
+            for r, pieces in enumerate(per_rank):
+                total = sum(pc.hi - pc.lo for pc in pieces) or 1
+                done = 0
+                for pc in pieces:
+                    mid = done + (pc.hi - pc.lo) / 2
+                    groups[min(self.overlap_chunks - 1, int(mid * self.overlap_chunks / total))][r].append(pc)
+                    done += pc.hi - pc.lo
+            self._chunks = []
+            for g in groups:
+                flat = [pc for r in range(self.world_size) for pc in g[r]]
+                views = build_gather_views(flat, self._all_params, self.world_size)
+                mine = {id(self._all_params[pc.index]) for pc in g[self.rank]}
+                self._chunks.append((mine, views))
+        return self._chunks
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        if not self.gather or self.overlap_chunks <= 1 or dist.get_backend(self.process_group) != 'nccl':
+            return super().step(closure)
+        self.steps += 1
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self._refresh_entries()
+        device = self._all_params[0].device
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=device)
+        compute = torch.cuda.current_stream(device)
+        self._comm_stream.wait_stream(compute)
+        received = 0
+        for ci, (mine, views) in enumerate(self._chunk_plan()):
+            entries = [e for e in self._entries if id(e.p) in mine]
+            fused = [e for e in entries if e.fused]
+            if fused:
+                self._fused_step(fused, group_key=ci)
+            for e in entries:
+                if not e.fused:
+                    self._generic_update(e)
+            ready = torch.cuda.Event()
+            ready.record(compute)
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ready)
+                received += exchange_pieces(views, self.rank, self.process_group)
+        compute.wait_stream(self._comm_stream)
+        self.last_gather_bytes = received
+        if self.kernel_events:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.kernel_events.append(('step_end', ev))
+        return loss
 
 
 def build_gather_views(plan: Sequence[Piece], params: Sequence[torch.Tensor], world_size: int) -> List[List[torch.Tensor]]:

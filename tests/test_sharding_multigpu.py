@@ -1,0 +1,51 @@
+"""Two real GPUs over NCCL: the sharded, overlapped step leaves every rank with the parameters of
+the unsharded step, bit for bit.  Skipped with fewer than two GPUs."""
+import os
+import random
+
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, name, steps, flat):
+    import torch.distributed as dist
+    from ista_daslab_optimizers_b200 import MicroAdam
+    from ista_daslab_optimizers_b200.sharding import ShardedMicroAdam, flatten_parameters
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), NCCL_NVLS_ENABLE='0')
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        case = cases.CASES[name]
+        kw = dict(m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init, alpha=case.alpha, betas=case.betas,
+                  weight_decay=case.weight_decay, eps=case.eps, d_block_size=case.d_block_size)
+        ref_params = [torch.nn.Parameter(p.cuda()) for p in case.params()]
+        ref = MicroAdam(ref_params, **kw)
+        params = [torch.nn.Parameter(p.cuda()) for p in case.params()]
+        if flat:
+            flatten_parameters(params)
+        opt = ShardedMicroAdam(params, overlap_chunks=3, **kw)
+        for t in range(steps):
+            grads = case.grads(t)
+            for p, q, g in zip(ref_params, params, grads):
+                p.grad = g.cuda()
+                q.grad = g.cuda()
+            ref.step()
+            opt.step()
+            torch.cuda.synchronize()
+            for i, (p, q) in enumerate(zip(ref_params, params)):
+                assert torch.equal(p.detach().view(torch.int16 if p.dtype == torch.bfloat16 else torch.int32),
+                                   q.detach().view(torch.int16 if q.dtype == torch.bfloat16 else torch.int32)), (rank, t, i)
+        assert opt.last_gather_bytes > 0
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
+@pytest.mark.parametrize('name,flat', [('bf16_wd', True), ('mixed_fp32_alpha', False)])
+def test_two_gpus_match_one(name, flat):
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, 29600 + random.randrange(2000), name, 3, flat), nprocs=2, join=True)
