@@ -36,6 +36,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
+// Bulk copy shared -> global (`bytes` a multiple of 16, both addresses 16-byte aligned) as one
+// bulk group of the calling thread.  Shared memory written by ordinary stores must be made visible
+// to the copy engine first (fence_async_smem by the writers, then a barrier).
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(smem_addr(src_smem)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The calling thread's bulk stores have finished reading shared memory / have completed.
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's ordinary shared-memory accesses before later copy-engine accesses.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Asks L2 for the 128-byte lines of [base, base + bytes), the block's NT threads sharing the lines.
+template <int NT>
+__device__ __forceinline__ void prefetch_l2(uintptr_t base, int64_t bytes) {
+    const uintptr_t first = base & ~(uintptr_t)127;
+    const int lines = (int)((base + bytes - first + 127) >> 7);
+    for (int i = threadIdx.x; i < lines; i += NT)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(first + ((uintptr_t)i << 7)));
+}
+
 __device__ __forceinline__ void cp_async_4(void* dst_smem, const void* src_gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(dst_smem)), "l"(src_gmem) : "memory");
 }

@@ -25,18 +25,28 @@ __device__ __forceinline__ float magic_byte(uint32_t v) {
 
 // x[e] = Qinv(code_e) = RN(RN(code * u) + mn).  With F = 2^23 + code (exact), fma(F, u, -2^23 u)
 // rounds the exact value code * u once, which is RN(code * u); valid while 2^23 * |u| does not
-// overflow and u >= +0 (a negative u would turn the +0 of code 0 into -0); the caller checks both.
+// overflow and u >= +0 (a negative u would turn the +0 of code 0 into -0): `fast` says so.
 // Two elements per instruction: the packed f32x2 forms round each component like the scalar ones.
-__device__ __forceinline__ void decode_octet_fast(uint32_t w, const QParams& q, float (&x)[8]) {
+// The constants depend on the quantisation block only; callers that decode several octets of a
+// block build them once.
+struct DecodeConsts { float2 u2, nb2, mn2; bool fast; };
+
+__device__ __forceinline__ DecodeConsts decode_consts(const QParams& q) {
+    DecodeConsts c;
+    const float nb = -(8388608.0f * q.u);
+    c.u2 = make_float2(q.u, q.u); c.nb2 = make_float2(nb, nb); c.mn2 = make_float2(q.mn, q.mn);
+    c.fast = q.u >= 0.0f && q.u < CODEC_U_MAX;          // also false for NaN
+    return c;
+}
+
+__device__ __forceinline__ void decode_octet_fast(uint32_t w, const DecodeConsts& c, float (&x)[8]) {
     uint32_t hi, lo;
     split_nibbles(w, hi, lo);
-    const float nb = -(8388608.0f * q.u);
-    const float2 u2 = make_float2(q.u, q.u), nb2 = make_float2(nb, nb), mn2 = make_float2(q.mn, q.mn);
     float2 p;
-    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<0>(hi), magic_byte<0>(lo)), u2, nb2), mn2); x[0] = p.x; x[1] = p.y;
-    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<1>(hi), magic_byte<1>(lo)), u2, nb2), mn2); x[2] = p.x; x[3] = p.y;
-    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<2>(hi), magic_byte<2>(lo)), u2, nb2), mn2); x[4] = p.x; x[5] = p.y;
-    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<3>(hi), magic_byte<3>(lo)), u2, nb2), mn2); x[6] = p.x; x[7] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<0>(hi), magic_byte<0>(lo)), c.u2, c.nb2), c.mn2); x[0] = p.x; x[1] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<1>(hi), magic_byte<1>(lo)), c.u2, c.nb2), c.mn2); x[2] = p.x; x[3] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<2>(hi), magic_byte<2>(lo)), c.u2, c.nb2), c.mn2); x[4] = p.x; x[5] = p.y;
+    p = __fadd2_rn(__ffma2_rn(make_float2(magic_byte<3>(hi), magic_byte<3>(lo)), c.u2, c.nb2), c.mn2); x[6] = p.x; x[7] = p.y;
 }
 
 __device__ __forceinline__ void decode_octet_exact(uint32_t w, const QParams& q, float (&x)[8]) {
@@ -45,7 +55,8 @@ __device__ __forceinline__ void decode_octet_exact(uint32_t w, const QParams& q,
 }
 
 __device__ __forceinline__ void decode_octet(uint32_t w, const QParams& q, float (&x)[8]) {
-    if (q.u >= 0.0f && q.u < CODEC_U_MAX) decode_octet_fast(w, q, x);   // also false for NaN
+    const DecodeConsts c = decode_consts(q);
+    if (c.fast) decode_octet_fast(w, c, x);
     else decode_octet_exact(w, q, x);
 }
 
@@ -67,19 +78,36 @@ __device__ __forceinline__ uint32_t encode_octet_exact(const float (&r)[8], cons
 // definition's clamp gives it.  CLAMP = false is for callers whose statistics are the exact
 // minimum and maximum of the values (bf16 data: no rounding of the statistics), where
 // 0 <= r - mn <= mx - mn makes s~ fall in [0.5, 15.5 + 2^-18] by itself.
-template <bool CLAMP = true>
-__device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QParams& q) {
-    if (!(q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX)) return encode_octet_exact(r, q, 8);
+// min and max of 8 values with the 3-input min / max of sm_100.
+__device__ __forceinline__ float min3(float a, float b, float c) { float d; asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+__device__ __forceinline__ void octet_min_max(const float (&v)[8], float& lo, float& hi) {
+    lo = fminf(min3(v[0], v[1], v[2]), min3(min3(v[3], v[4], v[5]), v[6], v[7]));
+    hi = fmaxf(max3(v[0], v[1], v[2]), max3(max3(v[3], v[4], v[5]), v[6], v[7]));
+}
+
+struct EncodeConsts { float2 nmn2, r02; bool fast; };
+
+__device__ __forceinline__ EncodeConsts encode_consts(const QParams& q) {
+    EncodeConsts c;
+    c.fast = q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX;
     const float r0 = __frcp_rn(q.u);
+    c.nmn2 = make_float2(-q.mn, -q.mn); c.r02 = make_float2(r0, r0);
+    return c;
+}
+
+// Requires c.fast.
+template <bool CLAMP>
+__device__ __forceinline__ uint32_t encode_octet_fast(const float (&r)[8], const QParams& q, const EncodeConsts& c) {
     const float MAGIC = 12582912.0f;              // 1.5 * 2^23: low mantissa bits of x + MAGIC hold round-down(x)
-    const float2 nmn2 = make_float2(-q.mn, -q.mn), r02 = make_float2(r0, r0), half2v = make_float2(0.5f, 0.5f);
+    const float2 half2v = make_float2(0.5f, 0.5f);
     const float2 mg2 = make_float2(MAGIC, MAGIC), nmg2 = make_float2(-MAGIC, -MAGIC), neg1 = make_float2(-1.0f, -1.0f);
     const float2 nhalf2 = make_float2(-0.5f, -0.5f);
     float f[8], d[8];
     float worst = 0.0f;                            // largest |frac(s~) - 0.5| of the octet
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-        float2 s = __ffma2_rn(__fadd2_rn(make_float2(r[2 * b], r[2 * b + 1]), nmn2), r02, half2v);   // r - mn == r + (-mn)
+        float2 s = __ffma2_rn(__fadd2_rn(make_float2(r[2 * b], r[2 * b + 1]), c.nmn2), c.r02, half2v);   // r - mn == r + (-mn)
         if (CLAMP) {
             s.x = fminf(fmaxf(s.x, 0.25f), 15.5f);
             s.y = fminf(fmaxf(s.y, 0.25f), 15.5f);
@@ -103,12 +131,42 @@ __device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QPar
     return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
 }
 
-// min and max of 8 values with the 3-input min / max of sm_100.
-__device__ __forceinline__ float min3(float a, float b, float c) { float d; asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
-__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
-__device__ __forceinline__ void octet_min_max(const float (&v)[8], float& lo, float& hi) {
-    lo = fminf(min3(v[0], v[1], v[2]), min3(min3(v[3], v[4], v[5]), v[6], v[7]));
-    hi = fmaxf(max3(v[0], v[1], v[2]), max3(max3(v[3], v[4], v[5]), v[6], v[7]));
+// The same codes without the per-octet branch: `worst` returns the largest |frac(s~) - 0.5| of the
+// octet, and the caller re-codes the octet with encode_octet_fast when it exceeds CODEC_SAFE_FRAC.
+// Several octets coded this way in a row overlap in the pipeline.  Requires c.fast.
+constexpr float CODEC_SAFE_FRAC = 0.5f - 1.52587890625e-5f;
+template <bool CLAMP>
+__device__ __forceinline__ uint32_t encode_octet_speculative(const float (&r)[8], const EncodeConsts& c, float& worst) {
+    const float MAGIC = 12582912.0f;
+    const float2 half2v = make_float2(0.5f, 0.5f);
+    const float2 mg2 = make_float2(MAGIC, MAGIC), nmg2 = make_float2(-MAGIC, -MAGIC), neg1 = make_float2(-1.0f, -1.0f);
+    const float2 nhalf2 = make_float2(-0.5f, -0.5f);
+    float f[8];
+    worst = 0.0f;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float2 s = __ffma2_rn(__fadd2_rn(make_float2(r[2 * b], r[2 * b + 1]), c.nmn2), c.r02, half2v);
+        if (CLAMP) {
+            s.x = fminf(fmaxf(s.x, 0.25f), 15.5f);
+            s.y = fminf(fmaxf(s.y, 0.25f), 15.5f);
+        }
+        const float2 fl = __fadd2_rn(__fadd2_rd(s, mg2), nmg2);
+        const float2 dd = __fadd2_rn(__ffma2_rn(fl, neg1, s), nhalf2);
+        worst = fmaxf(worst, fmaxf(fabsf(dd.x), fabsf(dd.y)));
+        f[2 * b] = fl.x; f[2 * b + 1] = fl.y;
+    }
+    const uint32_t b0 = __float_as_uint(__fmaf_rn(f[0], 16.0f, f[1]) + 8388608.0f);
+    const uint32_t b1 = __float_as_uint(__fmaf_rn(f[2], 16.0f, f[3]) + 8388608.0f);
+    const uint32_t b2 = __float_as_uint(__fmaf_rn(f[4], 16.0f, f[5]) + 8388608.0f);
+    const uint32_t b3 = __float_as_uint(__fmaf_rn(f[6], 16.0f, f[7]) + 8388608.0f);
+    return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
+
+template <bool CLAMP = true>
+__device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QParams& q) {
+    const EncodeConsts c = encode_consts(q);
+    if (!c.fast) return encode_octet_exact(r, q, 8);
+    return encode_octet_fast<CLAMP>(r, q, c);
 }
 
 // Two floats -> two bf16 (round to nearest even) in one conversion; low half = first value.
@@ -125,6 +183,13 @@ __device__ __forceinline__ uint32_t abs_bf16x2(uint32_t a) { return a & 0x7FFF7F
 __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// Lane-wise max(|a|, |b|); the sign bit of each lane is the xor of the operands' signs (mask it off).
+__device__ __forceinline__ uint32_t maxabs_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
 

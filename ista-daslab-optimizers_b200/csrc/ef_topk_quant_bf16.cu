@@ -124,6 +124,28 @@ __device__ __forceinline__ void resolve_selection_smem(int need_ties, SmemSel& s
     __syncthreads();
 }
 
+// One octet of a = bf16(g + Qinv(e)) in place; returns the largest |a| of the octet.
+template <bool FAST>
+__device__ __forceinline__ float dequant_octet(uint4* tile4, const uint32_t* ef, int o, const QParams& q, const DecodeConsts& dc) {
+    float gv[8], x[8];
+    unpack8(tile4[o], gv);
+    if (FAST) decode_octet_fast(ef[o], dc, x);
+    else decode_octet_exact(ef[o], q, x);
+    uint4 out;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const float2 s = __fadd2_rn(make_float2(gv[2 * p], gv[2 * p + 1]), make_float2(x[2 * p], x[2 * p + 1]));
+        ow[p] = pack_bf16x2_rne(s.x, s.y);
+    }
+    tile4[o] = out;
+    const uint32_t m2 = maxabs_bf16x2(maxabs_bf16x2(ow[0], ow[1]), maxabs_bf16x2(ow[2], ow[3]));
+    return fmaxf(fabsf(__uint_as_float(m2 << 16)), fabsf(__uint_as_float(m2 & 0xFFFF0000u)));
+}
+
+// QB64: quant_block_size is 64, so a thread's quantisation block is 8 octets and the loops over
+// them unroll; tiles that are not whole (a tensor's last block) or not aligned take the general code.
+template <bool QB64>
 __global__ void __launch_bounds__(S_NT, 2)
 ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
     extern __shared__ __align__(128) unsigned char smem_raw[];       // [staging: tile | codes | statistics][SmemSel]
@@ -158,8 +180,15 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
 
         MAB_CTICK_DECL
         // ---- bring the tile in -------------------------------------------------------------------
+        // (selection scratch is cleared here: the barrier that ends the load publishes it)
+        if (t == 0) { ss.kmax = 0; ss.n_member = 0; }
+        if (t < 64) ss.rot[t] = 0;
+        if (t < 256) ss.hist[t] = 0;
+        for (int w = t; w < SEL_WORDS; w += S_NT) { ss.gt_bm[w] = 0u; ss.tie_bm[w] = 0u; }
         if (staged) {
             if (t == 0) {
+                bulk_wait_read();                                     // the previous tile's codes have left shared memory
+                fence_async_smem();
                 mbar_arrive_expect_tx(&s_bar, (uint32_t)n * 2u + ((uint32_t)n >> 1));
                 bulk_g2s(st.tile, g, (uint32_t)n * 2u, &s_bar);
                 bulk_g2s(st.ef, ef_g, (uint32_t)n >> 1, &s_bar);
@@ -176,11 +205,13 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             const bool ok = mbar_wait(&s_bar, parity);
             parity ^= 1u;
             if (__syncthreads_or(!ok)) {
-                if (t == 0) atomicExch(&g_copy_timeout_bf16, 1);
+                if (t == 0) { atomicExch(&g_copy_timeout_bf16, 1); bulk_wait_all(); }
                 return;
             }
         } else {
             // ragged tile (a tensor's last block, or unaligned buffers): plain loads, zero padded to whole octets
+            if (t == 0) bulk_wait_read();                             // the previous tile's codes have left shared memory
+            __syncthreads();
             for (int i = t; i < n_oct * 8; i += S_NT) st.tile[i] = (i < n) ? g[i] : (uint16_t)0;
             for (int i = t; i < n_oct; i += S_NT) {
                 uint32_t w = 0;
@@ -191,6 +222,15 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             __syncthreads();
         }
         MAB_CTICK(0);
+        if (unit + (int)gridDim.x < total_units) {           // the tile after this one: into L2 while this one is worked on
+            const int nu = unit + gridDim.x;
+            const int nti = find_tensor(s_first, n_tensors, nu);
+            const mab_tensor& N = tensors[nti];
+            const int64_t nbase = (int64_t)(nu - s_first[nti]) * N.d_block_size;
+            const int64_t nn = min((int64_t)N.d_block_size, N.d - nbase);
+            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(N.grad) + nbase), nn * 2);
+            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.error + (nbase >> 1)), (nn + 1) >> 1);
+        }
         const uint16_t* s_mn = st.mn + skip;
         const uint16_t* s_mx = st.mx + skip;
         uint4* tile4 = reinterpret_cast<uint4*>(st.tile);
@@ -198,7 +238,25 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
         // register slot i of a thread: block t + (i >> cshift) * S_NT, chunk (i + lane) mod cpq of that block
         float omax[8];
-        {
+        if (QB64 && staged) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) omax[i] = 0.0f;
+            if (t < n_qb) {
+                const QParams q = qparams(s_mn[t], s_mx[t]);
+                const DecodeConsts dc = decode_consts(q);
+                if (dc.fast) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) omax[i] = dequant_octet<true>(tile4, st.ef, (t << 3) + ((i + lane) & 7), q, dc);
+                } else {
+#pragma unroll 1
+                    for (int i = 0; i < 8; ++i) {
+                        const float m = dequant_octet<false>(tile4, st.ef, (t << 3) + ((i + lane) & 7), q, dc);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) if (j == i) omax[j] = m;
+                    }
+                }
+            }
+        } else {
             QParams q = {0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -235,9 +293,6 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
 
         MAB_CTICK(1);
         // ---- exact top-k ---------------------------------------------------------------------------
-        if (t == 0) ss.kmax = 0;
-        if (t < 64) ss.rot[t] = 0;
-        __syncthreads();
         {
             float tm = 0.0f;
 #pragma unroll
@@ -320,8 +375,8 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                         for (int level = 0; level < 5; ++level) {
                             const unsigned W1 = (unsigned)(r_hi - r_lo);
                             sh = W1 < 256 ? 0 : (32 - __clz(W1)) - 8;
-                            if (t < 256) ss.hist[t] = 0;
-                            __syncthreads();
+                            if (level > 0 && t < 256) ss.hist[t] = 0;      // level 0 finds it cleared at the tile's start
+                            __syncthreads();                                // also publishes the candidate list
                             for (int i = t; i < C; i += S_NT) {
                                 const int key = __float_as_int(fabsf(ss.cand_val[i]));
                                 if (key >= r_lo && key <= r_hi) atomicAdd(&ss.hist[(key - r_lo) >> sh], 1);
@@ -357,9 +412,6 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                         }
                         if (R <= 32 || sh <= 16) {
                             const bool by_rank = R <= 32;
-                            if (t == 0) ss.n_member = 0;
-                            for (int w = t; w < SEL_WORDS; w += S_NT) { ss.gt_bm[w] = 0u; ss.tie_bm[w] = 0u; }
-                            __syncthreads();
                             for (int i = t; i < C; i += S_NT) {
                                 const int key = __float_as_int(fabsf(ss.cand_val[i]));
                                 const uint32_t pos = ss.cand_pos[i];
@@ -477,6 +529,50 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // ---- statistics and codes of the residual, one thread per quantisation block --------------------
         uint16_t* mn_out = T.min_vals + qb0;
         uint16_t* mx_out = T.max_vals + qb0;
+        if (QB64 && staged) {
+            if (t < n_qb) {
+                uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = tile4[(t << 3) + ((c + lane) & 7)];
+                    hi2 = max_bf16x2(max_bf16x2(hi2, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
+                    lo2 = min_bf16x2(min_bf16x2(lo2, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
+                }
+                hi2 = max_bf16x2(hi2, hi2 >> 16);
+                lo2 = min_bf16x2(lo2, lo2 >> 16);
+                const uint16_t mn_b = (uint16_t)(lo2 & 0xFFFFu), mx_b = (uint16_t)(hi2 & 0xFFFFu);
+                mn_out[t] = mn_b; mx_out[t] = mx_b;
+                const QParams q2 = qparams(mn_b, mx_b);
+                const EncodeConsts ec = encode_consts(q2);
+                if (ec.fast) {
+                    uint32_t redo = 0u;                                   // octets with a value too close to a code boundary
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const int o = (t << 3) + ((c + lane) & 7);
+                        float r[8], worst;
+                        unpack8(tile4[o], r);
+                        st.ef[o] = encode_octet_speculative<false>(r, ec, worst);   // exact statistics of bf16 values: no clamp needed
+                        redo |= (worst > CODEC_SAFE_FRAC) ? (1u << c) : 0u;
+                    }
+                    while (redo) {
+                        const int c = __ffs(redo) - 1;
+                        redo &= redo - 1;
+                        const int o = (t << 3) + ((c + lane) & 7);
+                        float r[8];
+                        unpack8(tile4[o], r);
+                        st.ef[o] = encode_octet_fast<false>(r, q2, ec);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < 8; ++c) {
+                        const int o = (t << 3) + ((c + lane) & 7);
+                        float r[8];
+                        unpack8(tile4[o], r);
+                        st.ef[o] = encode_octet_exact(r, q2, 8);
+                    }
+                }
+            }
+        } else
         for (int b = t; b < n_qb; b += S_NT) {
             uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;  // running packed max (from -inf) and min (from +inf)
             const int o_first = b << cshift;
@@ -514,10 +610,22 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 }
             }
         }
+        uint8_t* ef_out = T.error + (base >> 1);
+        if (staged) {
+            // codes out through the copy engine; the wait sits before the next tile's load
+            fence_async_smem();
+            __syncthreads();
+            MAB_CTICK(5);
+            if (t == 0) bulk_s2g(ef_out, st.ef, (uint32_t)n >> 1);
+            MAB_CTICK(6);
+#ifdef MAB_STATS
+            if (threadIdx.x == 0) atomicAdd(&g_stats_c[15], 1ull);
+#endif
+            continue;
+        }
         __syncthreads();
         MAB_CTICK(5);
         // codes out: whole words coalesced, the ragged end byte by byte
-        uint8_t* ef_out = T.error + (base >> 1);
         const int full_words = ((reinterpret_cast<uintptr_t>(ef_out) & 3) == 0) ? (n >> 3) : 0;
         for (int i = t; i < full_words; i += S_NT) reinterpret_cast<uint32_t*>(ef_out)[i] = st.ef[i];
         for (int i = full_words + t; i < n_oct; i += S_NT) {
@@ -530,6 +638,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         if (threadIdx.x == 0) atomicAdd(&g_stats_c[15], 1ull);
 #endif
     }
+    if (t == 0) bulk_wait_all();
 }
 
 int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s) {
@@ -538,8 +647,13 @@ int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int 
     const int smem = BfStage::bytes(max_dbs, qshift) + (int)sizeof(SmemSel);
     if (2 * (smem + 3 * 1024) > device_max_optin_smem() + 1024) return 1;       // two CTAs per SM do not fit: caller uses the other kernel
     const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count() * 2);
-    MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    ef_topk_quant_bf16_kernel<<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
+    if (qshift == 6) {
+        MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ef_topk_quant_bf16_kernel<true><<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
+    } else {
+        MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ef_topk_quant_bf16_kernel<false><<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
+    }
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_bf16_kernel launch");

@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "window.cuh"
 #include "fused.cuh"
+#include "async_copy.cuh"
 
 namespace mab {
 
@@ -292,15 +293,6 @@ __device__ __forceinline__ float adam_update_fast(float m, float v, float inv_bc
     float s;
     asm("sqrt.approx.f32 %0, %1;" : "=f"(s) : "f"(v * inv_bc2));
     return __fdividef(m * inv_bc1, s + eps);
-}
-
-// Asks L2 for the 128-byte lines of [base, base + bytes), the block's threads sharing the lines.
-template <int NT>
-__device__ __forceinline__ void prefetch_l2(uintptr_t base, int64_t bytes) {
-    const uintptr_t first = base & ~(uintptr_t)127;
-    const int lines = (int)((base + bytes - first + 127) >> 7);
-    for (int i = threadIdx.x; i < lines; i += NT)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(first + ((uintptr_t)i << 7)));
 }
 
 // Prefetches what the tile kernel will read of one unit: the block's parameters and its slices of
