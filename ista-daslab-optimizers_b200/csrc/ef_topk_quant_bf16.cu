@@ -39,16 +39,15 @@ __device__ int g_copy_timeout_bf16;
 struct __align__(16) SmemSel {
     uint32_t gt_bm[SEL_WORDS], tie_bm[SEL_WORDS], sel_bm[SEL_WORDS];
     int      sel_before[SEL_WORDS];
-    float    cand_val[S_CAND_CAP];
-    uint16_t cand_pos[S_CAND_CAP];       // position in the tile; bit 15 set once selected
+    uint32_t cand[S_CAND_CAP];           // candidates as (|value| bits << 16) | (0xFFFF - position): larger is better, all distinct
     uint16_t oct_list[S_OCT_CAP];        // octets that hold a candidate
     int      hist[256];
-    int      member[32];
+    uint32_t member[32];
     int      rot[64];
     int      counters[40];
     int      ctrl[8];
     int      scan[36];
-    int      n_member, kmax;
+    int      n_list, n_cand, kmax;
 };
 
 struct BfStage {
@@ -124,6 +123,18 @@ __device__ __forceinline__ void resolve_selection_smem(int need_ties, SmemSel& s
     __syncthreads();
 }
 
+// Reserves `cnt` consecutive slots behind *counter for every lane (one atomic per warp); returns the
+// lane's first slot.  All 32 lanes must call.
+__device__ __forceinline__ int warp_alloc(int cnt, int* counter) {
+    int inc = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, d); if (lane_id() >= d) inc += v; }
+    int base = 0;
+    if (lane_id() == 31 && inc) base = atomicAdd(counter, inc);
+    base = __shfl_sync(0xffffffffu, base, 31);
+    return base + inc - cnt;
+}
+
 // One octet of a = bf16(g + Qinv(e)) in place; returns the largest |a| of the octet.
 template <bool FAST>
 __device__ __forceinline__ float dequant_octet(uint4* tile4, const uint32_t* ef, int o, const QParams& q, const DecodeConsts& dc) {
@@ -181,7 +192,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         MAB_CTICK_DECL
         // ---- bring the tile in -------------------------------------------------------------------
         // (selection scratch is cleared here: the barrier that ends the load publishes it)
-        if (t == 0) { ss.kmax = 0; ss.n_member = 0; }
+        if (t == 0) { ss.kmax = 0; ss.n_list = 0; ss.n_cand = 0; }
         if (t < 64) ss.rot[t] = 0;
         if (t < 256) ss.hist[t] = 0;
         for (int w = t; w < SEL_WORDS; w += S_NT) { ss.gt_bm[w] = 0u; ss.tie_bm[w] = 0u; }
@@ -304,6 +315,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         const int kmax = ss.kmax;
         bool done = false;
         int C = 0;
+        uint32_t Tc_sel = 0;
         if (kmax == 0) {
             // every key is zero: the k lowest positions win the ties
             for (int w = t; w < SEL_WORDS; w += S_NT) {
@@ -340,119 +352,115 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             const int T_lo = have_lo ? lo : 0;
             if (T_lo > 0) {
                 const float T_lo_f = __int_as_float(T_lo);
-                // candidate octets -> list
+                const uint32_t T16 = ((uint32_t)T_lo + 0xFFFFu) >> 16;          // the bound as a bf16 magnitude
+                // 1. octets whose maximum reaches the bound -> list (any order)
                 int mine = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) mine += (omax[i] >= T_lo_f) ? 1 : 0;
-                int n_list;
-                int at = block_exclusive_scan(mine, ss.scan, n_list);
-                if (n_list <= S_OCT_CAP) {
+                int at = warp_alloc(mine, &ss.n_list);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        if (omax[i] >= T_lo_f)
-                            ss.oct_list[at++] = (uint16_t)(((t + (i >> cshift) * S_NT) << cshift) + ((i + lane) & (cpq - 1)));
-                    __syncthreads();
-                    // candidates of the listed octets (up to two octets per thread)
-                    mine = 0;
-                    for (int i = t; i < n_list; i += S_NT) {
-                        float v[8];
-                        unpack8(tile4[ss.oct_list[i]], v);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) mine += (fabsf(v[e]) >= T_lo_f) ? 1 : 0;
+                for (int i = 0; i < 8; ++i)
+                    if (omax[i] >= T_lo_f) {
+                        if (at < S_OCT_CAP) ss.oct_list[at] = (uint16_t)(((t + (i >> cshift) * S_NT) << cshift) + ((i + lane) & (cpq - 1)));
+                        ++at;
                     }
-                    at = block_exclusive_scan(mine, ss.scan, C);
-                    if (C <= S_CAND_CAP) {
-                        for (int i = t; i < n_list; i += S_NT) {
-                            const uint32_t o = ss.oct_list[i];
-                            float v[8];
-                            unpack8(tile4[o], v);
+                __syncthreads();
+                const int n_list = ss.n_list;
+                if (n_list <= S_OCT_CAP) {
+                    // 2. their values that reach the bound -> candidates (any order)
+                    for (int i0 = 0; i0 < n_list; i0 += S_NT) {
+                        const int i = i0 + t;
+                        uint32_t o = 0, mask = 0;
+                        if (i < n_list) {
+                            o = ss.oct_list[i];
+                            const uint4 v = tile4[o];
+                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (fabsf(v[e]) >= T_lo_f) { ss.cand_val[at] = v[e]; ss.cand_pos[at] = (uint16_t)((o << 3) | e); ++at; }
-                        }
-                        // radix histogram levels over [T_lo, kmax]; bf16 keys: a bin of <= 2^16 key bits is one value
-                        int r_lo = T_lo, r_hi = kmax, k_rem = k, R = C, sh = 31;
-                        for (int level = 0; level < 5; ++level) {
-                            const unsigned W1 = (unsigned)(r_hi - r_lo);
-                            sh = W1 < 256 ? 0 : (32 - __clz(W1)) - 8;
-                            if (level > 0 && t < 256) ss.hist[t] = 0;      // level 0 finds it cleared at the tile's start
-                            __syncthreads();                                // also publishes the candidate list
-                            for (int i = t; i < C; i += S_NT) {
-                                const int key = __float_as_int(fabsf(ss.cand_val[i]));
-                                if (key >= r_lo && key <= r_hi) atomicAdd(&ss.hist[(key - r_lo) >> sh], 1);
+                            for (int p = 0; p < 4; ++p) {
+                                mask |= ((w[p] & 0x7FFFu) >= T16) ? (1u << (2 * p)) : 0u;
+                                mask |= (((w[p] >> 16) & 0x7FFFu) >= T16) ? (2u << (2 * p)) : 0u;
                             }
-                            __syncthreads();
-                            if (warp == 0) {
-                                int h[8], s = 0;
+                        }
+                        int slot = warp_alloc(__popc(mask), &ss.n_cand);
+                        while (mask) {
+                            const uint32_t pos = (o << 3) + (__ffs(mask) - 1);
+                            mask &= mask - 1;
+                            if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(st.tile[pos] & 0x7FFFu) << 16) | (0xFFFFu - pos);
+                            ++slot;
+                        }
+                    }
+                    __syncthreads();
+                    C = ss.n_cand;
+                    if (C <= S_CAND_CAP) {
+                        // 3. one warp finds the k-th largest candidate (the composite values are distinct, so
+                        //    there are no ties left to break): 256-bin radix levels over the live range, the
+                        //    last <= 32 members ranked directly
+                        if (warp == S_NT / 32 - 1) {
+                            uint32_t lo_c = T16 << 16, hi_c = ((uint32_t)kmax & 0xFFFF0000u) | 0xFFFFu, Tc = 0;
+                            int k_rem = k;
+                            for (int level = 0; level < 6; ++level) {
+                                const uint32_t W1 = hi_c - lo_c;
+                                const int sh = W1 < 256u ? 0 : (32 - __clz(W1)) - 8;
+                                if (level > 0) {
 #pragma unroll
-                                for (int i = 0; i < 8; ++i) { h[i] = ss.hist[lane * 8 + i]; s += h[i]; }
-                                int suf = s;
+                                    for (int j = 0; j < 8; ++j) ss.hist[lane * 8 + j] = 0;
+                                    __syncwarp();
+                                }
+                                for (int i = lane; i < C; i += 32) {
+                                    const uint32_t c = ss.cand[i];
+                                    if (c >= lo_c && c <= hi_c) atomicAdd(&ss.hist[(c - lo_c) >> sh], 1);
+                                }
+                                __syncwarp();
+                                int h[8], sum = 0;
 #pragma unroll
-                                for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_down_sync(0xffffffffu, suf, o); if (lane + o < 32) suf += v; }
+                                for (int j = 0; j < 8; ++j) { h[j] = ss.hist[lane * 8 + j]; sum += h[j]; }
+                                int suf = sum;
+#pragma unroll
+                                for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_down_sync(0xffffffffu, suf, d); if (lane + d < 32) suf += v; }
                                 const unsigned okm = __ballot_sync(0xffffffffu, suf >= k_rem);
                                 const int owner = 31 - __clz(okm);
-                                if (lane == owner) {
-                                    int above = suf - s, b = 7;
+                                int above = suf - sum, bsel = 7;
 #pragma unroll
-                                    for (int i = 7; i >= 0; --i) if (b == i && above + h[i] < k_rem) { above += h[i]; b = i - 1; }
-                                    int hb = 0;
+                                for (int j = 7; j >= 0; --j) if (bsel == j && above + h[j] < k_rem) { above += h[j]; bsel = j - 1; }
+                                int hb = 0;
 #pragma unroll
-                                    for (int i = 0; i < 8; ++i) if (i == b) hb = h[i];
-                                    ss.ctrl[0] = lane * 8 + b; ss.ctrl[1] = k_rem - above; ss.ctrl[2] = hb;
-                                }
-                            }
-                            __syncthreads();
-                            const int b_star = ss.ctrl[0];
-                            k_rem = ss.ctrl[1];
-                            R = ss.ctrl[2];
-                            const int n_lo = r_lo + (b_star << sh);
-                            r_hi = (int)min((int64_t)r_hi, (int64_t)n_lo + ((int64_t)1 << sh) - 1);
-                            r_lo = n_lo;
-                            if (R <= 32 || sh <= 16) break;
-                        }
-                        if (R <= 32 || sh <= 16) {
-                            const bool by_rank = R <= 32;
-                            for (int i = t; i < C; i += S_NT) {
-                                const int key = __float_as_int(fabsf(ss.cand_val[i]));
-                                const uint32_t pos = ss.cand_pos[i];
-                                if (key > r_hi) { ss.cand_pos[i] = (uint16_t)(pos | 0x8000u); atomicOr(&ss.gt_bm[pos >> 5], 1u << (pos & 31)); }
-                                else if (key >= r_lo) {
-                                    if (by_rank) ss.member[atomicAdd(&ss.n_member, 1)] = i;
-                                    else atomicOr(&ss.tie_bm[pos >> 5], 1u << (pos & 31));
-                                }
-                            }
-                            __syncthreads();
-                            int need_ties = 0;
-                            if (by_rank) {
-                                const int nm = ss.n_member;
-                                for (int mw = warp; mw < nm; mw += S_NT / 32) {   // member mw against all members, one ballot
-                                    const int mi = ss.member[mw];
-                                    const int my_key = __float_as_int(fabsf(ss.cand_val[mi]));
-                                    const int my_pos = (int)(ss.cand_pos[mi] & 0x7FFFu);
-                                    const int idx = lane < nm ? ss.member[lane] : -1;
-                                    const int key = idx >= 0 ? __float_as_int(fabsf(ss.cand_val[idx])) : -1;
-                                    const int pos = idx >= 0 ? (int)(ss.cand_pos[idx] & 0x7FFFu) : 0x7fffffff;
-                                    const unsigned beats = __ballot_sync(0xffffffffu, key > my_key || (key == my_key && pos < my_pos));
-                                    if (lane == 0 && __popc(beats) < k_rem) {
-                                        ss.cand_pos[mi] = (uint16_t)(my_pos | 0x8000);
-                                        atomicOr(&ss.gt_bm[my_pos >> 5], 1u << (my_pos & 31));
+                                for (int j = 0; j < 8; ++j) if (j == bsel) hb = h[j];
+                                const int b_star = __shfl_sync(0xffffffffu, lane * 8 + bsel, owner);
+                                k_rem -= __shfl_sync(0xffffffffu, above, owner);
+                                hb = __shfl_sync(0xffffffffu, hb, owner);
+                                lo_c += (uint32_t)b_star << sh;
+                                hi_c = min(hi_c, lo_c + ((1u << sh) - 1u));
+                                if (sh == 0) { Tc = lo_c; break; }
+                                if (hb <= 32) {
+                                    int base = 0;
+                                    for (int i0 = 0; i0 < C; i0 += 32) {
+                                        const int i = i0 + lane;
+                                        const uint32_t c = i < C ? ss.cand[i] : 0u;
+                                        const bool in = c >= lo_c && c <= hi_c;
+                                        const unsigned bal = __ballot_sync(0xffffffffu, in);
+                                        if (in) ss.member[base + __popc(bal & ((1u << lane) - 1u))] = c;
+                                        base += __popc(bal);
                                     }
+                                    __syncwarp();
+                                    const uint32_t me = lane < base ? ss.member[lane] : 0u;
+                                    int greater = 0;
+                                    for (int j = 0; j < base; ++j) greater += (__shfl_sync(0xffffffffu, me, j) > me) ? 1 : 0;
+                                    const unsigned hit = __ballot_sync(0xffffffffu, lane < base && greater == k_rem - 1);
+                                    Tc = __shfl_sync(0xffffffffu, me, __ffs(hit) - 1);
+                                    break;
                                 }
-                            } else {
-                                need_ties = k_rem;
                             }
-                            resolve_selection_smem(need_ties, ss);
-                            if (!by_rank) {
-                                for (int i = t; i < C; i += S_NT) {
-                                    const uint32_t pos = ss.cand_pos[i];
-                                    const int key = __float_as_int(fabsf(ss.cand_val[i]));
-                                    if (!(pos & 0x8000u) && key >= r_lo && key <= r_hi && ((ss.sel_bm[pos >> 5] >> (pos & 31)) & 1u))
-                                        ss.cand_pos[i] = (uint16_t)(pos | 0x8000u);
-                                }
-                                __syncthreads();
-                            }
-                            done = true;
+                            if (lane == 0) ss.ctrl[3] = (int)Tc;
                         }
+                        __syncthreads();
+                        Tc_sel = (uint32_t)ss.ctrl[3];
+                        // 4. selected positions -> bitmap -> ranks
+                        for (int i = t; i < C; i += S_NT) {
+                            const uint32_t c = ss.cand[i];
+                            if (c >= Tc_sel) { const uint32_t pos = 0xFFFFu - (c & 0xFFFFu); atomicOr(&ss.gt_bm[pos >> 5], 1u << (pos & 31)); }
+                        }
+                        resolve_selection_smem(0, ss);
+                        done = true;
                     }
                 }
             }
@@ -496,21 +504,14 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
 
         MAB_CTICK(3);
         // ---- I[row], V[row]; selected positions become 0 in the tile ------------------------------------
-        {
-            const int w0 = t * S_WPT;
-#pragma unroll
-            for (int i = 0; i < S_WPT; ++i) {
-                uint32_t sel = ss.sel_bm[w0 + i];
-                int p = ss.sel_before[w0 + i];
-                while (sel) { const int b = __ffs(sel) - 1; sel &= sel - 1; i_out[p++] = (int16_t)((w0 + i) * 32 + b); }
-            }
-        }
         if (C >= 0) {
             for (int i = t; i < C; i += S_NT) {
-                const uint32_t pos = ss.cand_pos[i];
-                if (pos & 0x8000u) {
-                    const uint32_t q = pos & 0x7FFFu, w = q >> 5;
-                    v_out[ss.sel_before[w] + __popc(ss.sel_bm[w] & ((1u << (q & 31)) - 1u))] = (uint16_t)(__float_as_uint(ss.cand_val[i]) >> 16);
+                const uint32_t c = ss.cand[i];
+                if (c >= Tc_sel) {
+                    const uint32_t q = 0xFFFFu - (c & 0xFFFFu), w = q >> 5;
+                    const int rank = ss.sel_before[w] + __popc(ss.sel_bm[w] & ((1u << (q & 31)) - 1u));
+                    i_out[rank] = (int16_t)q;
+                    v_out[rank] = st.tile[q];
                     st.tile[q] = 0;
                 }
             }
@@ -520,7 +521,14 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             for (int i = 0; i < S_WPT; ++i) {
                 uint32_t sel = ss.sel_bm[w0 + i];
                 int p = ss.sel_before[w0 + i];
-                while (sel) { const int b = __ffs(sel) - 1; sel &= sel - 1; const int q = (w0 + i) * 32 + b; v_out[p++] = st.tile[q]; st.tile[q] = 0; }
+                while (sel) {
+                    const int b = __ffs(sel) - 1;
+                    sel &= sel - 1;
+                    const int q = (w0 + i) * 32 + b;
+                    i_out[p] = (int16_t)q;
+                    v_out[p++] = st.tile[q];
+                    st.tile[q] = 0;
+                }
             }
         }
         __syncthreads();
