@@ -91,7 +91,8 @@ __device__ __forceinline__ uint32_t cvt_bf16x2_rne(float a, float b) {
 
 // p <- round_p(round_p(p * decay) - lr * u) for 8 values, two per instruction (packed f32x2
 // operations round each component like the scalar ones).
-template <typename TP>
+// HAS_U = false: only the decay (the caller updates the few touched elements afterwards).
+template <typename TP, bool HAS_U = true>
 __device__ __forceinline__ void update_octet(float (&pv)[8], const float (&u)[8], bool do_decay, float2 decay2, float2 neg_lr2) {
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
@@ -103,7 +104,7 @@ __device__ __forceinline__ void update_octet(float (&pv)[8], const float (&u)[8]
                 x = make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
             }
         }
-        x = __ffma2_rn(neg_lr2, make_float2(u[2 * b], u[2 * b + 1]), x);
+        if (HAS_U) x = __ffma2_rn(neg_lr2, make_float2(u[2 * b], u[2 * b + 1]), x);
         pv[2 * b] = x.x; pv[2 * b + 1] = x.y;
     }
 }
@@ -129,7 +130,15 @@ template <> struct RawOctet<uint16_t> {
 };
 
 // Where the streaming loop gets the update of octet o (8 consecutive elements of the range) from.
+struct NoU {                    // no update: the stream only applies the weight decay
+    static constexpr bool has_u = false;
+    __device__ __forceinline__ void load(int, float (&v)[8]) const {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+    }
+};
 struct DenseU {                 // a dense float array in shared memory, 16-byte aligned
+    static constexpr bool has_u = true;
     const float* u;
     __device__ __forceinline__ void load(int o, float (&v)[8]) const {
         const float4 a = reinterpret_cast<const float4*>(u + o * 8)[0], b = reinterpret_cast<const float4*>(u + o * 8)[1];
@@ -137,6 +146,7 @@ struct DenseU {                 // a dense float array in shared memory, 16-byte
     }
 };
 struct SparseU {                // touched positions as a bitmap, their updates compact in slot order
+    static constexpr bool has_u = true;
     const uint32_t* bitmap;     // bit i of the range set <=> position i touched
     const uint16_t* prefix;     // touched positions in lower bitmap words
     const float2* mv;           // .x = update of the slot
@@ -200,7 +210,7 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
                     float pv[8], u[8];
                     cur[i].unpack(pv);
                     src.load(o, u);
-                    update_octet<TP>(pv, u, do_decay, decay2, neg_lr2);
+                    update_octet<TP, USrc::has_u>(pv, u, do_decay, decay2, neg_lr2);
                     Octet<TP>::store(p + o * 8, pv, true, 8);
                 }
             }
@@ -213,7 +223,7 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
             float pv[8], u[8];
             Octet<TP>::load(p + o * 8, pv, false, n);
             src.load(o, u);
-            update_octet<TP>(pv, u, do_decay, decay2, neg_lr2);
+            update_octet<TP, USrc::has_u>(pv, u, do_decay, decay2, neg_lr2);
             Octet<TP>::store(p + o * 8, pv, false, n);
         }
         return;
@@ -284,7 +294,7 @@ __host__ __device__ constexpr int wt_row_stride(int max_k) { return ((max_k * 2 
 
 __host__ __device__ constexpr int wt_smem_bytes(int rows, int max_k) {
     const int e = (rows * max_k + 3) & ~3;
-    return 8 * e + rows * 2 * wt_row_stride(max_k) + 4 * WT_WORDS + 2 * WT_WORDS;
+    return 8 * e + rows * 2 * wt_row_stride(max_k) + 4 * WT_WORDS + 2 * WT_WORDS + 2 * e;
 }
 
 // Fast (not correctly rounded) form of m_hat / (sqrt(v_hat) + eps): the update is specified to
@@ -304,10 +314,13 @@ __device__ __forceinline__ void prefetch_unit(const mab_tensor& T, int blk, int 
     const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
     const int kcnt = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
     prefetch_l2<NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
-    const int64_t koff = (int64_t)blk * T.k_block_size_many;
-    for (int r = 0; r < rows; ++r) {
-        prefetch_l2<NT>(reinterpret_cast<uintptr_t>(T.I + koff + (int64_t)r * T.k), 2 * kcnt);
-        prefetch_l2<NT>(reinterpret_cast<uintptr_t>(T.V + koff + (int64_t)r * T.k), 2 * kcnt);
+    if ((int)threadIdx.x < 2 * rows) {                         // one thread per row slice of I or V
+        const int r = threadIdx.x >> 1;
+        const int64_t off = (int64_t)blk * T.k_block_size_many + (int64_t)r * T.k;
+        const uintptr_t base = (threadIdx.x & 1) ? reinterpret_cast<uintptr_t>(T.V + off) : reinterpret_cast<uintptr_t>(T.I + off);
+        const uintptr_t end = base + 2u * kcnt;
+        for (uintptr_t line = base & ~(uintptr_t)127; line < end; line += 128)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
     }
 }
 
@@ -329,6 +342,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     unsigned char* raw = reinterpret_cast<unsigned char*>(mv + ecap);       // rows x {I slice, V slice}, rstride bytes each
     uint32_t* bitmap = reinterpret_cast<uint32_t*>(raw + rows * 2 * rstride);
     uint16_t* prefix = reinterpret_cast<uint16_t*>(bitmap + WT_WORDS);
+    uint16_t* spos = prefix + WT_WORDS;                                      // position of each slot
     const int t = threadIdx.x;
 
     for (int i = t; i < n_tensors; i += WT_THREADS) s_first[i] = tensors[i].first_unit_a;
@@ -423,7 +437,9 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         for (int i = t; i < E; i += WT_THREADS) {
             uint16_t* pp = pos_ptr(i);
             const uint32_t pos = *pp;
-            *pp = (uint16_t)(prefix[pos >> 5] + __popc(bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u)));
+            const uint32_t slot = prefix[pos >> 5] + __popc(bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u));
+            *pp = (uint16_t)slot;
+            spos[slot] = (uint16_t)pos;                        // entries of one position write the same value
         }
         __syncthreads();
         MAB_BTICK(3);
@@ -449,9 +465,26 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         }
         __syncthreads();
         MAB_BTICK(5);
-        // 6. stream the whole block; each octet finds its updates through the bitmap
-        const SparseU src{bitmap, prefix, mv};
-        stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk);
+        if (MODE == MODE_STEP && !ALPHA) {
+            // 6. without the alpha term only the touched positions get an update: stream the block for the
+            //    weight decay alone (nothing to stream without decay), then update the touched elements
+            //    one by one; fma(-lr, 0, x) == x, so the untouched elements are already final
+            if (T.weight_decay > 0.0) {
+                stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, NoU{}, blk_base, n_blk);
+                __syncthreads();                               // the decayed values are read back below
+            }
+            MAB_BTICK(6);
+            TP* p = reinterpret_cast<TP*>(T.param) + blk_base;
+            const float neg_lr = T.neg_lr_f32;
+            for (int s2 = t; s2 < touched; s2 += WT_THREADS) {
+                const int pos = spos[s2];
+                Elem<TP>::store(p, pos, __fmaf_rn(neg_lr, mv[s2].x, Elem<TP>::load(p, pos)));
+            }
+        } else {
+            // 6. stream the whole block; each octet finds its updates through the bitmap
+            const SparseU src{bitmap, prefix, mv};
+            stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk);
+        }
         MAB_BTICK(7);
         __syncthreads();                                       // everything is reused by the next unit
         MAB_BTICK(8);
@@ -462,7 +495,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
 }
 
 template <typename TP, int MODE, bool ALPHA>
-__global__ void __launch_bounds__(WT_THREADS)
+__global__ void __launch_bounds__(WT_THREADS, ALPHA ? 1 : 4)
 window_tile_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int max_k,
                    const __grid_constant__ WindowArgs a) {
     window_tile_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, max_k, a);
