@@ -305,16 +305,10 @@ __device__ __forceinline__ float adam_update_fast(float m, float v, float inv_bc
     return __fdividef(m * inv_bc1, s + eps);
 }
 
-// Prefetches what the tile kernel will read of one unit: the block's parameters and its slices of
-// the valid window rows.
-template <typename TP, int NT>
-__device__ __forceinline__ void prefetch_unit(const mab_tensor& T, int blk, int rows) {
-    const int dbs = T.d_block_size;
-    const int64_t blk_base = (int64_t)blk * dbs;
-    const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
-    const int kcnt = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
-    prefetch_l2<NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
-    if ((int)threadIdx.x < 2 * rows) {                         // one thread per row slice of I or V
+// Asks L2 for one unit's slices of the valid window rows: one thread per row slice of I or V.
+__device__ __forceinline__ void prefetch_window_rows(const mab_tensor& T, int blk, int rows) {
+    if ((int)threadIdx.x < 2 * rows) {
+        const int kcnt = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
         const int r = threadIdx.x >> 1;
         const int64_t off = (int64_t)blk * T.k_block_size_many + (int64_t)r * T.k;
         const uintptr_t base = (threadIdx.x & 1) ? reinterpret_cast<uintptr_t>(T.V + off) : reinterpret_cast<uintptr_t>(T.I + off);
@@ -350,23 +344,27 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     __syncthreads();
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
     const int chunks_per_row = rstride >> 4;
-    if (MODE == MODE_STEP && (int)blockIdx.x < total_units) {
-        const int ti = find_tensor(s_first, n_tensors, blockIdx.x);
-        prefetch_unit<TP, WT_THREADS>(tensors[ti], blockIdx.x - s_first[ti], rows);
-    }
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int ti = find_tensor(s_first, n_tensors, unit);
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
-        if (MODE == MODE_STEP && unit + (int)gridDim.x < total_units) {     // the unit after this one: into L2 while this one runs
-            const int nu = unit + gridDim.x;
-            const int nti = find_tensor(s_first, n_tensors, nu);
-            prefetch_unit<TP, WT_THREADS>(tensors[nti], nu - s_first[nti], rows);
-        }
         const int dbs = T.d_block_size, nfull = T.topk_full_blocks_count;
         const int64_t blk_base = (int64_t)blk * dbs;
         const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
+        if (MODE == MODE_STEP) {
+            // this block's parameters travel to L2 while the window is worked on (asked for any earlier,
+            // other CTAs' traffic pushes them out again before they are used); the next unit's window
+            // rows are small and are asked for now
+#ifndef MAB_X_NOPF
+            prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
+#endif
+            if (unit + (int)gridDim.x < total_units) {
+                const int nu = unit + gridDim.x;
+                const int nti = find_tensor(s_first, n_tensors, nu);
+                prefetch_window_rows(tensors[nti], nu - s_first[nti], rows);
+            }
+        }
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
         const int64_t koff = (int64_t)blk * T.k_block_size_many;
         const int64_t pitch = T.k;
