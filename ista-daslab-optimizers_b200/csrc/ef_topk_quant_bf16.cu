@@ -1,15 +1,20 @@
-// Kernel A for bf16 gradients: the tile lives in shared memory, two CTAs per SM.
+// Kernel A for bf16 gradients: the tile lives in shared memory, three CTAs per SM.
 //
-// A bf16 tile (29 056 values) is 58 KB, so two tiles fit one SM.  The tile is staged by the bulk
-// copy engine, turned into a = g + Qinv(e) in place, searched, zeroed at the selected positions and
-// re-quantised, all in shared memory; registers hold nothing across phases, so a CTA needs only 512
-// threads with 64 registers and two CTAs run per SM: one tile's barrier-bound selection overlaps the
-// other tile's arithmetic.  A thread owns whole quantisation blocks (64 consecutive values for
-// quant_block_size 64), so block statistics need no shuffles and the decode / encode constants are
-// computed once per block instead of once per 8 values.
+// A bf16 tile (29 056 values) is 58 KB.  Only the tile and 16 KB of selection scratch sit in shared
+// memory (codes and statistics are read from and written to global memory directly, coalesced), so
+// three CTAs of 256 threads fit one SM and one tile's latency-bound selection overlaps the other
+// tiles' arithmetic.  The tile is staged by the bulk copy engine, turned into a = g + Qinv(e) in
+// place, searched, zeroed at the selected positions and re-quantised.
+//
+// Work is mapped two ways.  Decode and encode walk the tile octet by octet (thread t owns octets
+// t, t + 256, ...: consecutive lanes touch consecutive 16-byte pieces of the tile and consecutive
+// code words in global memory) and fetch the constants of an octet's quantisation block from a
+// small table in shared memory.  Statistics walk it block by block (thread t owns quantisation
+// blocks t, t + 256; no shuffles).  For quant_block_size 64 the block tables fit the scratch; other
+// block sizes take general per-block code in the same kernel.
 //
 // Results are bit-identical to the register-resident kernel in ef_topk_quant.cu (same arithmetic,
-// same tie rule); that kernel keeps serving fp32 gradients, whose 116 KB tiles allow one CTA per SM.
+// same tie rule); that kernel keeps serving fp32 gradients.
 #include "common.cuh"
 #include "select.cuh"
 #include "codec_fast.cuh"
@@ -18,11 +23,15 @@
 
 namespace mab {
 
-constexpr int S_NT = 512;
-constexpr int S_WPT = SEL_WORDS / S_NT;     // bitmap words per thread
-constexpr int S_CAND_CAP = 2048;
-constexpr int S_OCT_CAP = 1024;
+constexpr int S_NT = 256;
+constexpr int S_CTAS = 3;                    // resident CTAs per SM the shared memory is sized for
+constexpr int S_SLOTS = SEL_MAX_TILE / 8 / S_NT;   // octets per thread: 16
+constexpr int S_WPT = SEL_WORDS / S_NT;      // bitmap words per thread: 4
+constexpr int S_CAND_CAP = 1536;
+constexpr int S_WLIST = 128;                 // octets with a candidate, per warp
+constexpr int S_QTAB = 512;                  // quantisation blocks whose constants fit the tables
 constexpr int S_MAX_TENSORS = 512;
+static_assert(S_WPT == 4, "a thread owns four consecutive bitmap words");
 
 #ifdef MAB_STATS
 __device__ unsigned long long g_stats_c[16];
@@ -37,31 +46,23 @@ __device__ unsigned long long g_stats_c[16];
 __device__ int g_copy_timeout_bf16;
 
 struct __align__(16) SmemSel {
-    uint32_t gt_bm[SEL_WORDS], tie_bm[SEL_WORDS], sel_bm[SEL_WORDS];
-    int      sel_before[SEL_WORDS];
-    uint32_t cand[S_CAND_CAP];           // candidates as (|value| bits << 16) | (0xFFFF - position): larger is better, all distinct
-    uint16_t oct_list[S_OCT_CAP];        // octets that hold a candidate
+    union {
+        uint32_t cand[S_CAND_CAP];       // candidates as (|value| bits << 16) | (0xFFFF - position): larger is better, all distinct
+        struct {                         // before and after the selection: constants of each quantisation block
+            float2 mu[S_QTAB];           //   (min, u)
+            float  r0[S_QTAB];           //   1/u for the encoder, 0 where the defining form must run
+        } qt;
+    };
+    uint32_t sel_bm[SEL_WORDS];          // selected positions
+    uint16_t sel_before[SEL_WORDS];      // selected positions in lower words
+    uint16_t oct_list[(S_NT / 32) * S_WLIST];
     int      hist[256];
     uint32_t member[32];
     int      rot[64];
     int      counters[40];
     int      ctrl[8];
     int      scan[36];
-    int      n_list, n_cand, kmax;
-};
-
-struct BfStage {
-    uint16_t* tile; uint32_t* ef; uint16_t* mn; uint16_t* mx;
-    __host__ __device__ static int tile_bytes(int elems) { return (elems * 2 + 127) & ~127; }
-    __host__ __device__ static int ef_bytes(int elems) { return ((elems >> 1) + 127) & ~127; }
-    __host__ __device__ static int st_bytes(int elems, int qshift) { return ((((elems >> qshift) + 4) * 2) + 15) & ~15; }
-    __host__ __device__ static int bytes(int elems, int qshift) { return tile_bytes(elems) + ef_bytes(elems) + 2 * st_bytes(elems, qshift); }
-    __device__ BfStage(unsigned char* raw, int elems, int qshift) {
-        tile = reinterpret_cast<uint16_t*>(raw);
-        ef = reinterpret_cast<uint32_t*>(raw + tile_bytes(elems));
-        mn = reinterpret_cast<uint16_t*>(raw + tile_bytes(elems) + ef_bytes(elems));
-        mx = reinterpret_cast<uint16_t*>(raw + tile_bytes(elems) + ef_bytes(elems) + st_bytes(elems, qshift));
-    }
+    int      n_member, n_cand, kmax, pad;
 };
 
 __device__ __forceinline__ void unpack8(const uint4& a, float (&v)[8]) {
@@ -71,7 +72,17 @@ __device__ __forceinline__ void unpack8(const uint4& a, float (&v)[8]) {
     v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
 }
 
-__device__ __forceinline__ int key_of_bits(uint16_t b) { return (int)(b & 0x7FFFu) << 16; }   // |value| as float key bits
+// Reserves `cnt` consecutive slots behind *counter for every lane (one atomic per warp); returns the
+// lane's first slot.  All 32 lanes must call.
+__device__ __forceinline__ int warp_alloc(int cnt, int* counter) {
+    int inc = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, d); if (lane_id() >= d) inc += v; }
+    int base = 0;
+    if (lane_id() == 31 && inc) base = atomicAdd(counter, inc);
+    base = __shfl_sync(0xffffffffu, base, 31);
+    return base + inc - cnt;
+}
 
 // Number of tile elements with key >= thr (key bits), every thread of the CTA calling.
 __device__ __forceinline__ int tile_count_ge(const uint16_t* tile, int n_oct, int thr, int* counter) {
@@ -89,20 +100,19 @@ __device__ __forceinline__ int tile_count_ge(const uint16_t* tile, int n_oct, in
     return *reinterpret_cast<volatile int*>(counter);
 }
 
-// From gt_bm / tie_bm: sel_bm = gt | (the need_ties lowest tie positions), sel_before = prefix popcount.
-// Every thread owns S_WPT consecutive bitmap words.  Starts and ends with a barrier.
-__device__ __forceinline__ void resolve_selection_smem(int need_ties, SmemSel& ss) {
+// sel_bm = gt | (the need_ties lowest positions of tie), sel_before = prefix popcount, from the
+// thread's own four words of both masks.  Starts and ends with a barrier.
+__device__ __forceinline__ void resolve_selection_regs(const uint32_t (&gt)[S_WPT], uint32_t (&tw)[S_WPT], int need_ties, SmemSel& ss) {
     __syncthreads();
     const int w0 = threadIdx.x * S_WPT;
     uint32_t sel[S_WPT];
     int total;
 #pragma unroll
-    for (int i = 0; i < S_WPT; ++i) sel[i] = ss.gt_bm[w0 + i];
+    for (int i = 0; i < S_WPT; ++i) sel[i] = gt[i];
     if (need_ties > 0) {
-        uint32_t tw[S_WPT];
         int cnt = 0;
 #pragma unroll
-        for (int i = 0; i < S_WPT; ++i) { tw[i] = ss.tie_bm[w0 + i]; cnt += __popc(tw[i]); }
+        for (int i = 0; i < S_WPT; ++i) cnt += __popc(tw[i]);
         int before = block_exclusive_scan(cnt, ss.scan, total);
 #pragma unroll
         for (int i = 0; i < S_WPT; ++i) {
@@ -119,29 +129,37 @@ __device__ __forceinline__ void resolve_selection_smem(int need_ties, SmemSel& s
     for (int i = 0; i < S_WPT; ++i) cnt += __popc(sel[i]);
     int before = block_exclusive_scan(cnt, ss.scan, total);
 #pragma unroll
-    for (int i = 0; i < S_WPT; ++i) { ss.sel_bm[w0 + i] = sel[i]; ss.sel_before[w0 + i] = before; before += __popc(sel[i]); }
+    for (int i = 0; i < S_WPT; ++i) { ss.sel_bm[w0 + i] = sel[i]; ss.sel_before[w0 + i] = (uint16_t)before; before += __popc(sel[i]); }
     __syncthreads();
 }
 
-// Reserves `cnt` consecutive slots behind *counter for every lane (one atomic per warp); returns the
-// lane's first slot.  All 32 lanes must call.
-__device__ __forceinline__ int warp_alloc(int cnt, int* counter) {
-    int inc = cnt;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, d); if (lane_id() >= d) inc += v; }
-    int base = 0;
-    if (lane_id() == 31 && inc) base = atomicAdd(counter, inc);
-    base = __shfl_sync(0xffffffffu, base, 31);
-    return base + inc - cnt;
+// The four code bytes of octet o (elements [8 o, 8 o + 8) of a tile of n elements), missing bytes as 0.
+__device__ __forceinline__ uint32_t load_code_word(const uint8_t* ef_g, bool aligned4, int o, int n) {
+    if (aligned4 && o * 8 + 8 <= n) return reinterpret_cast<const uint32_t*>(ef_g)[o];
+    uint32_t w = 0;
+    for (int b = 0; b < 4; ++b) if (o * 8 + 2 * b < n) w |= (uint32_t)ef_g[o * 4 + b] << (8 * b);
+    return w;
 }
 
-// One octet of a = bf16(g + Qinv(e)) in place; returns the largest |a| of the octet.
-template <bool FAST>
-__device__ __forceinline__ float dequant_octet(uint4* tile4, const uint32_t* ef, int o, const QParams& q, const DecodeConsts& dc) {
+__device__ __forceinline__ void store_code_word(uint8_t* ef_g, bool aligned4, int o, int n, uint32_t w) {
+    if (aligned4 && o * 8 + 8 <= n) { reinterpret_cast<uint32_t*>(ef_g)[o] = w; return; }
+    for (int b = 0; b < 4; ++b) if (o * 8 + 2 * b < n) ef_g[o * 4 + b] = (uint8_t)(w >> (8 * b));
+}
+
+#ifndef S_GROUP
+#define S_GROUP 2
+#endif
+constexpr int S_FULL = 14;                   // 29 056 values = 3632 octets: every thread has 14 whole octets, some a 15th
+
+// One octet of a = bf16(g + Qinv(e)) in place (positions >= n of a ragged tile stay zero); returns the
+// largest |a| of the octet.
+// RAGGED = false promises a whole octet; `commit` = false computes but leaves the tile as it is.
+template <bool FAST, bool RAGGED>
+__device__ __forceinline__ float dequant_octet(uint4* tile4, int o, int n, uint32_t codes, const QParams& q, const DecodeConsts& dc, bool commit) {
     float gv[8], x[8];
     unpack8(tile4[o], gv);
-    if (FAST) decode_octet_fast(ef[o], dc, x);
-    else decode_octet_exact(ef[o], q, x);
+    if (FAST) decode_octet_fast(codes, dc, x);
+    else decode_octet_exact(codes, q, x);
     uint4 out;
     uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
@@ -149,21 +167,96 @@ __device__ __forceinline__ float dequant_octet(uint4* tile4, const uint32_t* ef,
         const float2 s = __fadd2_rn(make_float2(gv[2 * p], gv[2 * p + 1]), make_float2(x[2 * p], x[2 * p + 1]));
         ow[p] = pack_bf16x2_rne(s.x, s.y);
     }
-    tile4[o] = out;
+    if (RAGGED && o * 8 + 8 > n) {                           // the tile's last, short octet
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const int e0 = o * 8 + 2 * p;
+            if (e0 + 1 >= n) ow[p] = (e0 >= n) ? 0u : (ow[p] & 0xFFFFu);
+        }
+    }
+    if (commit) tile4[o] = out;
     const uint32_t m2 = maxabs_bf16x2(maxabs_bf16x2(ow[0], ow[1]), maxabs_bf16x2(ow[2], ow[3]));
     return fmaxf(fabsf(__uint_as_float(m2 << 16)), fabsf(__uint_as_float(m2 & 0xFFFF0000u)));
 }
 
-// QB64: quant_block_size is 64, so a thread's quantisation block is 8 octets and the loops over
-// them unroll; tiles that are not whole (a tensor's last block) or not aligned take the general code.
+// a = bf16(g + Qinv(e)) in place for the thread's octets t, t + S_NT, ...; per-octet maxima to omax.
+// The first FS octets of every thread are promised to exist, to be whole and to find their block in
+// the table, so their code is one branch-free block whose octets the compiler can interleave.
+template <int FS>
+__device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, bool tables, const uint16_t* mn_g, const uint16_t* mx_g,
+                                              int cshift, int n, int n_oct, const uint32_t (&cw)[S_SLOTS], float (&omax)[S_SLOTS]) {
+    const int t = threadIdx.x;
+    uint32_t slow = 0u;                                      // octets whose block needs the defining decode
+#pragma unroll
+    for (int j = 0; j < S_SLOTS; ++j) {
+        omax[j] = 0.0f;
+        const int o = t + j * S_NT;
+        if (j < FS) {
+            if (j % S_GROUP == 0) asm volatile("" ::: "memory");   // octets are interleaved within a group only (register pressure)
+            const float2 c = ss.qt.mu[o >> 3];
+            const QParams q = {c.x, c.y};
+            const DecodeConsts dc = decode_consts(q);
+            const float m = dequant_octet<true, false>(tile4, o, n, cw[j], q, dc, dc.fast);
+            omax[j] = dc.fast ? m : 0.0f;
+            slow |= dc.fast ? 0u : (1u << j);
+        } else if (o < n_oct) {
+            QParams q;
+            if (tables) { const float2 c = ss.qt.mu[o >> 3]; q.mn = c.x; q.u = c.y; }
+            else q = qparams(mn_g[o >> cshift], mx_g[o >> cshift]);
+            const DecodeConsts dc = decode_consts(q);
+            if (!dc.fast) slow |= 1u << j;
+            else omax[j] = dequant_octet<true, true>(tile4, o, n, cw[j], q, dc, true);
+        }
+    }
+    if (slow) {
+#pragma unroll
+        for (int j = 0; j < S_SLOTS; ++j) {
+            if ((slow >> j) & 1u) {
+                const int o = t + j * S_NT;
+                const QParams q = qparams(mn_g[o >> cshift], mx_g[o >> cshift]);
+                omax[j] = dequant_octet<false, true>(tile4, o, n, cw[j], q, decode_consts(q), true);
+            }
+        }
+    }
+}
+
+// Codes of the thread's octets from the block tables, written to global memory; octets that came too
+// close to a code boundary (or whose block is degenerate) are left to the caller in `redo`.  The
+// first FS octets of every thread are promised to exist, to be whole and their code words aligned.
+template <int FS>
+__device__ __forceinline__ void encode_phase(const uint4* tile4, const SmemSel& ss, uint8_t* ef_out, bool ef_al4, int n, int n_oct, uint32_t& redo) {
+    const int t = threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < S_SLOTS; ++j) {
+        const int o = t + j * S_NT;
+        if (j < FS || o < n_oct) {
+            if (j < FS && j % S_GROUP == 0) asm volatile("" ::: "memory");
+            const float2 mu = ss.qt.mu[o >> 3];
+            const float r0 = ss.qt.r0[o >> 3];
+            EncodeConsts ec;
+            ec.nmn2 = make_float2(-mu.x, -mu.x); ec.r02 = make_float2(r0, r0); ec.fast = true;
+            float r[8], worst;
+            unpack8(tile4[o], r);
+            const uint32_t w = encode_octet_speculative<false>(r, ec, worst);   // exact statistics of bf16 values: no clamp needed
+            const bool ok = worst <= CODEC_SAFE_FRAC && r0 != 0.0f;
+            if (j < FS) { if (ok) reinterpret_cast<uint32_t*>(ef_out)[o] = w; }
+            else if (ok) store_code_word(ef_out, ef_al4, o, n, w);
+            redo |= ok ? 0u : (1u << j);
+        }
+    }
+}
+
+// QB64: quant_block_size is 64: the per-block constants fit the shared-memory tables and the loops
+// over a block's 8 octets unroll.
 template <bool QB64>
-__global__ void __launch_bounds__(S_NT, 2)
+__global__ void __launch_bounds__(S_NT, S_CTAS)
 ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];       // [staging: tile | codes | statistics][SmemSel]
+    extern __shared__ __align__(128) unsigned char smem_raw[];       // [tile][SmemSel]
     __shared__ int s_first[S_MAX_TENSORS + 1];
     __shared__ __align__(8) uint64_t s_bar;
-    const BfStage st(smem_raw, stage_elems, qshift);
-    SmemSel& ss = *reinterpret_cast<SmemSel*>(smem_raw + BfStage::bytes(stage_elems, qshift));
+    uint16_t* tile = reinterpret_cast<uint16_t*>(smem_raw);
+    uint4* tile4 = reinterpret_cast<uint4*>(smem_raw);
+    SmemSel& ss = *reinterpret_cast<SmemSel*>(smem_raw + ((stage_elems * 2 + 127) & ~127));
     const int t = threadIdx.x, lane = lane_id(), warp = warp_id();
     for (int i = t; i < n_tensors; i += S_NT) s_first[i] = tensors[i].first_unit_a;
     if (t == 0) { s_first[n_tensors] = total_units; mbar_init(&s_bar, 1); }
@@ -182,54 +275,54 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         const int n = (int)min((int64_t)dbs, T.d - base);
         const int k = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
         const uint16_t* g = reinterpret_cast<const uint16_t*>(T.grad) + base;
-        const uint8_t* ef_g = T.error + (base >> 1);
+        const uint8_t* ef_in = T.error + (base >> 1);
+        uint8_t* ef_out = T.error + (base >> 1);
         const int64_t qb0 = base >> qshift;
         const int n_oct = (n + 7) >> 3, n_qb = (n + (1 << qshift) - 1) >> qshift;
-        const int skip = (int)(qb0 & 1);
-        const bool staged = (n & 31) == 0 && (n & ((1 << qshift) - 1)) == 0 && aligned16(g) && aligned16(ef_g) &&
-                            ((reinterpret_cast<uintptr_t>(T.min_vals) | reinterpret_cast<uintptr_t>(T.max_vals)) & 3) == 0;
+        const bool staged = (n & 7) == 0 && aligned16(g);            // the bulk copy moves whole 16-byte pieces
+        const bool ef_al4 = (reinterpret_cast<uintptr_t>(ef_in) & 3) == 0;
+        const bool tables = QB64 && n_qb <= S_QTAB;
+        const uint16_t* mn_g = T.min_vals + qb0;
+        const uint16_t* mx_g = T.max_vals + qb0;
 
         MAB_CTICK_DECL
-        // ---- bring the tile in -------------------------------------------------------------------
+        // ---- bring the tile in; meanwhile codes -> registers, decode constants -> table ---------------------
         // (selection scratch is cleared here: the barrier that ends the load publishes it)
-        if (t == 0) { ss.kmax = 0; ss.n_list = 0; ss.n_cand = 0; }
+        if (t == 0) { ss.kmax = 0; ss.n_member = 0; ss.n_cand = 0; ss.ctrl[4] = 0; }
         if (t < 64) ss.rot[t] = 0;
-        if (t < 256) ss.hist[t] = 0;
-        for (int w = t; w < SEL_WORDS; w += S_NT) { ss.gt_bm[w] = 0u; ss.tie_bm[w] = 0u; }
+        ss.hist[t] = 0;
+#pragma unroll
+        for (int i = 0; i < S_WPT; ++i) ss.sel_bm[t * S_WPT + i] = 0u;
         if (staged) {
             if (t == 0) {
-                bulk_wait_read();                                     // the previous tile's codes have left shared memory
                 fence_async_smem();
-                mbar_arrive_expect_tx(&s_bar, (uint32_t)n * 2u + ((uint32_t)n >> 1));
-                bulk_g2s(st.tile, g, (uint32_t)n * 2u, &s_bar);
-                bulk_g2s(st.ef, ef_g, (uint32_t)n >> 1, &s_bar);
+                mbar_arrive_expect_tx(&s_bar, (uint32_t)n * 2u);
+                bulk_g2s(tile, g, (uint32_t)n * 2u, &s_bar);
             }
-            const int words = ((n_qb + skip) + 1) >> 1;
-            const uint32_t* mn_src = reinterpret_cast<const uint32_t*>(T.min_vals + qb0 - skip);
-            const uint32_t* mx_src = reinterpret_cast<const uint32_t*>(T.max_vals + qb0 - skip);
-            for (int i = t; i < words; i += S_NT) {
-                cp_async_4(reinterpret_cast<uint32_t*>(st.mn) + i, mn_src + i);
-                cp_async_4(reinterpret_cast<uint32_t*>(st.mx) + i, mx_src + i);
+        } else {
+            // ragged tile (a tensor's last block, or an unaligned buffer): plain loads, zero padded to whole octets
+            for (int i = t; i < n_oct * 8; i += S_NT) tile[i] = (i < n) ? g[i] : (uint16_t)0;
+        }
+        uint32_t cw[S_SLOTS];
+#pragma unroll
+        for (int j = 0; j < S_SLOTS; ++j) {
+            const int o = t + j * S_NT;
+            cw[j] = (o < n_oct) ? load_code_word(ef_in, ef_al4, o, n) : 0u;
+        }
+        if (tables) {
+            for (int b = t; b < n_qb; b += S_NT) {
+                const QParams q = qparams(mn_g[b], mx_g[b]);
+                ss.qt.mu[b] = make_float2(q.mn, q.u);
             }
-            cp_async_commit();
-            cp_async_wait_all();
+        }
+        if (staged) {
             const bool ok = mbar_wait(&s_bar, parity);
             parity ^= 1u;
             if (__syncthreads_or(!ok)) {
-                if (t == 0) { atomicExch(&g_copy_timeout_bf16, 1); bulk_wait_all(); }
+                if (t == 0) atomicExch(&g_copy_timeout_bf16, 1);
                 return;
             }
         } else {
-            // ragged tile (a tensor's last block, or unaligned buffers): plain loads, zero padded to whole octets
-            if (t == 0) bulk_wait_read();                             // the previous tile's codes have left shared memory
-            __syncthreads();
-            for (int i = t; i < n_oct * 8; i += S_NT) st.tile[i] = (i < n) ? g[i] : (uint16_t)0;
-            for (int i = t; i < n_oct; i += S_NT) {
-                uint32_t w = 0;
-                for (int b = 0; b < 4; ++b) if ((i * 8 + 2 * b) < n) w |= (uint32_t)ef_g[i * 4 + b] << (8 * b);
-                st.ef[i] = w;
-            }
-            for (int i = t; i < n_qb; i += S_NT) { st.mn[i + skip] = T.min_vals[qb0 + i]; st.mx[i + skip] = T.max_vals[qb0 + i]; }
             __syncthreads();
         }
         MAB_CTICK(0);
@@ -241,91 +334,40 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             const int64_t nn = min((int64_t)N.d_block_size, N.d - nbase);
             prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(N.grad) + nbase), nn * 2);
             prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.error + (nbase >> 1)), (nn + 1) >> 1);
+            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.min_vals + (nbase >> qshift)), ((nn >> qshift) + 1) * 2);
+            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.max_vals + (nbase >> qshift)), ((nn >> qshift) + 1) * 2);
         }
-        const uint16_t* s_mn = st.mn + skip;
-        const uint16_t* s_mx = st.mx + skip;
-        uint4* tile4 = reinterpret_cast<uint4*>(st.tile);
 
         // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
-        // register slot i of a thread: block t + (i >> cshift) * S_NT, chunk (i + lane) mod cpq of that block
-        float omax[8];
-        if (QB64 && staged) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) omax[i] = 0.0f;
-            if (t < n_qb) {
-                const QParams q = qparams(s_mn[t], s_mx[t]);
-                const DecodeConsts dc = decode_consts(q);
-                if (dc.fast) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) omax[i] = dequant_octet<true>(tile4, st.ef, (t << 3) + ((i + lane) & 7), q, dc);
-                } else {
-#pragma unroll 1
-                    for (int i = 0; i < 8; ++i) {
-                        const float m = dequant_octet<false>(tile4, st.ef, (t << 3) + ((i + lane) & 7), q, dc);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) if (j == i) omax[j] = m;
-                    }
-                }
-            }
-        } else {
-            QParams q = {0.f, 0.f};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                omax[i] = 0.0f;
-                const int b = t + (i >> cshift) * S_NT;
-                if (b < n_qb) {
-                    if ((i & (cpq - 1)) == 0) q = qparams(s_mn[b], s_mx[b]);
-                    const int o = (b << cshift) + ((i + lane) & (cpq - 1));
-                    if (o < n_oct) {
-                        float gv[8], x[8];
-                        unpack8(tile4[o], gv);
-                        decode_octet(st.ef[o], q, x);
-                        uint4 out;
-                        uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
-                        uint32_t m2 = 0u;                                     // packed running max of |a|
-#pragma unroll
-                        for (int p = 0; p < 4; ++p) {
-                            const float2 s = __fadd2_rn(make_float2(gv[2 * p], gv[2 * p + 1]), make_float2(x[2 * p], x[2 * p + 1]));
-                            uint32_t w = pack_bf16x2_rne(s.x, s.y);
-                            if (!staged) {                                    // padding of a ragged tile stays zero
-                                const int e0 = o * 8 + 2 * p;
-                                if (e0 + 1 >= n) w = (e0 >= n) ? 0u : (w & 0xFFFFu);
-                            }
-                            ow[p] = w;
-                            m2 = max_bf16x2(m2, abs_bf16x2(w));
-                        }
-                        const float m = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xFFFF0000u));
-                        tile4[o] = out;
-                        omax[i] = m;
-                    }
-                }
-            }
-        }
+        float omax[S_SLOTS];
+        if (tables && (n & 7) == 0 && n_oct >= S_FULL * S_NT) dequant_phase<S_FULL>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax);
+        else dequant_phase<0>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax);
 
         MAB_CTICK(1);
         // ---- exact top-k ---------------------------------------------------------------------------
         {
             float tm = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) tm = fmaxf(tm, omax[i]);
+            for (int j = 0; j < S_SLOTS; ++j) tm = fmaxf(tm, omax[j]);
             const int wm = __reduce_max_sync(0xffffffffu, __float_as_int(tm));
             if (lane == 0 && wm) atomicMax(&ss.kmax, wm);
         }
         __syncthreads();
         const int kmax = ss.kmax;
         bool done = false;
-        int C = 0;
+        int C = -1;                                          // >= 0: the selection is described by the candidate list
         uint32_t Tc_sel = 0;
         if (kmax == 0) {
             // every key is zero: the k lowest positions win the ties
-            for (int w = t; w < SEL_WORDS; w += S_NT) {
-                const int lo = w * 32;
-                ss.gt_bm[w] = (lo + 32 <= k) ? 0xFFFFFFFFu : (lo < k ? ((1u << (k - lo)) - 1u) : 0u);
-                ss.tie_bm[w] = 0u;
+            uint32_t gt[S_WPT], tw[S_WPT];
+#pragma unroll
+            for (int i = 0; i < S_WPT; ++i) {
+                const int lo = (t * S_WPT + i) * 32;
+                gt[i] = (lo + 32 <= k) ? 0xFFFFFFFFu : (lo < k ? ((1u << (k - lo)) - 1u) : 0u);
+                tw[i] = 0u;
             }
-            resolve_selection_smem(0, ss);
+            resolve_selection_regs(gt, tw, 0, ss);
             done = true;
-            C = -1;                                          // values (all zero) are taken from the tile below
         }
         if (!done && kmax < 0x7f800000 && k <= n_oct) {
             // lower bound of the k-th key on octet maxima: at least k octets reach it, at most ~1.5 k
@@ -336,7 +378,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             for (int it = 0; it < 64; ++it) {
                 int mine = 0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mine += (__float_as_int(omax[i]) >= gq) ? 1 : 0;
+                for (int j = 0; j < S_SLOTS; ++j) mine += (__float_as_int(omax[j]) >= gq) ? 1 : 0;
                 mine = __reduce_add_sync(0xffffffffu, mine);
                 if (lane == 0 && mine) atomicAdd(&ss.rot[it], mine);
                 __syncthreads();
@@ -349,119 +391,129 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 else { gq = (int)max((int64_t)hi - step, (int64_t)1); step <<= 1; }
             }
             guess = lo;
+            MAB_CTICK(8);
             const int T_lo = have_lo ? lo : 0;
             if (T_lo > 0) {
                 const float T_lo_f = __int_as_float(T_lo);
                 const uint32_t T16 = ((uint32_t)T_lo + 0xFFFFu) >> 16;          // the bound as a bf16 magnitude
-                // 1. octets whose maximum reaches the bound -> list (any order)
-                int mine = 0;
+                // 1. each warp lists its octets whose maximum reaches the bound and turns their values that
+                //    reach it into candidates (any order)
+                uint16_t* wlist = ss.oct_list + warp * S_WLIST;
+                int n_w = 0;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mine += (omax[i] >= T_lo_f) ? 1 : 0;
-                int at = warp_alloc(mine, &ss.n_list);
+                for (int j = 0; j < S_SLOTS; ++j) {
+                    const bool q = omax[j] >= T_lo_f;
+                    const unsigned bal = __ballot_sync(0xffffffffu, q);
+                    const int at = n_w + __popc(bal & ((1u << lane) - 1u));
+                    if (q && at < S_WLIST) wlist[at] = (uint16_t)(t + j * S_NT);
+                    n_w += __popc(bal);
+                }
+                if (lane == 0 && n_w > S_WLIST) ss.ctrl[4] = 1;
+                n_w = min(n_w, S_WLIST);
+                __syncwarp();
+                for (int e0 = 0; e0 < n_w; e0 += 32) {
+                    const int e = e0 + lane;
+                    uint32_t o = 0, mask = 0;
+                    if (e < n_w) {
+                        o = wlist[e];
+                        const uint4 v = tile4[o];
+                        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (omax[i] >= T_lo_f) {
-                        if (at < S_OCT_CAP) ss.oct_list[at] = (uint16_t)(((t + (i >> cshift) * S_NT) << cshift) + ((i + lane) & (cpq - 1)));
-                        ++at;
+                        for (int p = 0; p < 4; ++p) {
+                            mask |= ((w[p] & 0x7FFFu) >= T16) ? (1u << (2 * p)) : 0u;
+                            mask |= (((w[p] >> 16) & 0x7FFFu) >= T16) ? (2u << (2 * p)) : 0u;
+                        }
                     }
+                    int slot = warp_alloc(__popc(mask), &ss.n_cand);
+                    while (mask) {
+                        const uint32_t pos = (o << 3) + (__ffs(mask) - 1);
+                        mask &= mask - 1;
+                        if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(tile[pos] & 0x7FFFu) << 16) | (0xFFFFu - pos);
+                        ++slot;
+                    }
+                }
                 __syncthreads();
-                const int n_list = ss.n_list;
-                if (n_list <= S_OCT_CAP) {
-                    // 2. their values that reach the bound -> candidates (any order)
-                    for (int i0 = 0; i0 < n_list; i0 += S_NT) {
-                        const int i = i0 + t;
-                        uint32_t o = 0, mask = 0;
-                        if (i < n_list) {
-                            o = ss.oct_list[i];
-                            const uint4 v = tile4[o];
-                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                MAB_CTICK(10);
+                const int n_cand = ss.n_cand;
+                if (n_cand <= S_CAND_CAP && ss.ctrl[4] == 0) {
+                    C = n_cand;
+                    // 2. the k-th largest candidate.  The composite values are distinct, so no ties are left to
+                    //    break.  256-bin radix levels over the live range, filled by all threads; every warp
+                    //    reads the histogram for itself (no barrier for the result); the last <= 32 members
+                    //    are gathered and ranked directly, again by every warp for itself.
+                    {
+                        uint32_t lo_c = T16 << 16, hi_c = ((uint32_t)kmax & 0xFFFF0000u) | 0xFFFFu;
+                        int k_rem = k;
+                        for (int level = 0; level < 6; ++level) {
+                            const uint32_t W1 = hi_c - lo_c;
+                            const int sh = W1 < 256u ? 0 : (32 - __clz(W1)) - 8;
+                            if (level > 0) {
+                                __syncthreads();
+                                ss.hist[t] = 0;
+                                __syncthreads();
+                            }
+                            for (int i = t; i < C; i += S_NT) {
+                                const uint32_t c = ss.cand[i];
+                                if (c >= lo_c && c <= hi_c) atomicAdd(&ss.hist[(c - lo_c) >> sh], 1);
+                            }
+                            __syncthreads();
+                            int h[8], sum = 0;
+                            {
+                                const int4 ha = reinterpret_cast<const int4*>(ss.hist)[lane * 2], hb4 = reinterpret_cast<const int4*>(ss.hist)[lane * 2 + 1];
+                                h[0] = ha.x; h[1] = ha.y; h[2] = ha.z; h[3] = ha.w; h[4] = hb4.x; h[5] = hb4.y; h[6] = hb4.z; h[7] = hb4.w;
+                            }
 #pragma unroll
-                            for (int p = 0; p < 4; ++p) {
-                                mask |= ((w[p] & 0x7FFFu) >= T16) ? (1u << (2 * p)) : 0u;
-                                mask |= (((w[p] >> 16) & 0x7FFFu) >= T16) ? (2u << (2 * p)) : 0u;
+                            for (int j = 0; j < 8; ++j) sum += h[j];
+                            int suf = sum;
+#pragma unroll
+                            for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_down_sync(0xffffffffu, suf, d); if (lane + d < 32) suf += v; }
+                            const unsigned okm = __ballot_sync(0xffffffffu, suf >= k_rem);
+                            const int owner = 31 - __clz(okm);
+                            int above = suf - sum, bsel = 7;
+#pragma unroll
+                            for (int j = 7; j >= 0; --j) if (bsel == j && above + h[j] < k_rem) { above += h[j]; bsel = j - 1; }
+                            int hb = 0;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) if (j == bsel) hb = h[j];
+                            const int b_star = __shfl_sync(0xffffffffu, lane * 8 + bsel, owner);
+                            k_rem -= __shfl_sync(0xffffffffu, above, owner);
+                            hb = __shfl_sync(0xffffffffu, hb, owner);
+                            lo_c += (uint32_t)b_star << sh;
+                            hi_c = min(hi_c, lo_c + ((1u << sh) - 1u));
+                            if (sh == 0) { Tc_sel = lo_c; break; }
+                            if (hb <= 32) {
+                                for (int i = t; i < C; i += S_NT) {
+                                    const uint32_t c = ss.cand[i];
+                                    if (c >= lo_c && c <= hi_c) ss.member[atomicAdd(&ss.n_member, 1)] = c;
+                                }
+                                __syncthreads();
+                                const uint32_t me = lane < hb ? ss.member[lane] : 0u;
+                                int greater = 0;
+                                for (int j = 0; j < hb; ++j) greater += (ss.member[j] > me) ? 1 : 0;
+                                const unsigned hit = __ballot_sync(0xffffffffu, lane < hb && greater == k_rem - 1);
+                                Tc_sel = __shfl_sync(0xffffffffu, me, __ffs(hit) - 1);
+                                break;
                             }
                         }
-                        int slot = warp_alloc(__popc(mask), &ss.n_cand);
-                        while (mask) {
-                            const uint32_t pos = (o << 3) + (__ffs(mask) - 1);
-                            mask &= mask - 1;
-                            if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(st.tile[pos] & 0x7FFFu) << 16) | (0xFFFFu - pos);
-                            ++slot;
-                        }
+                    }
+                    MAB_CTICK(11);
+                    // 3. selected positions -> bitmap -> ranks
+                    for (int i = t; i < C; i += S_NT) {
+                        const uint32_t c = ss.cand[i];
+                        if (c >= Tc_sel) { const uint32_t pos = 0xFFFFu - (c & 0xFFFFu); atomicOr(&ss.sel_bm[pos >> 5], 1u << (pos & 31)); }
                     }
                     __syncthreads();
-                    C = ss.n_cand;
-                    if (C <= S_CAND_CAP) {
-                        // 3. one warp finds the k-th largest candidate (the composite values are distinct, so
-                        //    there are no ties left to break): 256-bin radix levels over the live range, the
-                        //    last <= 32 members ranked directly
-                        if (warp == S_NT / 32 - 1) {
-                            uint32_t lo_c = T16 << 16, hi_c = ((uint32_t)kmax & 0xFFFF0000u) | 0xFFFFu, Tc = 0;
-                            int k_rem = k;
-                            for (int level = 0; level < 6; ++level) {
-                                const uint32_t W1 = hi_c - lo_c;
-                                const int sh = W1 < 256u ? 0 : (32 - __clz(W1)) - 8;
-                                if (level > 0) {
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) ss.hist[lane * 8 + j] = 0;
-                                    __syncwarp();
-                                }
-                                for (int i = lane; i < C; i += 32) {
-                                    const uint32_t c = ss.cand[i];
-                                    if (c >= lo_c && c <= hi_c) atomicAdd(&ss.hist[(c - lo_c) >> sh], 1);
-                                }
-                                __syncwarp();
-                                int h[8], sum = 0;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) { h[j] = ss.hist[lane * 8 + j]; sum += h[j]; }
-                                int suf = sum;
-#pragma unroll
-                                for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_down_sync(0xffffffffu, suf, d); if (lane + d < 32) suf += v; }
-                                const unsigned okm = __ballot_sync(0xffffffffu, suf >= k_rem);
-                                const int owner = 31 - __clz(okm);
-                                int above = suf - sum, bsel = 7;
-#pragma unroll
-                                for (int j = 7; j >= 0; --j) if (bsel == j && above + h[j] < k_rem) { above += h[j]; bsel = j - 1; }
-                                int hb = 0;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) if (j == bsel) hb = h[j];
-                                const int b_star = __shfl_sync(0xffffffffu, lane * 8 + bsel, owner);
-                                k_rem -= __shfl_sync(0xffffffffu, above, owner);
-                                hb = __shfl_sync(0xffffffffu, hb, owner);
-                                lo_c += (uint32_t)b_star << sh;
-                                hi_c = min(hi_c, lo_c + ((1u << sh) - 1u));
-                                if (sh == 0) { Tc = lo_c; break; }
-                                if (hb <= 32) {
-                                    int base = 0;
-                                    for (int i0 = 0; i0 < C; i0 += 32) {
-                                        const int i = i0 + lane;
-                                        const uint32_t c = i < C ? ss.cand[i] : 0u;
-                                        const bool in = c >= lo_c && c <= hi_c;
-                                        const unsigned bal = __ballot_sync(0xffffffffu, in);
-                                        if (in) ss.member[base + __popc(bal & ((1u << lane) - 1u))] = c;
-                                        base += __popc(bal);
-                                    }
-                                    __syncwarp();
-                                    const uint32_t me = lane < base ? ss.member[lane] : 0u;
-                                    int greater = 0;
-                                    for (int j = 0; j < base; ++j) greater += (__shfl_sync(0xffffffffu, me, j) > me) ? 1 : 0;
-                                    const unsigned hit = __ballot_sync(0xffffffffu, lane < base && greater == k_rem - 1);
-                                    Tc = __shfl_sync(0xffffffffu, me, __ffs(hit) - 1);
-                                    break;
-                                }
-                            }
-                            if (lane == 0) ss.ctrl[3] = (int)Tc;
-                        }
-                        __syncthreads();
-                        Tc_sel = (uint32_t)ss.ctrl[3];
-                        // 4. selected positions -> bitmap -> ranks
-                        for (int i = t; i < C; i += S_NT) {
-                            const uint32_t c = ss.cand[i];
-                            if (c >= Tc_sel) { const uint32_t pos = 0xFFFFu - (c & 0xFFFFu); atomicOr(&ss.gt_bm[pos >> 5], 1u << (pos & 31)); }
-                        }
-                        resolve_selection_smem(0, ss);
-                        done = true;
+                    {
+                        const uint4 wq = reinterpret_cast<const uint4*>(ss.sel_bm)[t];
+                        const int c0 = __popc(wq.x), c1 = __popc(wq.y), c2 = __popc(wq.z), c3 = __popc(wq.w);
+                        int total;
+                        const int before = block_exclusive_scan(c0 + c1 + c2 + c3, ss.scan, total);
+                        ushort4 sb;
+                        sb.x = (uint16_t)before; sb.y = (uint16_t)(before + c0); sb.z = (uint16_t)(before + c0 + c1); sb.w = (uint16_t)(before + c0 + c1 + c2);
+                        reinterpret_cast<ushort4*>(ss.sel_before)[t] = sb;
                     }
+                    __syncthreads();
+                    done = true;
                 }
             }
         }
@@ -478,28 +530,31 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             int Tk = 0;
             for (int bit = 30; bit >= 16; --bit) {          // bf16 keys have 16 zero bits below
                 const int cand = Tk | (1 << bit);
-                if (tile_count_ge(st.tile, n_oct, cand, &ss.counters[bit]) >= k) Tk = cand;
+                if (tile_count_ge(tile, n_oct, cand, &ss.counters[bit]) >= k) Tk = cand;
             }
-            const int n_gt = tile_count_ge(st.tile, n_oct, Tk + 0x10000, &ss.counters[32]);
+            const int n_gt = tile_count_ge(tile, n_oct, Tk + 0x10000, &ss.counters[32]);
             const int need = k - n_gt;
             const float Tf = __int_as_float(Tk);
-            uint8_t* gtb = reinterpret_cast<uint8_t*>(ss.gt_bm);
-            uint8_t* tieb = reinterpret_cast<uint8_t*>(ss.tie_bm);
-            for (int o = t; o < SEL_WORDS * 4; o += S_NT) {
-                uint32_t gm = 0, tm = 0;
-                if (o < n_oct) {
-                    float v[8];
-                    unpack8(tile4[o], v);
+            uint32_t gt[S_WPT], tw[S_WPT];                  // the thread's 128 positions = 16 octets
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const bool valid = o * 8 + e < n;     // padding never competes, whatever the threshold
-                        gm |= (valid && fabsf(v[e]) > Tf) ? (1u << e) : 0u;
-                        tm |= (valid && fabsf(v[e]) == Tf) ? (1u << e) : 0u;
+            for (int i = 0; i < S_WPT; ++i) {
+                gt[i] = 0u; tw[i] = 0u;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int o = (t * S_WPT + i) * 4 + b;
+                    if (o < n_oct) {
+                        float v[8];
+                        unpack8(tile4[o], v);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const bool valid = o * 8 + e < n;     // padding never competes, whatever the threshold
+                            gt[i] |= (valid && fabsf(v[e]) > Tf) ? (1u << (8 * b + e)) : 0u;
+                            tw[i] |= (valid && fabsf(v[e]) == Tf) ? (1u << (8 * b + e)) : 0u;
+                        }
                     }
                 }
-                gtb[o] = (uint8_t)gm; tieb[o] = (uint8_t)tm;
             }
-            resolve_selection_smem(need, ss);
+            resolve_selection_regs(gt, tw, need, ss);
         }
 
         MAB_CTICK(3);
@@ -511,8 +566,8 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                     const uint32_t q = 0xFFFFu - (c & 0xFFFFu), w = q >> 5;
                     const int rank = ss.sel_before[w] + __popc(ss.sel_bm[w] & ((1u << (q & 31)) - 1u));
                     i_out[rank] = (int16_t)q;
-                    v_out[rank] = st.tile[q];
-                    st.tile[q] = 0;
+                    v_out[rank] = tile[q];
+                    tile[q] = 0;
                 }
             }
         } else {
@@ -526,135 +581,107 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                     sel &= sel - 1;
                     const int q = (w0 + i) * 32 + b;
                     i_out[p] = (int16_t)q;
-                    v_out[p++] = st.tile[q];
-                    st.tile[q] = 0;
+                    v_out[p++] = tile[q];
+                    tile[q] = 0;
                 }
             }
         }
         __syncthreads();
 
         MAB_CTICK(4);
-        // ---- statistics and codes of the residual, one thread per quantisation block --------------------
+        // ---- statistics and codes of the residual ----------------------------------------------------------
         uint16_t* mn_out = T.min_vals + qb0;
         uint16_t* mx_out = T.max_vals + qb0;
-        if (QB64 && staged) {
-            if (t < n_qb) {
-                uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;
+        if (tables && (n & 63) == 0) {
+            // whole blocks of 64: statistics block by block (a thread's 8 octets, rotated so that a warp's
+            // 16-byte reads spread over the banks), constants to the tables, then codes octet by octet
+            for (int b = t; b < n_qb; b += S_NT) {
+                uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;  // running packed max (from -inf) and min (from +inf)
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint4 v = tile4[(t << 3) + ((c + lane) & 7)];
+                    const uint4 v = tile4[(b << 3) + ((c + lane) & 7)];
                     hi2 = max_bf16x2(max_bf16x2(hi2, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
                     lo2 = min_bf16x2(min_bf16x2(lo2, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
                 }
                 hi2 = max_bf16x2(hi2, hi2 >> 16);
                 lo2 = min_bf16x2(lo2, lo2 >> 16);
                 const uint16_t mn_b = (uint16_t)(lo2 & 0xFFFFu), mx_b = (uint16_t)(hi2 & 0xFFFFu);
-                mn_out[t] = mn_b; mx_out[t] = mx_b;
+                mn_out[b] = mn_b; mx_out[b] = mx_b;
                 const QParams q2 = qparams(mn_b, mx_b);
                 const EncodeConsts ec = encode_consts(q2);
-                if (ec.fast) {
-                    uint32_t redo = 0u;                                   // octets with a value too close to a code boundary
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int o = (t << 3) + ((c + lane) & 7);
-                        float r[8], worst;
-                        unpack8(tile4[o], r);
-                        st.ef[o] = encode_octet_speculative<false>(r, ec, worst);   // exact statistics of bf16 values: no clamp needed
-                        redo |= (worst > CODEC_SAFE_FRAC) ? (1u << c) : 0u;
-                    }
-                    while (redo) {
-                        const int c = __ffs(redo) - 1;
-                        redo &= redo - 1;
-                        const int o = (t << 3) + ((c + lane) & 7);
-                        float r[8];
-                        unpack8(tile4[o], r);
-                        st.ef[o] = encode_octet_fast<false>(r, q2, ec);
-                    }
-                } else {
-#pragma unroll 1
-                    for (int c = 0; c < 8; ++c) {
-                        const int o = (t << 3) + ((c + lane) & 7);
-                        float r[8];
-                        unpack8(tile4[o], r);
-                        st.ef[o] = encode_octet_exact(r, q2, 8);
-                    }
-                }
+                ss.qt.mu[b] = make_float2(q2.mn, q2.u);
+                ss.qt.r0[b] = ec.fast ? ec.r02.x : 0.0f;
             }
-        } else
-        for (int b = t; b < n_qb; b += S_NT) {
-            uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;  // running packed max (from -inf) and min (from +inf)
-            const int o_first = b << cshift;
-            for (int c = 0; c < cpq; ++c) {
-                const int o = o_first + ((c + lane) & (cpq - 1));
-                if (o < n_oct) {
-                    const uint4 v = tile4[o];
-                    const int cnt = n - o * 8;
-                    if (cnt >= 8) {
-                        hi2 = max_bf16x2(max_bf16x2(hi2, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
-                        lo2 = min_bf16x2(min_bf16x2(lo2, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
-                    } else {                                   // the tensor's last, short octet: valid elements only
-                        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                        for (int e = 0; e < cnt; ++e) {
-                            const uint32_t x = (w[e >> 1] >> (16 * (e & 1))) & 0xFFFFu;
-                            hi2 = max_bf16x2(hi2, x | (x << 16));
-                            lo2 = min_bf16x2(lo2, x | (x << 16));
+            __syncthreads();
+            uint32_t redo = 0u;                              // octets too close to a code boundary, or of a degenerate block
+            if ((n & 7) == 0 && n_oct >= S_FULL * S_NT && ef_al4) encode_phase<S_FULL>(tile4, ss, ef_out, ef_al4, n, n_oct, redo);
+            else encode_phase<0>(tile4, ss, ef_out, ef_al4, n, n_oct, redo);
+            while (redo) {
+                const int j = __ffs(redo) - 1;
+                redo &= redo - 1;
+                const int o = t + j * S_NT;
+                const float2 mu = ss.qt.mu[o >> 3];
+                const QParams q2 = {mu.x, mu.y};
+                float r[8];
+                unpack8(tile4[o], r);
+                store_code_word(ef_out, ef_al4, o, n, encode_octet<false>(r, q2));
+            }
+            __syncthreads();                                 // the tile is overwritten by the next load
+        } else {
+            // any block size, ragged ends: one thread per quantisation block
+            for (int b = t; b < n_qb; b += S_NT) {
+                uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;
+                const int o_first = b << cshift;
+                for (int c = 0; c < cpq; ++c) {
+                    const int o = o_first + ((c + lane) & (cpq - 1));
+                    if (o < n_oct) {
+                        const uint4 v = tile4[o];
+                        const int cnt = n - o * 8;
+                        if (cnt >= 8) {
+                            hi2 = max_bf16x2(max_bf16x2(hi2, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
+                            lo2 = min_bf16x2(min_bf16x2(lo2, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
+                        } else {                                   // the tensor's last, short octet: valid elements only
+                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                            for (int e = 0; e < cnt; ++e) {
+                                const uint32_t x = (w[e >> 1] >> (16 * (e & 1))) & 0xFFFFu;
+                                hi2 = max_bf16x2(hi2, x | (x << 16));
+                                lo2 = min_bf16x2(lo2, x | (x << 16));
+                            }
                         }
                     }
                 }
-            }
-            hi2 = max_bf16x2(hi2, hi2 >> 16 | hi2 << 16);
-            lo2 = min_bf16x2(lo2, lo2 >> 16 | lo2 << 16);
-            const uint16_t mn_b = (uint16_t)(lo2 & 0xFFFFu), mx_b = (uint16_t)(hi2 & 0xFFFFu);
-            mn_out[b] = mn_b; mx_out[b] = mx_b;
-            const QParams q2 = qparams(mn_b, mx_b);
-            for (int c = 0; c < cpq; ++c) {
-                const int o = o_first + ((c + lane) & (cpq - 1));
-                if (o < n_oct) {
-                    float r[8];
-                    unpack8(tile4[o], r);
-                    const int cnt = n - o * 8;
-                    // bf16 values: the statistics are their exact minimum and maximum, no clamp needed
-                    st.ef[o] = cnt >= 8 ? encode_octet<false>(r, q2) : encode_octet_exact(r, q2, cnt);
+                hi2 = max_bf16x2(hi2, hi2 >> 16 | hi2 << 16);
+                lo2 = min_bf16x2(lo2, lo2 >> 16 | lo2 << 16);
+                const uint16_t mn_b = (uint16_t)(lo2 & 0xFFFFu), mx_b = (uint16_t)(hi2 & 0xFFFFu);
+                mn_out[b] = mn_b; mx_out[b] = mx_b;
+                const QParams q2 = qparams(mn_b, mx_b);
+                for (int c = 0; c < cpq; ++c) {
+                    const int o = o_first + ((c + lane) & (cpq - 1));
+                    if (o < n_oct) {
+                        float r[8];
+                        unpack8(tile4[o], r);
+                        const int cnt = n - o * 8;
+                        // bf16 values: the statistics are their exact minimum and maximum, no clamp needed
+                        store_code_word(ef_out, ef_al4, o, n, cnt >= 8 ? encode_octet<false>(r, q2) : encode_octet_exact(r, q2, cnt));
+                    }
                 }
             }
+            __syncthreads();                                 // the tile is overwritten by the next load
         }
-        uint8_t* ef_out = T.error + (base >> 1);
-        if (staged) {
-            // codes out through the copy engine; the wait sits before the next tile's load
-            fence_async_smem();
-            __syncthreads();
-            MAB_CTICK(5);
-            if (t == 0) bulk_s2g(ef_out, st.ef, (uint32_t)n >> 1);
-            MAB_CTICK(6);
-#ifdef MAB_STATS
-            if (threadIdx.x == 0) atomicAdd(&g_stats_c[15], 1ull);
-#endif
-            continue;
-        }
-        __syncthreads();
         MAB_CTICK(5);
-        // codes out: whole words coalesced, the ragged end byte by byte
-        const int full_words = ((reinterpret_cast<uintptr_t>(ef_out) & 3) == 0) ? (n >> 3) : 0;
-        for (int i = t; i < full_words; i += S_NT) reinterpret_cast<uint32_t*>(ef_out)[i] = st.ef[i];
-        for (int i = full_words + t; i < n_oct; i += S_NT) {
-            const uint32_t w = st.ef[i];
-            for (int b = 0; b < 4; ++b) if (i * 8 + 2 * b < n) ef_out[i * 4 + b] = (uint8_t)(w >> (8 * b));
-        }
-        __syncthreads();                                     // the staging area is overwritten by the next tile
-        MAB_CTICK(6);
 #ifdef MAB_STATS
         if (threadIdx.x == 0) atomicAdd(&g_stats_c[15], 1ull);
 #endif
     }
-    if (t == 0) bulk_wait_all();
 }
 
 int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s) {
     int qshift = 0;
     while ((1 << qshift) < qbs) ++qshift;
-    const int smem = BfStage::bytes(max_dbs, qshift) + (int)sizeof(SmemSel);
-    if (2 * (smem + 3 * 1024) > device_max_optin_smem() + 1024) return 1;       // two CTAs per SM do not fit: caller uses the other kernel
-    const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count() * 2);
+    const int smem = ((max_dbs * 2 + 127) & ~127) + (int)sizeof(SmemSel);
+    const int per_sm = std::min(S_CTAS, (device_max_optin_smem() + 1024) / (smem + 3 * 1024 + 128));
+    if (per_sm < 2) return 1;                                // not even two CTAs per SM: the caller uses the other kernel
+    const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count() * per_sm);
     if (qshift == 6) {
         MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         ef_topk_quant_bf16_kernel<true><<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
