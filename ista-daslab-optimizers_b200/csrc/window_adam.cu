@@ -353,12 +353,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         const int64_t blk_base = (int64_t)blk * dbs;
         const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
         if (MODE == MODE_STEP) {
-            // this block's parameters travel to L2 while the window is worked on (asked for any earlier,
-            // other CTAs' traffic pushes them out again before they are used); the next unit's window
-            // rows are small and are asked for now
-#ifndef MAB_X_NOPF
-            prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
-#endif
+            // the next unit's window rows are small and are asked into L2 now
             if (unit + (int)gridDim.x < total_units) {
                 const int nu = unit + gridDim.x;
                 const int nti = find_tensor(s_first, n_tensors, nu);
@@ -404,6 +399,10 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        // this block's parameters travel to L2 while the window is worked on, behind the window rows
+        // (asked for any earlier, other CTAs' traffic pushes them out again before they are used)
+        if (MODE == MODE_STEP)
+            prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
         for (int i = t; i < WT_WORDS; i += WT_THREADS) bitmap[i] = 0u;
         for (int i = t; i < E; i += WT_THREADS) mv[i] = make_float2(0.0f, 0.0f);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
