@@ -215,6 +215,8 @@ def main():
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--seed', type=int, default=0)
+    ap.add_argument('--exchange', default='rows', choices=['rows', 'params'],
+                    help='N > 1: what the ranks exchange (window rows, or updated parameters)')
     args = ap.parse_args()
     spec = workload_spec(args.workload)
     if args.impl == 'reference':
@@ -243,7 +245,8 @@ def main():
     n_params = sum(p.numel() for p in params)
     kw = dict(m=HYPER['m'], lr=HYPER['lr'], quant_block_size=HYPER['quant_block_size'], k_init=HYPER['k_init'],
               alpha=HYPER['alpha'], betas=HYPER['betas'], weight_decay=spec['weight_decay'], eps=HYPER['eps'])
-    opt = ShardedMicroAdam(params, **kw) if world > 1 else MicroAdam(params, **kw)
+    exchange = args.exchange if (world > 1 and HYPER['alpha'] == 0) else 'params'
+    opt = ShardedMicroAdam(params, exchange=exchange, **kw) if world > 1 else MicroAdam(params, **kw)
 
     def set_grads(t):
         for p, g in zip(params, grad_sets[t % len(grad_sets)][1]):
@@ -280,6 +283,9 @@ def main():
     calls = [ev for ev in events if isinstance(ev, list)]            # one per fused call (several per step when overlapped)
     t_a = sum(ev[0].elapsed_time(ev[1]) for ev in calls) / steps
     t_b = sum(ev[1].elapsed_time(ev[2]) for ev in calls) / steps
+    rows_calls = [ev[1] for ev in events if isinstance(ev, tuple) and ev[0] == 'rows']   # [start, after A, after exchange, after B]
+    t_a += sum(ev[0].elapsed_time(ev[1]) for ev in rows_calls) / steps
+    t_b += sum(ev[2].elapsed_time(ev[3]) for ev in rows_calls) / steps
     # exchange time that is not hidden behind the kernels: step time minus kernel time
     t_gather = max(0.0, elapsed_ms / steps - t_a - t_b) if world > 1 else 0.0
     stats = torch.tensor([elapsed_ms, t_a, t_b, t_gather], dtype=torch.float64, device=device)
@@ -333,21 +339,23 @@ def main():
     rows_avg = sum(rows_per_step) / len(rows_per_step)
     ba, bb = algorithmic_bytes_per_param(spec['dtype'], rows_avg)
     per_rank_params = n_params / world
+    # parameters one rank's launch of each kernel covers: kernel B runs over all of them when window rows are exchanged
+    params_a, params_b = per_rank_params, (n_params if exchange == 'rows' else per_rank_params)
     dt = 'bf16' if spec['dtype'] == torch.bfloat16 else 'f32'
     kernels = []
-    for name, b, ms in (('ef_topk_quant', ba, t_a), ('window_adam', bb, t_b)):
-        gbs = per_rank_params * b / (ms * 1e-3) / 1e9
+    for name, b, ms, np_k in (('ef_topk_quant', ba, t_a, params_a), ('window_adam', bb, t_b, params_b)):
+        gbs = np_k * b / (ms * 1e-3) / 1e9
         tr = NCU_TRAFFIC_BYTES_PER_PARAM.get((name, dt))
-        kernels.append({'kernel': name, 'ms': ms, 'algorithmic_bytes': per_rank_params * b, 'achieved_gbs': gbs,
-                        'frac': gbs / peak, 'traffic': None if tr is None else tr * per_rank_params})
+        kernels.append({'kernel': name, 'ms': ms, 'algorithmic_bytes': np_k * b, 'achieved_gbs': gbs,
+                        'frac': gbs / peak, 'traffic': None if tr is None else tr * np_k})
     dom = max(kernels, key=lambda k: k['ms'])
-    step_gbs = per_rank_params * (ba + bb) / ((t_a + t_b) * 1e-3) / 1e9
+    step_gbs = (params_a * ba + params_b * bb) / ((t_a + t_b) * 1e-3) / 1e9
 
     line = {
         'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': steps, 'warmup': warmup,
         'ms_per_step': elapsed_ms / steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
         'dtype': dt, 'data': 'synthetic',
-        'config': {'workload': spec['label'], 'params': n_params, 'parallelism': f'zero1-shard{world}+allgather' if world > 1 else 'single',
+        'config': {'workload': spec['label'], 'params': n_params, 'parallelism': (f'shard{world}: kernel A sharded, window rows exchanged, kernel B replicated' if exchange == 'rows' else f'zero1-shard{world}+allgather') if world > 1 else 'single',
                    'l2_policy': 'inputs larger than L2 (GBs per step vs 126 MB)', 'grad_sets': len(grad_sets),
                    'arithmetic': 'fp32 on bf16/fp32 storage, 4-bit codes', **{k: v for k, v in HYPER.items() if k != 'betas'},
                    'weight_decay': spec['weight_decay']},

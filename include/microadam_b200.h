@@ -126,7 +126,8 @@ typedef struct mab_tensor {
     int32_t   param_dtype;
     int32_t   grad_dtype;
     int32_t   ring_index;        /* st['index']: row of I, V written this step                  */
-    int32_t   reserved0;
+    int32_t   row_pitch;         /* elements between consecutive rows of I and of V; 0 = k (rows of
+                                    several tensors side by side in one buffer have a larger pitch) */
     double    lr;                /* group['lr'] of this step                                    */
     double    weight_decay;      /* group['weight_decay'] of this step                          */
     /* filled in by the library */

@@ -88,6 +88,7 @@ static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
     if (t->k_block_size_many < 1 || t->k_block_size_many > t->d_block_size) return "k_block_size_many out of range";
     if ((covered < t->d) != (t->k_block_size_few > 0) || t->k_block_size_few > t->d - covered) return "k_block_size_few out of range";
     if (t->k != nfull * t->k_block_size_many + t->k_block_size_few) return "k inconsistent with the block geometry";
+    if (t->row_pitch != 0 && t->row_pitch < t->k) return "row_pitch smaller than k";
     if (nfull + 1 >= (int64_t)1 << 28) return "too many blocks";
     if (t->ring_index < 0 || t->ring_index >= a->m) return "ring_index outside [0, m)";
     const size_t pe = t->param_dtype == MAB_F32 ? 4 : 2, ge = t->grad_dtype == MAB_F32 ? 4 : 2;

@@ -256,7 +256,7 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
 
         MAB_TICK(11);
         // ---- exact top-k ---------------------------------------------------------------------
-        const int64_t row_off = (int64_t)T.ring_index * T.k + (int64_t)blk * T.k_block_size_many;
+        const int64_t row_off = (int64_t)T.ring_index * row_pitch_of(T) + (int64_t)blk * T.k_block_size_many;
         uint16_t* v_out = T.V + row_off;
         int n_cand = 0;
         int oct_slot[SEL_OCTETS];

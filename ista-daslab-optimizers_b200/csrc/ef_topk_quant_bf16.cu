@@ -518,7 +518,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             }
         }
         MAB_CTICK(2);
-        const int64_t row_off = (int64_t)T.ring_index * T.k + (int64_t)blk * T.k_block_size_many;
+        const int64_t row_off = (int64_t)T.ring_index * row_pitch_of(T) + (int64_t)blk * T.k_block_size_many;
         int16_t* i_out = T.I + row_off;
         uint16_t* v_out = T.V + row_off;
         if (!done) {

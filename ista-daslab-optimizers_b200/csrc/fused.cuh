@@ -7,6 +7,9 @@ namespace mab {
 
 __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Elements between consecutive rows of a tensor's I and V.
+__host__ __device__ __forceinline__ int64_t row_pitch_of(const mab_tensor& t) { return t.row_pitch > 0 ? (int64_t)t.row_pitch : t.k; }
+
 // Index of the tensor whose unit range contains `unit`: largest i with first[i] <= unit.
 // first[0..n] is ascending with first[n] = total units; tensors without units repeat a value.
 __device__ __forceinline__ int find_tensor(const int* first, int n, int unit) {

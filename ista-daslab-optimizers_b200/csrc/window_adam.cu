@@ -362,7 +362,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         }
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
         const int64_t koff = (int64_t)blk * T.k_block_size_many;
-        const int64_t pitch = T.k;
+        const int64_t pitch = row_pitch_of(T);
         const uintptr_t I_blk = reinterpret_cast<uintptr_t>(T.I + koff), V_blk = reinterpret_cast<uintptr_t>(T.V + koff);
         const uintptr_t I_lo = reinterpret_cast<uintptr_t>(T.I), I_hi = reinterpret_cast<uintptr_t>(T.I + (int64_t)a.m * pitch);
         const uintptr_t V_lo = reinterpret_cast<uintptr_t>(T.V), V_hi = reinterpret_cast<uintptr_t>(T.V + (int64_t)a.m * pitch);
@@ -534,7 +534,7 @@ __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ 
         const int len = min(WIN_SR, n_blk - s0);
         const int64_t koff = (int64_t)blk * T.k_block_size_many;
 
-        window_to_update(T.I + koff, T.V + koff, T.k, kcnt, s0, len, a, sm);
+        window_to_update(T.I + koff, T.V + koff, row_pitch_of(T), kcnt, s0, len, a, sm);
         if (T.grad_dtype == MAB_BF16) {
             for (int i = threadIdx.x; i < len; i += WIN_THREADS) sm.m_acc[i] = round_as(sm.m_acc[i], true);
             __syncthreads();

@@ -36,7 +36,7 @@ class MabTensor(Structure):
         ('d_block_size', c_int32), ('topk_full_blocks_count', c_int32),
         ('k_block_size_many', c_int32), ('k_block_size_few', c_int32),
         ('param_dtype', c_int32), ('grad_dtype', c_int32),
-        ('ring_index', c_int32), ('reserved0', c_int32),
+        ('ring_index', c_int32), ('row_pitch', c_int32),
         ('lr', c_double), ('weight_decay', c_double),
         ('decay_f32', c_float), ('neg_lr_f32', c_float),
         ('first_unit_a', c_int32), ('first_unit_b', c_int32),

@@ -8,6 +8,16 @@ top-k blocks, balanced by element count; a rank keeps optimizer state only for i
 only those parameters, and the updated ranges are then exchanged so that every rank again holds
 all parameters (one all-gather with unequal pieces).
 
+Two ways to exchange (`exchange=`):
+
+* 'params' (any alpha): the owner runs both kernels on its slices and the updated parameter ranges
+  travel, (N-1)/N of all parameter bytes into every GPU per step;
+* 'rows' (alpha = 0): only kernel A (error feedback, top-k) is sharded.  The window rows of all
+  tensors sit side by side in one buffer per rank, every rank sends the columns of the row it
+  just produced (4 bytes per selected value, 0.04 bytes per parameter at k = 1 %), and every rank
+  then runs kernel B over all parameters.  The error-feedback state stays sharded, the window
+  (0.4 bytes per parameter at m = 10, k = 1 %) is replicated, and no parameter crosses a link.
+
 A cut inside a tensor is made only on a top-k block boundary that is also a quantisation block
 boundary, so a rank's slice of a tensor behaves exactly like a smaller tensor of its own and the
 sharded result is bit-identical to the unsharded one.  Tensors where that is impossible
@@ -18,10 +28,15 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import ctypes
+import math
+
 import torch
 import torch.distributed as dist
 
+from . import _native as N
 from .micro_adam import MicroAdam
+from .tools import block_split
 
 
 @dataclass(frozen=True)
@@ -100,8 +115,14 @@ class ShardedMicroAdam(MicroAdam):
 
     def __init__(self, params, m, lr, quant_block_size, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0,
                  eps=1e-8, *, process_group=None, rank: Optional[int] = None, world_size: Optional[int] = None,
-                 gather: bool = True, overlap_chunks: int = 6, **kw):
+                 gather: bool = True, overlap_chunks: int = 6, exchange: str = 'params', **kw):
         super().__init__(params, m, lr, quant_block_size, k_init, alpha, betas, weight_decay, eps, **kw)
+        if exchange not in ('params', 'rows'):
+            raise ValueError("exchange must be 'params' or 'rows'")
+        if exchange == 'rows' and (self.alpha != 0 or not self.use_fused):
+            raise ValueError("exchange='rows' needs alpha == 0 and the fused kernels (the alpha term reads the "
+                             "error feedback of every element, which only its owner holds)")
+        self.exchange = exchange
         self.process_group = process_group
         if rank is None or world_size is None:
             if not (dist.is_available() and dist.is_initialized()):
@@ -156,8 +177,171 @@ class ShardedMicroAdam(MicroAdam):
                 self._chunks.append((mine, views))
         return self._chunks
 
+    # ---------------------------------------------------------------------------- exchange of window rows
+    def _geometry(self, d: int) -> dict:
+        """Block geometry of a flat range of d elements (micro_adam.py:70-84)."""
+        dbs = d if d < self.d_block_size else self.d_block_size
+        nfull, d_index = block_split(d, dbs)
+        k_many = int(math.ceil(dbs * self.k_init))
+        k_few = int(math.ceil((d - d_index) * self.k_init))
+        return dict(d=d, d_block_size=dbs, nfull=nfull if d_index > 0 else 0, k_many=k_many, k_few=k_few,
+                    k=k_many * nfull + k_few)
+
+    def _rows_setup(self):
+        """State of the 'rows' mode: one I and one V buffer [m, sum of k] for all tensors, error feedback for
+        the owned slices only; per-parameter state keeps the reference's key names (I, V are views)."""
+        params = self._all_params
+        dev = params[0].device
+        geos = [self._geometry(p.numel()) for p in params]
+        self._col = [0]
+        for g in geos:
+            self._col.append(self._col[-1] + g['k'])
+        self._pitch = self._col[-1] + 64                     # slack: staging reads whole 16-byte pieces
+        if self._pitch >= 2 ** 31:
+            raise ValueError('too many window columns for one buffer')
+        self._I_flat = torch.zeros(self.m, self._pitch, dtype=torch.int16, device=dev)
+        self._V_flat = torch.zeros(self.m, self._pitch, dtype=torch.bfloat16, device=dev)
+        self._dummy = torch.zeros(64, dtype=torch.uint8, device=dev)
+        self._ring = 0
+        mine = {pc.index: pc for pc in self.plan if pc.rank == self.rank}
+        self._rows_items = []
+        for i, (p, g) in enumerate(zip(params, geos)):
+            st = self.state[p]
+            c0 = self._col[i]
+            st.update(d=g['d'], d_block_size=g['d_block_size'], topk_full_blocks_count=g['nfull'], k=g['k'],
+                      k_block_size_many=g['k_many'], k_block_size_few=g['k_few'], index=0,
+                      I=self._I_flat[:, c0:c0 + g['k']], V=self._V_flat[:, c0:c0 + g['k']])
+            item = dict(p=p, full=g, col=c0, piece=None)
+            pc = mine.get(i)
+            if pc is not None and pc.hi > pc.lo:
+                sg = self._geometry(pc.hi - pc.lo)
+                nq, _ = block_split(sg['d'], self.quant_block_size)
+                st['shard_lo'], st['shard_hi'] = pc.lo, pc.hi
+                st['error'] = torch.zeros((sg['d'] + 1) // 2, dtype=torch.uint8, device=dev)
+                st['min_vals'] = torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev)
+                st['max_vals'] = torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev)
+                item['piece'] = (pc.lo, pc.hi, sg, c0 + (pc.lo // g['d_block_size']) * g['k_many'])
+            self._rows_items.append(item)
+        # every rank's columns of a row are one contiguous range: its pieces are consecutive in the list
+        self._rank_cols = []
+        for r in range(self.world_size):
+            cols = []
+            for pc in self.plan:
+                if pc.rank == r and pc.hi > pc.lo:
+                    g = geos[pc.index]
+                    lo_c = self._col[pc.index] + (pc.lo // g['d_block_size']) * g['k_many']
+                    cols.append((lo_c, lo_c + self._geometry(pc.hi - pc.lo)['k']))
+            for (a0, a1), (b0, b1) in zip(cols, cols[1:]):
+                assert a1 == b0, 'a rank\'s window columns must be contiguous'
+            self._rank_cols.append((cols[0][0], cols[-1][1]) if cols else (0, 0))
+        self._rows_descs = None
+
+    def _rows_fill(self):
+        """Descriptor arrays of the two kernels: owned slices for kernel A, whole tensors for kernel B."""
+        items = [it for it in self._rows_items if it['p'].grad is not None]
+        key = tuple((id(it['p']), it['p'].grad.dtype) for it in items)
+        if self._rows_descs is None or self._rows_descs[0] != key:
+            a_items = [it for it in items if it['piece'] is not None]
+            da, db = (N.MabTensor * max(1, len(a_items)))(), (N.MabTensor * max(1, len(items)))()
+            for d, it in zip(da, a_items):
+                lo, hi, sg, col = it['piece']
+                st = self.state[it['p']]
+                d.error, d.min_vals, d.max_vals = st['error'].data_ptr(), st['min_vals'].data_ptr(), st['max_vals'].data_ptr()
+                d.I, d.V = self._I_flat.data_ptr() + 2 * col, self._V_flat.data_ptr() + 2 * col
+                d.d, d.k, d.d_block_size = sg['d'], sg['k'], sg['d_block_size']
+                d.topk_full_blocks_count, d.k_block_size_many, d.k_block_size_few = sg['nfull'], sg['k_many'], sg['k_few']
+                d.row_pitch = self._pitch
+            for d, it in zip(db, items):
+                g = it['full']
+                d.error = d.min_vals = d.max_vals = self._dummy.data_ptr()      # not read when alpha == 0
+                d.I, d.V = self._I_flat.data_ptr() + 2 * it['col'], self._V_flat.data_ptr() + 2 * it['col']
+                d.d, d.k, d.d_block_size = g['d'], g['k'], g['d_block_size']
+                d.topk_full_blocks_count, d.k_block_size_many, d.k_block_size_few = g['nfull'], g['k_many'], g['k_few']
+                d.row_pitch = self._pitch
+            self._rows_descs = (key, a_items, da, items, db)
+        _, a_items, da, items, db = self._rows_descs
+        group_of = {id(p): g for g in self.param_groups for p in g['params']}
+        for descs, its, sliced in ((da, a_items, True), (db, items, False)):
+            for d, it in zip(descs, its):
+                p, g = it['p'], it['p'].grad
+                if not (p.is_contiguous() and g.is_contiguous()):
+                    raise N.NativeError('parameters and gradients must be contiguous')
+                if not p.is_cuda:
+                    raise N.NativeError(f'parameter on {p.device}: MicroAdam for B200 has no CPU implementation')
+                lo = it['piece'][0] if sliced else 0
+                grp = group_of[id(p)]
+                d.param, d.grad = p.data_ptr() + lo * p.element_size(), g.data_ptr() + lo * g.element_size()
+                d.param_dtype, d.grad_dtype = N.dtype_code(p), N.dtype_code(g)
+                d.ring_index = self._ring
+                d.lr, d.weight_decay = float(grp['lr']), float(grp.get('weight_decay', self.weight_decay))
+        return a_items, da, items, db
+
+    def _rows_call(self, fn_name, descs, n):
+        if n == 0:
+            return
+        lib = N.load()
+        device = self._all_params[0].device
+        need = lib.mab_fused_step_workspace_bytes(n)
+        ws = self._rows_ws.get(fn_name)
+        if ws is None or ws.numel() < need:
+            ws = self._rows_ws[fn_name] = torch.empty(need, dtype=torch.uint8, device=device)
+        args = self._step_args()
+        with torch.cuda.device(device):
+            N.check(getattr(lib, fn_name)(descs, n, ctypes.byref(args), ws.data_ptr(), ws.numel(), N.current_stream(device)), fn_name)
+
+    def rows_phase_a(self):
+        """Kernel A on the owned slices: writes this rank's columns of row `ring` of I and V."""
+        a_items, da, _, _ = self._rows_fill()
+        self._rows_call('mab_fused_ef_topk_quant', da, len(a_items))
+
+    def row_views(self) -> List[List[torch.Tensor]]:
+        """Per rank, the columns of the current row of I and of V it owns, as contiguous byte views
+        (NCCL moves no int16)."""
+        return [[self._I_flat[self._ring, c0:c1].view(torch.uint8), self._V_flat[self._ring, c0:c1].view(torch.uint8)]
+                if c1 > c0 else [] for c0, c1 in self._rank_cols]
+
+    def rows_phase_b(self):
+        """Kernel B over all parameters, then the ring advances."""
+        _, _, items, db = self._rows_fill()
+        self._rows_call('mab_fused_window_adam_update', db, len(items))
+        self._ring = (self._ring + 1) % self.m
+        for it in items:
+            self.state[it['p']]['index'] = self._ring
+
+    def rows_prepare(self):
+        """Allocates the state of the 'rows' mode (done by the first step otherwise)."""
+        if not hasattr(self, '_rows_items'):
+            self._rows_ws = {}
+            self._rows_setup()
+
+    def _rows_step(self):
+        self.rows_prepare()
+        ev = None
+        if self.kernel_events is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
+        self.rows_phase_a()
+        if ev:
+            ev[1].record()
+        if self.gather:
+            self.last_gather_bytes = exchange_pieces(self.row_views(), self.rank, self.process_group)
+        if ev:
+            ev[2].record()
+        self.rows_phase_b()
+        if ev:
+            ev[3].record()
+            self.kernel_events.append(('rows', ev))
+
     @torch.no_grad()
     def step(self, closure=None):
+        if self.exchange == 'rows':
+            self.steps += 1
+            loss = None
+            if closure is not None:
+                with torch.enable_grad():
+                    loss = closure()
+            self._rows_step()
+            return loss
         if not self.gather or self.overlap_chunks <= 1 or dist.get_backend(self.process_group) != 'nccl':
             return super().step(closure)
         self.steps += 1

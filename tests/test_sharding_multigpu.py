@@ -11,7 +11,7 @@ import cases
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, name, steps, flat):
+def _worker(rank, world, port, name, steps, flat, exchange):
     import torch.distributed as dist
     from ista_daslab_optimizers_b200 import MicroAdam
     from ista_daslab_optimizers_b200.sharding import ShardedMicroAdam, flatten_parameters
@@ -27,7 +27,7 @@ def _worker(rank, world, port, name, steps, flat):
         params = [torch.nn.Parameter(p.cuda()) for p in case.params()]
         if flat:
             flatten_parameters(params)
-        opt = ShardedMicroAdam(params, overlap_chunks=3, **kw)
+        opt = ShardedMicroAdam(params, overlap_chunks=3, exchange=exchange, **kw)
         for t in range(steps):
             grads = case.grads(t)
             for p, q, g in zip(ref_params, params, grads):
@@ -45,7 +45,7 @@ def _worker(rank, world, port, name, steps, flat):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason='needs two GPUs')
-@pytest.mark.parametrize('name,flat', [('bf16_wd', True), ('mixed_fp32_alpha', False)])
-def test_two_gpus_match_one(name, flat):
+@pytest.mark.parametrize('name,flat,exchange', [('bf16_wd', True, 'params'), ('mixed_fp32_alpha', False, 'params'), ('bf16_wd', False, 'rows')])
+def test_two_gpus_match_one(name, flat, exchange):
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(2, 29600 + random.randrange(2000), name, 3, flat), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, 29600 + random.randrange(2000), name, 3, flat, exchange), nprocs=2, join=True)
