@@ -23,7 +23,9 @@ import torch
 
 from . import microadam_oracle as O
 
-DEFAULT_REFERENCE_DIR = os.environ.get('MICROADAM_REFERENCE_DIR', '/root/reference')
+# a checkout of the reference: $MICROADAM_REFERENCE_DIR, else a directory `reference` beside this repository
+DEFAULT_REFERENCE_DIR = os.environ.get('MICROADAM_REFERENCE_DIR') or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), '..', '..', 'reference'))
 
 
 def reference_available(reference_dir: str = DEFAULT_REFERENCE_DIR) -> bool:
