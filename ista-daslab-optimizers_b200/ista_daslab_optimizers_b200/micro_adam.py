@@ -11,6 +11,9 @@ order of sub-steps.  Differences a caller can observe:
 * on the fused path `p.grad` is left untouched (the reference uses it as scratch and leaves the
   update in it, micro_adam.py:276-313); on the operator-level path it is scratch as in the reference;
 * alpha == -2 (micro_adam.py:238-273) is rejected with NotImplementedError;
+* the logging probes (micro_adam.py:155-156, 306-308, 320-324, 330-350) run only when a `log_fn` is given: every
+  `log_interval` steps the step takes the operator-level path, gathers the same seven numbers and hands
+  `log_fn` the dictionary the reference sends to wandb;
 * `state_dict()` also carries the step counter (the reference loses it, micro_adam.py:35).
 
 There is no CPU path: parameters must live on a CUDA device and the native library must be built.
@@ -19,6 +22,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import time
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -37,7 +41,7 @@ class _Entry:
 
 class MicroAdam(torch.optim.Optimizer):
     def __init__(self, params, m, lr, quant_block_size, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0,
-                 eps=1e-8, *, d_block_size: Optional[int] = None, use_fused: bool = True):
+                 eps=1e-8, *, d_block_size: Optional[int] = None, use_fused: bool = True, log_fn=None):
         defaults = dict(lr=lr, weight_decay=weight_decay, eps=eps, alpha=alpha)
         super().__init__(params, defaults)
 
@@ -69,6 +73,7 @@ class MicroAdam(torch.optim.Optimizer):
         self.shared_memory_carveout = 100
         self.threads = 512
         self.use_fused = bool(use_fused)
+        self.log_fn = log_fn      # callable(dict) or None; None (the default) switches the probes off
 
         N.load()   # fail here, loudly, if the native library is not built
         if d_block_size is None:
@@ -151,18 +156,48 @@ class MicroAdam(torch.optim.Optimizer):
                 loss = closure()
 
         self._refresh_entries()
-        fused = [e for e in self._entries if e.fused]
-        generic = [e for e in self._entries if not e.fused]
+        probe = None
+        if self.log_fn is not None and self.steps % self.log_interval == 0:                          # micro_adam.py:155,306,320
+            probe = dict(norm_g=0.0, norm_u=0.0, norm_e=0.0, sp_u=0.0, t0=time.time())
+        fused = [e for e in self._entries if e.fused and probe is None]
+        generic = [e for e in self._entries if not e.fused or probe is not None]
         if fused:
             self._fused_step(fused)
         for e in generic:
-            self._generic_update(e)
+            self._generic_update(e, probe)
         self._after_update()
+        if probe is not None:
+            self._log(probe)
         if self.kernel_events and len(self.kernel_events[-1]) == 3:
             ev = torch.cuda.Event(enable_timing=True)   # end of whatever _after_update enqueued
             ev.record()
             self.kernel_events[-1].append(ev)
         return loss
+
+    def _log(self, probe: dict):
+        """micro_adam.py:330-350: sums the probes over the ranks and hands them to `log_fn` (the reference sends the
+        same keys to wandb; the quantisation-error entries belong to alpha == -2 and stay 0)."""
+        vals = [0.0, probe['norm_g'], probe['norm_u'], probe['norm_e'], probe['sp_u'], 0.0, time.time() - probe['t0']]
+        dist = torch.distributed
+        if dist.is_available() and dist.is_initialized():
+            dev = self._entries[0].p.device if self._entries and dist.get_backend() == 'nccl' else 'cpu'
+            sync = torch.tensor(vals, dtype=torch.float, device=dev)
+            dist.all_reduce(sync, op=dist.ReduceOp.SUM)
+            vals = sync.tolist()
+            if dist.get_rank() != 0:
+                return
+        norm_qe, norm_g, norm_u, norm_e, sp_u, sp_qe, elapsed = vals
+        self.log_fn({
+            'step/optimizer_steps': self.steps,
+            'step/gpu_mem_usage': torch.cuda.memory_allocated() / 2 ** 20 if torch.cuda.is_available() else 0.0,
+            'step/norm_quant_err': math.sqrt(norm_qe),
+            'step/sparsity_quant_err': sp_qe / self.model_size * 100.,
+            'step/norm_g': math.sqrt(norm_g),
+            'step/norm_u': math.sqrt(norm_u),
+            'step/norm_error': math.sqrt(norm_e),
+            'step/sparsity_u': sp_u / self.model_size * 100.,
+            'step/elapsed_step': elapsed,
+        })
 
     def _after_update(self):
         """Hook for subclasses (the sharded optimizer gathers the updated parameters here)."""
@@ -269,8 +304,9 @@ class MicroAdam(torch.optim.Optimizer):
                 ev[2].record()
                 self.kernel_events.append(ev)
 
-    def _generic_update(self, e: _Entry):
-        """The reference's update_step (micro_adam.py:146-328) on the operator-level kernels."""
+    def _generic_update(self, e: _Entry, probe: Optional[dict] = None):
+        """The reference's update_step (micro_adam.py:146-328) on the operator-level kernels; `probe` collects the
+        squared norms and the zero count the reference logs."""
         p, st = e.p, e.st
         group = self.param_groups[e.group]
         lr, wd = group['lr'], group.get('weight_decay', self.weight_decay)
@@ -281,6 +317,8 @@ class MicroAdam(torch.optim.Optimizer):
         index, I, V = st['index'], st['I'], st['V']
         error, min_vals, max_vals = st['error'], st['min_vals'], st['max_vals']
 
+        if probe is not None:
+            probe['norm_g'] += float(grad.float().norm(p=2) ** 2)                                      # :155-156
         N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1.0)                          # :190
         N.block_topk(d, dbs, k_many, k_few, grad, I[index])                                            # :193-200
         N.copy_values(d, k, dbs, k_many, I[index], grad, V[index], CopyDirection.d2k.value)            # :202-209
@@ -295,8 +333,15 @@ class MicroAdam(torch.optim.Optimizer):
         if self.densify_update_using_ef:
             N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, self.alpha)               # :298
         pf.add_(grad, alpha=-lr)                                                                       # :304
+        if probe is not None:                                                                          # :306-308
+            probe['norm_u'] += float(grad.float().norm(p=2) ** 2)
+            probe['sp_u'] += float((grad == 0).sum())
         if self.densify_update_using_ef:                                                               # :311-316
             grad.zero_()
             N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1 - self.alpha)
             N.quant_stats(d, qbs, min_vals, max_vals, grad)
             N.asymm_block_quant(d, qbs, error, min_vals, max_vals, grad)
+        if probe is not None:                                                                          # :320-324
+            grad.zero_()
+            N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1.0)
+            probe['norm_e'] += float(grad.float().norm(p=2) ** 2)

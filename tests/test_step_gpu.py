@@ -102,3 +102,38 @@ def test_rejects_alpha_minus_two_and_cpu_params():
     opt = MicroAdam([p], m=10, lr=1e-3, quant_block_size=64)
     with pytest.raises(_native.NativeError):
         opt.step()
+
+
+def test_logging_probes_report_the_reference_quantities():
+    """log_fn switches the probes of micro_adam.py:155-156, 306-308, 320-324 on: every log_interval steps the
+    seven numbers of micro_adam.py:330-350 arrive; the state stays what the unprobed optimizer produces."""
+    import math
+    from oracle import microadam_oracle as O
+    case = cases.CASES['bf16_wd']
+    logged = []
+    plain = cases.CudaAdapter(case, case.params())
+    probed = cases.CudaAdapter(case, case.params())
+    probed.opt.log_fn = logged.append
+    probed.opt.log_interval = 2
+    for t in range(4):
+        grads = case.grads(t)
+        plain.step(grads)
+        probed.step(grads)
+        if (t + 1) % 2 == 0:
+            rec = logged[-1]
+            assert rec['step/optimizer_steps'] == t + 1
+            norm_g = math.sqrt(sum(float(g.float().norm() ** 2) for g in grads))
+            assert rec['step/norm_g'] == pytest.approx(norm_g, rel=1e-3)
+            norm_e = 0.0
+            for i in range(len(case.shapes)):
+                st = probed.state(i)
+                x = torch.zeros(st['d'], dtype=case.dtype)
+                O.asymm_block_quant_inv(st['d'], case.qbs, st['error'].cpu(), st['min_vals'].cpu(), st['max_vals'].cpu(), x, 1.0)
+                norm_e += float(x.float().norm() ** 2)
+            assert rec['step/norm_error'] == pytest.approx(math.sqrt(norm_e), rel=1e-3)
+            assert 0.0 < rec['step/sparsity_u'] < 100.0 and rec['step/norm_u'] > 0.0
+    assert len(logged) == 2
+    for i in range(len(case.shapes)):
+        a, b = plain.state(i), probed.state(i)
+        assert torch.equal(a['I'], b['I']) and torch.equal(a['error'], b['error'])
+        torch.testing.assert_close(plain.param(i).float(), probed.param(i).float(), rtol=1e-2, atol=1e-9)
