@@ -10,7 +10,7 @@ order of sub-steps.  Differences a caller can observe:
   (torch.topk(sorted=False) at micro_adam.py:193-200 leaves both unspecified);
 * on the fused path `p.grad` is left untouched (the reference uses it as scratch and leaves the
   update in it, micro_adam.py:276-313); on the operator-level path it is scratch as in the reference;
-* alpha == -2 (micro_adam.py:238-273) is rejected with NotImplementedError;
+* alpha == -2 (micro_adam.py:238-273) runs on the operator-level path only (no fused kernel);
 * the logging probes (micro_adam.py:155-156, 306-308, 320-324, 330-350) run only when a `log_fn` is given: every
   `log_interval` steps the step takes the operator-level path, gathers the same seven numbers and hands
   `log_fn` the dictionary the reference sends to wandb;
@@ -46,9 +46,6 @@ class MicroAdam(torch.optim.Optimizer):
         super().__init__(params, defaults)
 
         assert (0 <= alpha < 1) or alpha == -2, 'Alpha must be in the [0, 1) interval or -2'   # micro_adam.py:18
-        if alpha == -2:
-            raise NotImplementedError('alpha == -2 (densify the update with the quantisation error, '
-                                      'micro_adam.py:238-273) has no B200 kernel yet')
         if not (1 <= int(m) <= N.MAB_MAX_WINDOW):
             raise ValueError(f'm must be in [1, {N.MAB_MAX_WINDOW}]')
 
@@ -63,7 +60,7 @@ class MicroAdam(torch.optim.Optimizer):
         self.eps = eps
 
         self.densify_update_using_ef = (self.alpha > 0)
-        self.densify_update_using_quant_error = False
+        self.densify_update_using_quant_error = (self.alpha == -2)                                    # micro_adam.py:31
 
         self.model_size = sum(p.numel() for group in self.param_groups for p in group['params'])
 
@@ -72,7 +69,7 @@ class MicroAdam(torch.optim.Optimizer):
         self.device = get_first_device()
         self.shared_memory_carveout = 100
         self.threads = 512
-        self.use_fused = bool(use_fused)
+        self.use_fused = bool(use_fused) and not self.densify_update_using_quant_error   # alpha == -2 has no fused kernel
         self.log_fn = log_fn      # callable(dict) or None; None (the default) switches the probes off
 
         N.load()   # fail here, loudly, if the native library is not built
@@ -176,8 +173,9 @@ class MicroAdam(torch.optim.Optimizer):
 
     def _log(self, probe: dict):
         """micro_adam.py:330-350: sums the probes over the ranks and hands them to `log_fn` (the reference sends the
-        same keys to wandb; the quantisation-error entries belong to alpha == -2 and stay 0)."""
-        vals = [0.0, probe['norm_g'], probe['norm_u'], probe['norm_e'], probe['sp_u'], 0.0, time.time() - probe['t0']]
+        same keys to wandb; the quantisation-error entries are those of alpha == -2, else 0)."""
+        vals = [probe.get('norm_qe', 0.0), probe['norm_g'], probe['norm_u'], probe['norm_e'], probe['sp_u'],
+                probe.get('sp_qe', 0.0), time.time() - probe['t0']]
         dist = torch.distributed
         if dist.is_available() and dist.is_initialized():
             dev = self._entries[0].p.device if self._entries and dist.get_backend() == 'nccl' else 'cpu'
@@ -328,6 +326,20 @@ class MicroAdam(torch.optim.Optimizer):
         N.asymm_block_quant(d, qbs, error, min_vals, max_vals, grad)                                   # :231
         if wd > 0:
             pf.mul_(1 - lr * wd)                                                                       # :234-235
+        if self.densify_update_using_quant_error:                                                      # :238-273, the form without lr
+            if 'quant_err' not in st:
+                st['quant_err'] = torch.zeros(d, dtype=p.dtype, device=p.device)                       # :67-68
+            quant_err = st['quant_err']
+            quant_err.zero_()
+            quant_err.add_(grad)                                                                       # :259-260
+            pf.add_(grad, alpha=-1)                                                                    # :263
+            grad.zero_()                                                                               # :266
+            N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1.0)                      # :267
+            pf.add_(grad)                                                                              # :268
+            quant_err.sub_(grad)                                                                       # :270
+            if probe is not None:                                                                      # :272-273
+                probe['norm_qe'] = probe.get('norm_qe', 0.0) + float(quant_err.float().norm(p=2) ** 2)
+                probe['sp_qe'] = probe.get('sp_qe', 0.0) + float((quant_err == 0).sum())
         N.compute_microadam_update(st['blocks'], self.threads, self.shared_memory_carveout, self.steps, self.beta1,
                                    self.beta2, self.eps, dbs, k_many, d, self.m, k, I, V, grad)        # :276-291
         if self.densify_update_using_ef:

@@ -256,12 +256,11 @@ def compute_microadam_update(blocks, threads, carveout, steps, beta1, beta2, eps
 
 class MicroAdamOracle:
     """Standalone CPU MicroAdam: same constructor meaning, state keys and step order as the
-    reference class (micro_adam.py:13-328).  alpha == -2 (micro_adam.py:238-273) is not
-    restated."""
+    reference class (micro_adam.py:13-328), alpha == -2 (micro_adam.py:238-273) included."""
 
     def __init__(self, params: Sequence[torch.Tensor], m, lr, quant_block_size, k_init=0.01, alpha=0,
                  betas=(0.9, 0.999), weight_decay=0, eps=1e-8, d_block_size=B200_D_BLOCK_SIZE):
-        assert 0 <= alpha < 1, 'the oracle covers alpha in [0, 1)'
+        assert 0 <= alpha < 1 or alpha == -2, 'alpha must be in [0, 1) or -2'                  # micro_adam.py:18
         self.params = list(params)
         self.m = m
         self.lr = lr
@@ -313,6 +312,17 @@ class MicroAdamOracle:
         asymm_block_quant(d, qbs, error, mn, mx, grad)                                # :231
         if wd > 0:
             p.mul_(1 - lr * wd)                                                       # :234-235
+        if self.alpha == -2:                                                          # :238-273, without lr
+            if 'quant_err' not in st:
+                st['quant_err'] = torch.zeros_like(p)                                 # :67-68
+            quant_err = st['quant_err']
+            quant_err.zero_()
+            quant_err.add_(grad.view(p.shape))                                        # :259-260
+            p.add_(grad.view(p.shape), alpha=-1)                                      # :263
+            grad.zero_()                                                              # :266
+            asymm_block_quant_inv(d, qbs, error, mn, mx, grad, 1)                     # :267
+            p.add_(grad.view(p.shape))                                                # :268
+            quant_err.sub_(grad.view(p.shape))                                        # :270
         grad.zero_()                                                                  # :276
         compute_microadam_update(0, 0, 0, self.steps, self.beta1, self.beta2, self.eps,
                                  geo.d_block_size, geo.k_block_size_many, d, self.m, geo.k, I, V, grad)

@@ -93,10 +93,10 @@ def test_grad_none_and_param_groups():
     assert opt2.steps == 1 and torch.equal(opt2.state[p1]['I'], opt.state[p1]['I'])
 
 
-def test_rejects_alpha_minus_two_and_cpu_params():
+def test_rejects_bad_alpha_and_cpu_params():
     from ista_daslab_optimizers_b200 import MicroAdam, _native
-    with pytest.raises(NotImplementedError):
-        MicroAdam([torch.nn.Parameter(torch.zeros(8, device='cuda'))], m=10, lr=1e-3, quant_block_size=64, alpha=-2)
+    with pytest.raises(AssertionError):
+        MicroAdam([torch.nn.Parameter(torch.zeros(8, device='cuda'))], m=10, lr=1e-3, quant_block_size=64, alpha=-1)
     p = torch.nn.Parameter(torch.zeros(8))
     p.grad = torch.zeros(8)
     opt = MicroAdam([p], m=10, lr=1e-3, quant_block_size=64)
