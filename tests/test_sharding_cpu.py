@@ -97,3 +97,27 @@ def test_exchange_gloo_world2(flat):
     numels = [5000, 3 * DBS + 100, 64, 2 * DBS]
     port = 29500 + random.randrange(2000)
     mp.spawn(_worker, args=(2, port, numels, flat), nprocs=2, join=True)
+
+
+def _reduce_worker(rank, world, port, numels):
+    from ista_daslab_optimizers_b200.sharding import reduce_to_owners
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        plan = plan_shards(numels, DBS, 64, world)
+        # rank r contributes (r + 1) * (position + 1) + tensor index
+        grads = [(rank + 1) * (torch.arange(n, dtype=torch.float32) + 1) + i for i, n in enumerate(numels)]
+        owned = reduce_to_owners(plan, grads, rank, world, None, average=True)
+        assert owned == 4 * sum(pc.hi - pc.lo for pc in plan if pc.rank == rank)
+        mean_factor = sum(r + 1 for r in range(world)) / world
+        for pc in plan:
+            if pc.rank == rank:                             # only the owner's copy of a range is defined afterwards
+                want = mean_factor * (torch.arange(pc.lo, pc.hi, dtype=torch.float32) + 1) + pc.index
+                torch.testing.assert_close(grads[pc.index][pc.lo:pc.hi], want, rtol=1e-6, atol=1e-6)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reduce_gradients_gloo_world2():
+    numels = [5000, 3 * DBS + 100, 64, 2 * DBS]
+    mp.spawn(_reduce_worker, args=(2, 29500 + random.randrange(2000), numels), nprocs=2, join=True)
