@@ -104,6 +104,40 @@ def plan_shards(numels: Sequence[int], d_block_size: int, quant_block_size: int,
     return pieces
 
 
+def block_geometry(d: int, d_block_size: int, k_init: float) -> dict:
+    """Block geometry of a flat range of d elements (micro_adam.py:70-84)."""
+    dbs = d if d < d_block_size else d_block_size
+    nfull, d_index = block_split(d, dbs)
+    k_many = int(math.ceil(dbs * k_init))
+    k_few = int(math.ceil((d - d_index) * k_init))
+    return dict(d=d, d_block_size=dbs, nfull=nfull if d_index > 0 else 0, k_many=k_many, k_few=k_few,
+                k=k_many * nfull + k_few)
+
+
+def plan_row_columns(numels: Sequence[int], plan: Sequence[Piece], d_block_size: int, k_init: float, world_size: int):
+    """Where the window rows of all tensors sit in one [m, sum k] buffer: (first column of every tensor and the
+    total, first column of every piece of the plan, the contiguous column range of every rank)."""
+    geos = [block_geometry(n, d_block_size, k_init) for n in numels]
+    col = [0]
+    for g in geos:
+        col.append(col[-1] + g['k'])
+    piece_col = {}
+    per_rank = [[] for _ in range(world_size)]
+    for pc in plan:
+        if pc.hi > pc.lo:
+            g = geos[pc.index]
+            c0 = col[pc.index] + (pc.lo // g['d_block_size']) * g['k_many']
+            piece_col[(pc.index, pc.lo)] = c0
+            per_rank[pc.rank].append((c0, c0 + block_geometry(pc.hi - pc.lo, d_block_size, k_init)['k']))
+    rank_cols = []
+    for cols in per_rank:
+        for (a0, a1), (b0, b1) in zip(cols, cols[1:]):
+            if a1 != b0:
+                raise AssertionError("a rank's window columns must be contiguous")
+        rank_cols.append((cols[0][0], cols[-1][1]) if cols else (0, 0))
+    return col, piece_col, rank_cols
+
+
 class ShardedMicroAdam(MicroAdam):
     """MicroAdam whose state and update are sharded over the ranks of `process_group`.
 
@@ -192,13 +226,7 @@ class ShardedMicroAdam(MicroAdam):
 
     # ---------------------------------------------------------------------------- exchange of window rows
     def _geometry(self, d: int) -> dict:
-        """Block geometry of a flat range of d elements (micro_adam.py:70-84)."""
-        dbs = d if d < self.d_block_size else self.d_block_size
-        nfull, d_index = block_split(d, dbs)
-        k_many = int(math.ceil(dbs * self.k_init))
-        k_few = int(math.ceil((d - d_index) * self.k_init))
-        return dict(d=d, d_block_size=dbs, nfull=nfull if d_index > 0 else 0, k_many=k_many, k_few=k_few,
-                    k=k_many * nfull + k_few)
+        return block_geometry(d, self.d_block_size, self.k_init)
 
     def _rows_setup(self):
         """State of the 'rows' mode: one I and one V buffer [m, sum of k] for all tensors, error feedback for
@@ -206,9 +234,8 @@ class ShardedMicroAdam(MicroAdam):
         params = self._all_params
         dev = params[0].device
         geos = [self._geometry(p.numel()) for p in params]
-        self._col = [0]
-        for g in geos:
-            self._col.append(self._col[-1] + g['k'])
+        self._col, piece_col, self._rank_cols = plan_row_columns([p.numel() for p in params], self.plan, self.d_block_size,
+                                                                 self.k_init, self.world_size)
         self._pitch = self._col[-1] + 64                     # slack: staging reads whole 16-byte pieces
         if self._pitch >= 2 ** 31:
             raise ValueError('too many window columns for one buffer')
@@ -233,20 +260,8 @@ class ShardedMicroAdam(MicroAdam):
                 st['error'] = torch.zeros((sg['d'] + 1) // 2, dtype=torch.uint8, device=dev)
                 st['min_vals'] = torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev)
                 st['max_vals'] = torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev)
-                item['piece'] = (pc.lo, pc.hi, sg, c0 + (pc.lo // g['d_block_size']) * g['k_many'])
+                item['piece'] = (pc.lo, pc.hi, sg, piece_col[(pc.index, pc.lo)])
             self._rows_items.append(item)
-        # every rank's columns of a row are one contiguous range: its pieces are consecutive in the list
-        self._rank_cols = []
-        for r in range(self.world_size):
-            cols = []
-            for pc in self.plan:
-                if pc.rank == r and pc.hi > pc.lo:
-                    g = geos[pc.index]
-                    lo_c = self._col[pc.index] + (pc.lo // g['d_block_size']) * g['k_many']
-                    cols.append((lo_c, lo_c + self._geometry(pc.hi - pc.lo)['k']))
-            for (a0, a1), (b0, b1) in zip(cols, cols[1:]):
-                assert a1 == b0, 'a rank\'s window columns must be contiguous'
-            self._rank_cols.append((cols[0][0], cols[-1][1]) if cols else (0, 0))
         self._rows_descs = None
 
     def _rows_fill(self):
