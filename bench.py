@@ -162,8 +162,8 @@ def reference_arm(args, spec):
         return
     steps = max(1, args.steps)
     warmup = max(0, min(args.warmup, 3))
-    if steps > 8:
-        steps = 8      # each step is ~1-3 s of CPU work; keeps the arm within a few minutes
+    if steps > 60:
+        steps = 60     # each step is ~0.5-1.5 s of CPU work on the sample; keeps the arm within a few minutes
     rate, threads, sample, ms, n = cpu_oracle_rate(spec, steps, warmup)
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': rate, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': steps,
