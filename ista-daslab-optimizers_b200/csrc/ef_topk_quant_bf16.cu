@@ -304,10 +304,18 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             for (int i = t; i < n_oct * 8; i += S_NT) tile[i] = (i < n) ? g[i] : (uint16_t)0;
         }
         uint32_t cw[S_SLOTS];
+        if (ef_al4 && (n & 7) == 0 && n_oct >= S_FULL * S_NT) {  // a full tile: the first S_FULL words of every thread exist and are whole
 #pragma unroll
-        for (int j = 0; j < S_SLOTS; ++j) {
-            const int o = t + j * S_NT;
-            cw[j] = (o < n_oct) ? load_code_word(ef_in, ef_al4, o, n) : 0u;
+            for (int j = 0; j < S_SLOTS; ++j) {
+                const int o = t + j * S_NT;
+                cw[j] = (j < S_FULL || o < n_oct) ? reinterpret_cast<const uint32_t*>(ef_in)[o] : 0u;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < S_SLOTS; ++j) {
+                const int o = t + j * S_NT;
+                cw[j] = (o < n_oct) ? load_code_word(ef_in, ef_al4, o, n) : 0u;
+            }
         }
         if (tables) {
             for (int b = t; b < n_qb; b += S_NT) {
@@ -332,10 +340,16 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             const mab_tensor& N = tensors[nti];
             const int64_t nbase = (int64_t)(nu - s_first[nti]) * N.d_block_size;
             const int64_t nn = min((int64_t)N.d_block_size, N.d - nbase);
+            // gradients: 128-byte lines over all threads; codes and statistics: a warp each (they are 4 and 64 times smaller)
             prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(N.grad) + nbase), nn * 2);
-            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.error + (nbase >> 1)), (nn + 1) >> 1);
-            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.min_vals + (nbase >> qshift)), ((nn >> qshift) + 1) * 2);
-            prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(N.max_vals + (nbase >> qshift)), ((nn >> qshift) + 1) * 2);
+            if (warp < 3) {
+                const uintptr_t pb = warp == 0 ? reinterpret_cast<uintptr_t>(N.error + (nbase >> 1))
+                                   : reinterpret_cast<uintptr_t>((warp == 1 ? N.min_vals : N.max_vals) + (nbase >> qshift));
+                const int64_t bytes = warp == 0 ? (nn + 1) >> 1 : ((nn >> qshift) + 1) * 2;
+                const uintptr_t first = pb & ~(uintptr_t)127;
+                const int lines = (int)((pb + bytes - first + 127) >> 7);
+                for (int i = lane; i < lines; i += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(first + ((uintptr_t)i << 7)));
+            }
         }
 
         // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
