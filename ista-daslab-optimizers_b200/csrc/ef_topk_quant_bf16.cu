@@ -61,6 +61,7 @@ struct __align__(16) SmemSel {
     int      rot[64];
     int      counters[40];
     int      ctrl[8];
+    int      wcount[S_NT / 32];          // octets listed by each warp
     int      scan[36];
     int      n_member, n_cand, kmax, pad;
 };
@@ -265,9 +266,10 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
     const int cpq = 1 << cshift;
     uint32_t parity = 0;
     int guess = 0;
+    int ti_next = -1;                           // tensor of the next unit, found while prefetching it
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
-        const int ti = find_tensor(s_first, n_tensors, unit);
+        const int ti = ti_next >= 0 ? ti_next : find_tensor(s_first, n_tensors, unit);
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
         const int dbs = T.d_block_size;
@@ -290,9 +292,9 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // (selection scratch is cleared here: the barrier that ends the load publishes it)
         if (t == 0) { ss.kmax = 0; ss.n_member = 0; ss.n_cand = 0; ss.ctrl[4] = 0; }
         if (t < 64) ss.rot[t] = 0;
+        if (t < S_NT / 32) ss.wcount[t] = 0;
         ss.hist[t] = 0;
-#pragma unroll
-        for (int i = 0; i < S_WPT; ++i) ss.sel_bm[t * S_WPT + i] = 0u;
+        reinterpret_cast<uint4*>(ss.sel_bm)[t] = make_uint4(0u, 0u, 0u, 0u);
         if (staged) {
             if (t == 0) {
                 fence_async_smem();
@@ -337,6 +339,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         if (unit + (int)gridDim.x < total_units) {           // the tile after this one: into L2 while this one is worked on
             const int nu = unit + gridDim.x;
             const int nti = find_tensor(s_first, n_tensors, nu);
+            ti_next = nti;
             const mab_tensor& N = tensors[nti];
             const int64_t nbase = (int64_t)(nu - s_first[nti]) * N.d_block_size;
             const int64_t nn = min((int64_t)N.d_block_size, N.d - nbase);
@@ -413,37 +416,43 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 // 1. each warp lists its octets whose maximum reaches the bound and turns their values that
                 //    reach it into candidates (any order)
                 uint16_t* wlist = ss.oct_list + warp * S_WLIST;
-                int n_w = 0;
 #pragma unroll
                 for (int j = 0; j < S_SLOTS; ++j) {
-                    const bool q = omax[j] >= T_lo_f;
-                    const unsigned bal = __ballot_sync(0xffffffffu, q);
-                    const int at = n_w + __popc(bal & ((1u << lane) - 1u));
-                    if (q && at < S_WLIST) wlist[at] = (uint16_t)(t + j * S_NT);
-                    n_w += __popc(bal);
+                    if (omax[j] >= T_lo_f) {
+                        const int at = atomicAdd(&ss.wcount[warp], 1);
+                        if (at < S_WLIST) wlist[at] = (uint16_t)(t + j * S_NT);
+                    }
                 }
+                __syncwarp();
+                int n_w = *reinterpret_cast<volatile int*>(&ss.wcount[warp]);
                 if (lane == 0 && n_w > S_WLIST) ss.ctrl[4] = 1;
                 n_w = min(n_w, S_WLIST);
-                __syncwarp();
-                for (int e0 = 0; e0 < n_w; e0 += 32) {
-                    const int e = e0 + lane;
-                    uint32_t o = 0, mask = 0;
-                    if (e < n_w) {
-                        o = wlist[e];
-                        const uint4 v = tile4[o];
-                        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                for (int e0 = 0; e0 < n_w; e0 += 64) {                // two listed octets per lane and round
+                    uint32_t o2[2] = {0u, 0u}, mask2[2] = {0u, 0u};
 #pragma unroll
-                        for (int p = 0; p < 4; ++p) {
-                            mask |= ((w[p] & 0x7FFFu) >= T16) ? (1u << (2 * p)) : 0u;
-                            mask |= (((w[p] >> 16) & 0x7FFFu) >= T16) ? (2u << (2 * p)) : 0u;
+                    for (int h = 0; h < 2; ++h) {
+                        const int e = e0 + h * 32 + lane;
+                        if (e < n_w) {
+                            o2[h] = wlist[e];
+                            const uint4 v = tile4[o2[h]];
+                            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                mask2[h] |= ((w[p] & 0x7FFFu) >= T16) ? (1u << (2 * p)) : 0u;
+                                mask2[h] |= (((w[p] >> 16) & 0x7FFFu) >= T16) ? (2u << (2 * p)) : 0u;
+                            }
                         }
                     }
-                    int slot = warp_alloc(__popc(mask), &ss.n_cand);
-                    while (mask) {
-                        const uint32_t pos = (o << 3) + (__ffs(mask) - 1);
-                        mask &= mask - 1;
-                        if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(tile[pos] & 0x7FFFu) << 16) | (0xFFFFu - pos);
-                        ++slot;
+                    int slot = warp_alloc(__popc(mask2[0]) + __popc(mask2[1]), &ss.n_cand);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t mask = mask2[h];
+                        while (mask) {
+                            const uint32_t pos = (o2[h] << 3) + (__ffs(mask) - 1);
+                            mask &= mask - 1;
+                            if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(tile[pos] & 0x7FFFu) << 16) | (0xFFFFu - pos);
+                            ++slot;
+                        }
                     }
                 }
                 __syncthreads();
