@@ -61,7 +61,6 @@ struct __align__(16) SmemSel {
     int      rot[64];
     int      counters[40];
     int      ctrl[8];
-    int      wcount[S_NT / 32];          // octets listed by each warp
     int      scan[36];
     int      n_member, n_cand, kmax, pad;
 };
@@ -286,13 +285,15 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         const bool tables = QB64 && n_qb <= S_QTAB;
         const uint16_t* mn_g = T.min_vals + qb0;
         const uint16_t* mx_g = T.max_vals + qb0;
+        const int64_t row_off = (int64_t)T.ring_index * row_pitch_of(T) + (int64_t)blk * T.k_block_size_many;
+        int16_t* i_out = T.I + row_off;                      // (read here, with the rest of the descriptor, not after the selection)
+        uint16_t* v_out = T.V + row_off;
 
         MAB_CTICK_DECL
         // ---- bring the tile in; meanwhile codes -> registers, decode constants -> table ---------------------
         // (selection scratch is cleared here: the barrier that ends the load publishes it)
         if (t == 0) { ss.kmax = 0; ss.n_member = 0; ss.n_cand = 0; ss.ctrl[4] = 0; }
         if (t < 64) ss.rot[t] = 0;
-        if (t < S_NT / 32) ss.wcount[t] = 0;
         ss.hist[t] = 0;
         reinterpret_cast<uint4*>(ss.sel_bm)[t] = make_uint4(0u, 0u, 0u, 0u);
         if (staged) {
@@ -416,17 +417,18 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 // 1. each warp lists its octets whose maximum reaches the bound and turns their values that
                 //    reach it into candidates (any order)
                 uint16_t* wlist = ss.oct_list + warp * S_WLIST;
+                int n_w = 0;
 #pragma unroll
                 for (int j = 0; j < S_SLOTS; ++j) {
-                    if (omax[j] >= T_lo_f) {
-                        const int at = atomicAdd(&ss.wcount[warp], 1);
-                        if (at < S_WLIST) wlist[at] = (uint16_t)(t + j * S_NT);
-                    }
+                    const bool q = omax[j] >= T_lo_f;
+                    const unsigned bal = __ballot_sync(0xffffffffu, q);
+                    const int at = n_w + __popc(bal & ((1u << lane) - 1u));
+                    if (q && at < S_WLIST) wlist[at] = (uint16_t)(t + j * S_NT);
+                    n_w += __popc(bal);
                 }
-                __syncwarp();
-                int n_w = *reinterpret_cast<volatile int*>(&ss.wcount[warp]);
                 if (lane == 0 && n_w > S_WLIST) ss.ctrl[4] = 1;
                 n_w = min(n_w, S_WLIST);
+                __syncwarp();
                 for (int e0 = 0; e0 < n_w; e0 += 64) {                // two listed octets per lane and round
                     uint32_t o2[2] = {0u, 0u}, mask2[2] = {0u, 0u};
 #pragma unroll
@@ -541,9 +543,6 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             }
         }
         MAB_CTICK(2);
-        const int64_t row_off = (int64_t)T.ring_index * row_pitch_of(T) + (int64_t)blk * T.k_block_size_many;
-        int16_t* i_out = T.I + row_off;
-        uint16_t* v_out = T.V + row_off;
         if (!done) {
             // general path: bisection on the key bits over the tile in shared memory (data-independent cost)
             C = -1;
