@@ -36,8 +36,8 @@ UNIT = 'Gparams/s'
 # DRAM bytes per parameter and launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum)
 # on a smaller case of the same kernel and scaled by the parameter count; see profiles/.  None = not captured.
 NCU_TRAFFIC_BYTES_PER_PARAM = {
-    ('ef_topk_quant', 'bf16'): 3.04, ('window_adam', 'bf16'): 4.13,
-    ('ef_topk_quant', 'f32'): 5.02, ('window_adam', 'f32'): 6.55,
+    ('ef_topk_quant', 'bf16'): 3.06, ('window_adam', 'bf16'): 4.14,
+    ('ef_topk_quant', 'f32'): 5.03, ('window_adam', 'f32'): 6.49,
 }
 
 
