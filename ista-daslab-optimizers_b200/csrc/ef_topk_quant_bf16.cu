@@ -32,6 +32,7 @@ constexpr int S_WLIST = 128;                 // octets with a candidate, per war
 constexpr int S_QTAB = 512;                  // quantisation blocks whose constants fit the tables
 constexpr int S_MAX_TENSORS = 512;
 static_assert(S_WPT == 4, "a thread owns four consecutive bitmap words");
+static_assert(S_QTAB == 2 * S_NT, "a thread builds the constants of two quantisation blocks");
 
 #ifdef MAB_STATS
 __device__ unsigned long long g_stats_c[16];
@@ -320,11 +321,12 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 cw[j] = (o < n_oct) ? load_code_word(ef_in, ef_al4, o, n) : 0u;
             }
         }
-        if (tables) {
-            for (int b = t; b < n_qb; b += S_NT) {
-                const QParams q = qparams(mn_g[b], mx_g[b]);
-                ss.qt.mu[b] = make_float2(q.mn, q.u);
-            }
+        if (tables) {                                        // S_QTAB = 2 * S_NT: a thread's two blocks, their loads issued together
+            const int b0 = t, b1 = t + S_NT;
+            const uint16_t mn0 = b0 < n_qb ? mn_g[b0] : (uint16_t)0, mx0 = b0 < n_qb ? mx_g[b0] : (uint16_t)0;
+            const uint16_t mn1 = b1 < n_qb ? mn_g[b1] : (uint16_t)0, mx1 = b1 < n_qb ? mx_g[b1] : (uint16_t)0;
+            if (b0 < n_qb) { const QParams q = qparams(mn0, mx0); ss.qt.mu[b0] = make_float2(q.mn, q.u); }
+            if (b1 < n_qb) { const QParams q = qparams(mn1, mx1); ss.qt.mu[b1] = make_float2(q.mn, q.u); }
         }
         if (staged) {
             const bool ok = mbar_wait(&s_bar, parity);
