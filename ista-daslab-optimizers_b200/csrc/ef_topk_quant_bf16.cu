@@ -267,8 +267,17 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
     uint32_t parity = 0;
     int guess = 0;
     int ti_next = -1;                           // tensor of the next unit, found while prefetching it
+    const uint16_t* g_next = nullptr;           // ... and its gradient tile, so that its copy can start before its descriptor is read again
+    int n_next = 0;
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+        bool issued = false;
+        if (t == 0 && g_next != nullptr && (n_next & 7) == 0 && aligned16(g_next)) {   // same test as `staged` below
+            fence_async_smem();
+            mbar_arrive_expect_tx(&s_bar, (uint32_t)n_next * 2u);
+            bulk_g2s(smem_raw, g_next, (uint32_t)n_next * 2u, &s_bar);
+            issued = true;
+        }
         const int ti = ti_next >= 0 ? ti_next : find_tensor(s_first, n_tensors, unit);
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
@@ -298,7 +307,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         ss.hist[t] = 0;
         reinterpret_cast<uint4*>(ss.sel_bm)[t] = make_uint4(0u, 0u, 0u, 0u);
         if (staged) {
-            if (t == 0) {
+            if (t == 0 && !issued) {
                 fence_async_smem();
                 mbar_arrive_expect_tx(&s_bar, (uint32_t)n * 2u);
                 bulk_g2s(tile, g, (uint32_t)n * 2u, &s_bar);
@@ -346,6 +355,8 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             const mab_tensor& N = tensors[nti];
             const int64_t nbase = (int64_t)(nu - s_first[nti]) * N.d_block_size;
             const int64_t nn = min((int64_t)N.d_block_size, N.d - nbase);
+            g_next = reinterpret_cast<const uint16_t*>(N.grad) + nbase;
+            n_next = (int)nn;
             // gradients: 128-byte lines over all threads; codes and statistics: a warp each (they are 4 and 64 times smaller)
             prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(N.grad) + nbase), nn * 2);
             if (warp < 3) {
