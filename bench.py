@@ -1,13 +1,22 @@
 """Benchmark of the B200 MicroAdam step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama3_8b|gpt2_flat] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama3_8b|gpt2_flat|sweep] [--impl ours|reference]
 
 One "step" is one MicroAdam optimizer step over the whole synthetic model with that step's
 gradients already resident in HBM.  The default workload is the Llama-3-8B-shaped bf16 parameter
 list (290 tensors, 8 030 257 152 parameters; m=10, k_init=0.01, quant_block_size=64,
-weight_decay=0.1) on one GPU; with N > 1 (launched by torch.distributed.run, one rank per GPU) the
-same model is sharded ZeRO-1 style over the N GPUs and the updated parameters are all-gathered
-after every step (strong scaling).  Rank 0 prints one JSON line.
+weight_decay=0.1) on one GPU.  With N > 1 (launched by torch.distributed.run, one rank per GPU) the
+same model is sharded over the N GPUs (strong scaling); by default (`--exchange rows`) the error
+feedback and the top-k selection are sharded, the ranks all-gather the window row the step produced
+and every rank applies the update to all parameters; `--exchange params` shards both kernels ZeRO-1
+style and all-gathers the updated parameters instead.  Rank 0 prints one JSON line.  At N = 1 the line
+also carries a `configs.gpt2_flat` record (the fp32 single-GPU configuration), at N > 1 a
+`params_mode` record (the same model with the parameter all-gather) and the time of the gradient
+reduce-scatter of the shard plan; `param_checksum` is a checksum of all parameters that is equal for
+every N exactly when the N-GPU run is bit-identical to the 1-GPU run.
+
+`--workload sweep` times one fp32 flat tensor over the grid d x k_init x m x quant_block_size and
+prints per-kernel and per-step GB/s for every point.
 
 `--impl reference` times the CPU oracle (the restatement of the reference's torch-level step, all
 host threads) on a bounded sample of the same workload instead.
@@ -29,12 +38,13 @@ for _p in (ROOT, os.path.join(ROOT, 'ista-daslab-optimizers_b200')):
 import torch  # noqa: E402
 
 HYPER = dict(m=10, lr=1e-3, k_init=0.01, quant_block_size=64, betas=(0.9, 0.999), eps=1e-8, alpha=0)
-FALLBACK_HBM_GBS = 6650.0      # earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
+FALLBACK_HBM_GBS = 6650.0      # copy bandwidth assumed when no measured peak file is present
 METRIC = 'microadam_step_throughput'
 UNIT = 'Gparams/s'
 
-# DRAM bytes per parameter and launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum)
-# on a smaller case of the same kernel and scaled by the parameter count; see profiles/.  None = not captured.
+# DRAM bytes per parameter and launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) captured on a
+# 134 217 728-element (bf16) / 67 108 864-element (fp32) flat tensor and scaled to the workload by its
+# parameter count (traffic grows in proportion to the elements a launch covers).  None = not captured.
 NCU_TRAFFIC_BYTES_PER_PARAM = {
     ('ef_topk_quant', 'bf16'): 3.06, ('window_adam', 'bf16'): 4.14,
     ('ef_topk_quant', 'f32'): 5.03, ('window_adam', 'f32'): 6.49,
@@ -45,10 +55,10 @@ def workload_spec(name: str):
     from ista_daslab_optimizers_b200 import synthetic as S
     if name == 'llama3_8b':
         return dict(shapes=S.llama3_8b_shapes(), dtype=torch.bfloat16, weight_decay=0.1, grad_sigma=1e-4,
-                    label='Llama-3-8B-shaped bf16 parameter list, 290 tensors, weight_decay=0.1 (BASELINE config 3)')
+                    label='Llama-3-8B-shaped bf16 parameter list, 290 tensors, weight_decay=0.1')
     if name == 'gpt2_flat':
         return dict(shapes=[(124439808,)], dtype=torch.float32, weight_decay=0.0, grad_sigma=1e-3,
-                    label='one fp32 flat parameter of 124,439,808 elements (BASELINE config 2)')
+                    label='one fp32 flat parameter of 124,439,808 elements (GPT-2-small size)')
     if name.startswith('flat_'):
         # flat_<bf16|f32>_<numel>: one flat tensor, for ncu captures on a case a few times larger than L2
         _, dt, numel = name.split('_')
@@ -58,12 +68,13 @@ def workload_spec(name: str):
     raise SystemExit(f'unknown workload {name}')
 
 
-def algorithmic_bytes_per_param(dtype, rows: int):
+def algorithmic_bytes_per_param(dtype, rows: float, k_init: float = None, qbs: int = None):
     """HBM bytes per parameter the step cannot avoid, split by kernel: gradient read, one nibble
     of error feedback in and out, bf16 min+max in and out, one (index, value) row out;
     then `rows` window rows in, parameter in and out."""
     e = 2 if dtype == torch.bfloat16 else 4
-    qbs, k = HYPER['quant_block_size'], HYPER['k_init']
+    qbs = HYPER['quant_block_size'] if qbs is None else qbs
+    k = HYPER['k_init'] if k_init is None else k_init
     a = e + 1.0 + 8.0 / qbs + 4.0 * k
     b = 4.0 * rows * k + 2.0 * e
     return a, b
@@ -152,29 +163,101 @@ def cpu_oracle_rate(spec, steps: int, warmup: int):
         dt = time.perf_counter() - t0
         if t >= warmup:
             times.append(dt)
-    total = sum(times)
-    return n * len(times) / total / 1e9, threads, sample, total / len(times) * 1e3, n
+    med = sorted(times)[len(times) // 2]                      # median step
+    return n / med / 1e9, threads, sample, med * 1e3, n
+
+
+def headline_config(spec, n_params, world, exchange, grad_sets):
+    """The `config` object of the JSON line (the same for both arms)."""
+    return {'workload': spec['label'], 'params': n_params, 'parallelism': parallelism_label(world, exchange),
+            'l2_policy': 'inputs larger than L2 (GBs per step vs 126 MB)', 'grad_sets': grad_sets,
+            'arithmetic': 'fp32 on bf16/fp32 storage, 4-bit codes', **{k: v for k, v in HYPER.items() if k != 'betas'},
+            'weight_decay': spec['weight_decay']}
 
 
 def reference_arm(args, spec):
+    """The reference's CPU path (the oracle port: the reference's own step needs native modules that are not part
+    of its tree) on all host threads; every step is one step over a bounded sample of the workload."""
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    steps = max(1, args.steps)
-    warmup = max(0, min(args.warmup, 3))
-    if steps > 60:
-        steps = 60     # each step is ~0.5-1.5 s of CPU work on the sample; keeps the arm within a few minutes
+    steps = min(max(1, args.steps), 200)
+    warmup = max(3, args.warmup)
     rate, threads, sample, ms, n = cpu_oracle_rate(spec, steps, warmup)
+    world = args.gpus
+    exchange = args.exchange if (world > 1 and HYPER['alpha'] == 0) else 'params'
+    n_params = sum(int(torch.Size(s).numel()) for s in spec['shapes'])
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': rate, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': steps,
         'warmup': warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
         'dtype': 'bf16' if spec['dtype'] == torch.bfloat16 else 'f32', 'data': 'synthetic',
-        'config': {'workload': spec['label'], 'sample': sample, 'sample_params': n, **{k: v for k, v in HYPER.items() if k != 'betas'}},
-        'cpu_baseline': {'value': rate, 'unit': UNIT, 'cores': threads, 'kind': 'port', 'sample': sample},
+        'config': headline_config(spec, n_params, world, exchange, max(1, args.grad_sets)),
+        'cpu_baseline': {'value': rate, 'unit': UNIT, 'cores': threads, 'kind': 'port', 'sample': sample, 'sample_params': n,
+                         'timing': f'median of {steps} steps after {warmup} warm-up steps, each over the sample'},
         'e2e': {'value': rate, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
     print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------- roofline sweep
+
+def sweep(args):
+    """One fp32 flat tensor over d x k_init x m x quant_block_size; gradients ~N(0, 1e-3), seed 1; timed at steady
+    state (after m + 2 steps, so that the window is full); GB/s per kernel and per step from CUDA events."""
+    from ista_daslab_optimizers_b200 import MicroAdam
+    assert torch.cuda.is_available(), 'the sweep needs a CUDA device'
+    device = torch.device('cuda', 0)
+    torch.cuda.set_device(device)
+    peak, peak_kind = measured_hbm_peak()
+    points = []
+    gen = torch.Generator(device=device)
+    for log2d in (20, 24, 28, 31):
+        if log2d > args.sweep_max_log2:
+            continue
+        d = 1 << log2d
+        gen.manual_seed(1)
+        grads = [torch.empty(d, device=device).normal_(0, 1e-3, generator=gen) for _ in range(2)]
+        for qbs in (32, 64, 100000):
+            for m in (5, 10, 20):
+                for k_init in (0.005, 0.01, 0.05):
+                    gen.manual_seed(2)
+                    p = torch.nn.Parameter(torch.empty(d, device=device).normal_(0, 0.02, generator=gen), requires_grad=False)
+                    opt = MicroAdam([p], m=m, lr=1e-3, quant_block_size=qbs, k_init=k_init, alpha=0, weight_decay=0.0)
+                    warm = m + 2
+                    timed = 3 if log2d >= 28 else 10
+                    for t in range(warm):
+                        p.grad = grads[t % 2].clone() if qbs == 100000 else grads[t % 2]
+                        opt.step()
+                    fused = all(e.fused for e in opt._entries)
+                    opt.kernel_events = [] if fused else None
+                    scratch = [grads[t % 2].clone() for t in range(timed)] if not fused else None   # the operator-level path overwrites p.grad
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for t in range(timed):
+                        p.grad = scratch[t] if scratch is not None else grads[t % 2]
+                        opt.step()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms = e0.elapsed_time(e1) / timed
+                    ba, bb = algorithmic_bytes_per_param(torch.float32, m, k_init, qbs)
+                    rec = {'d': d, 'log2_d': log2d, 'k_init': k_init, 'm': m, 'quant_block_size': qbs,
+                           'path': 'fused' if fused else 'operators', 'ms_per_step': ms,
+                           'step_gbs': d * (ba + bb) / (ms * 1e-3) / 1e9, 'step_frac': d * (ba + bb) / (ms * 1e-3) / 1e9 / peak}
+                    if fused:
+                        ev = [e for e in opt.kernel_events if isinstance(e, list)]
+                        ta = sum(e[0].elapsed_time(e[1]) for e in ev) / timed
+                        tb = sum(e[1].elapsed_time(e[2]) for e in ev) / timed
+                        rec['kernels'] = [{'kernel': 'ef_topk_quant', 'ms': ta, 'gbs': d * ba / (ta * 1e-3) / 1e9, 'frac': d * ba / (ta * 1e-3) / 1e9 / peak},
+                                          {'kernel': 'window_adam', 'ms': tb, 'gbs': d * bb / (tb * 1e-3) / 1e9, 'frac': d * bb / (tb * 1e-3) / 1e9 / peak}]
+                    points.append(rec)
+                    del opt, p, scratch
+        del grads
+        torch.cuda.empty_cache()
+    print(json.dumps({'metric': 'microadam_step_hbm_sweep', 'unit': 'GB/s', 'peak': peak, 'peak_kind': f'of {peak_kind}', 'dtype': 'f32',
+                      'data': 'synthetic', 'config': {'workload': 'one fp32 flat tensor: d x k_init x m x quant_block_size, weight_decay=0, alpha=0'},
+                      'points': points}))
 
 
 # ----------------------------------------------------------------------------------- GPU arm
@@ -204,49 +287,39 @@ def make_flat_grads(spec, offsets, total, device, seed):
     return flat, [flat[o:o + int(torch.Size(s).numel())].view(s) for o, s in zip(offsets, spec['shapes'])]
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=20)
-    ap.add_argument('--warmup', type=int, default=10)
-    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='llama3_8b', help='llama3_8b | gpt2_flat | flat_<bf16|f32>_<numel>')
-    ap.add_argument('--grad-sets', type=int, default=2, help='distinct pre-generated gradient sets cycled over the steps')
-    ap.add_argument('--e2e-steps', type=int, default=3)
-    ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--seed', type=int, default=0)
-    ap.add_argument('--exchange', default='rows', choices=['rows', 'params'],
-                    help='N > 1: what the ranks exchange (window rows, or updated parameters)')
-    args = ap.parse_args()
-    spec = workload_spec(args.workload)
-    if args.impl == 'reference':
-        reference_arm(args, spec)
-        return
-
-    import torch.distributed as dist
-    from ista_daslab_optimizers_b200 import MicroAdam, _native
+def build_optimizer(spec, params, world, exchange):
+    from ista_daslab_optimizers_b200 import MicroAdam
     from ista_daslab_optimizers_b200.sharding import ShardedMicroAdam
+    kw = dict(m=HYPER['m'], lr=HYPER['lr'], quant_block_size=HYPER['quant_block_size'], k_init=HYPER['k_init'],
+              alpha=HYPER['alpha'], betas=HYPER['betas'], weight_decay=spec['weight_decay'], eps=HYPER['eps'])
+    return ShardedMicroAdam(params, exchange=exchange, **kw) if world > 1 else MicroAdam(params, **kw)
 
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    rank = int(os.environ.get('RANK', '0'))
-    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
-    if world != args.gpus:
-        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 with torch.distributed.run')
-    assert torch.cuda.is_available(), 'bench.py needs a CUDA device: there is no CPU implementation to time'
+
+def parallelism_label(world, exchange):
+    if world == 1:
+        return 'single'
+    if exchange == 'rows':
+        return f'shard{world}: kernel A sharded, window rows all-gathered, kernel B replicated'
+    return f'zero1-shard{world}: both kernels sharded, updated parameters all-gathered'
+
+
+def whole_buffer_checksum(flat_p):
+    """Wrapping 64-bit sum of the parameter buffer's bit patterns: exact, order-independent, equal on every rank and
+    for every world size exactly when the parameters are bit-identical."""
+    words = flat_p.view(torch.int16) if flat_p.element_size() == 2 else flat_p.view(torch.int32)
+    return int(words.sum(dtype=torch.int64).item())
+
+
+def run_workload(spec, args, world, rank, local_rank, exchange, steps, warmup, e2e_steps):
+    """Builds the synthetic model, runs warm-up + timed steps + the end-to-end steps and returns the measurements
+    (max over ranks) as a dictionary."""
+    import torch.distributed as dist
+    from ista_daslab_optimizers_b200 import _native
     device = torch.device('cuda', local_rank)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group('nccl', device_id=device)
-    warmup = max(3, args.warmup)
-    steps = max(1, args.steps)
-
     flat_p, params, offsets = make_flat_model(spec, device, args.seed)
     grad_sets = [make_flat_grads(spec, offsets, flat_p.numel(), device, args.seed + 1 + i) for i in range(max(1, args.grad_sets))]
     n_params = sum(p.numel() for p in params)
-    kw = dict(m=HYPER['m'], lr=HYPER['lr'], quant_block_size=HYPER['quant_block_size'], k_init=HYPER['k_init'],
-              alpha=HYPER['alpha'], betas=HYPER['betas'], weight_decay=spec['weight_decay'], eps=HYPER['eps'])
-    exchange = args.exchange if (world > 1 and HYPER['alpha'] == 0) else 'params'
-    opt = ShardedMicroAdam(params, exchange=exchange, **kw) if world > 1 else MicroAdam(params, **kw)
+    opt = build_optimizer(spec, params, world, exchange)
 
     def set_grads(t):
         for p, g in zip(params, grad_sets[t % len(grad_sets)][1]):
@@ -292,14 +365,32 @@ def main():
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     elapsed_ms, t_a, t_b, t_gather = stats.tolist()
-    value = n_params * steps / (elapsed_ms * 1e-3) / 1e9
 
-    # ---- end to end: gradients start in pinned host memory, a parameter checksum comes back -----------
+    # ---- the gradient side of the shard plan (N > 1): every range summed into its owner, timed on its own -----------
+    reduce_ms = None
+    if world > 1 and args.time_grad_reduce:
+        scratch = torch.zeros_like(grad_sets[0][0])
+        views = [scratch[o:o + p.numel()].view(p.shape) for o, p in zip(offsets, params)]
+        from ista_daslab_optimizers_b200.sharding import reduce_to_owners
+        for _ in range(2):
+            reduce_to_owners(opt.plan, views, opt.rank, world, None, average=True)
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for _ in range(3):
+            reduce_to_owners(opt.plan, views, opt.rank, world, None, average=True)
+        r1.record()
+        barrier()
+        red = torch.tensor([r0.elapsed_time(r1) / 3], dtype=torch.float64, device=device)
+        dist.all_reduce(red, op=dist.ReduceOp.MAX)
+        reduce_ms = red.item()
+        del scratch, views
+
+    # ---- end to end: gradients start in pinned host memory, a checksum of all parameters comes back ---------------
     my_lo, my_hi = 0, flat_p.numel()
     if world > 1:
         mine = [(offsets[pc.index] + pc.lo, offsets[pc.index] + pc.hi) for pc in opt.plan if pc.rank == opt.rank]
         my_lo, my_hi = min(a for a, _ in mine), max(b for _, b in mine)
-    e2e_steps = max(0, min(args.e2e_steps, steps))
     gflat = grad_sets[0][0]
     try:
         host = torch.empty(my_hi - my_lo, dtype=spec['dtype'], pin_memory=True)
@@ -313,8 +404,8 @@ def main():
     h2d_bytes = (my_hi - my_lo) * gflat.element_size()
     barrier()
     t0 = time.perf_counter()
-    checksum = 0.0
-    for t in range(max(1, e2e_steps) if e2e_steps else 0):
+    checksum = None
+    for t in range(e2e_steps):
         if not chunked:
             gflat[my_lo:my_hi].copy_(host, non_blocking=True)
         else:
@@ -322,12 +413,121 @@ def main():
                 n = min(host.numel(), my_hi - o)
                 gflat[o:o + n].copy_(host[:n], non_blocking=True)
         opt.step()
-        checksum = flat_p[my_lo:my_hi:65536].float().sum().item()     # 4-byte device-to-host read, synchronises
+        checksum = whole_buffer_checksum(flat_p)                       # 8-byte device-to-host read, synchronises
     barrier()
     e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    e2e_value = n_params * e2e_steps / e2e_s.item() / 1e9 if e2e_steps else None
+    if checksum is None:
+        checksum = whole_buffer_checksum(flat_p)
+    if world > 1:
+        # every rank must hold the same parameters: a mismatch is a correctness failure, not a number to report
+        lohi = torch.tensor([checksum, -checksum], dtype=torch.int64, device=device)
+        dist.all_reduce(lohi, op=dist.ReduceOp.MIN)
+        if lohi[0].item() != -lohi[1].item():
+            raise SystemExit(f'rank {rank}: parameter checksums differ between the ranks ({lohi[0].item()} .. {-lohi[1].item()})')
+    out = dict(n_params=n_params, steps=steps, elapsed_ms=elapsed_ms, t_a=t_a, t_b=t_b, t_gather=t_gather, launches=launches,
+               clocks=clocks, rows_avg=sum(rows_per_step) / len(rows_per_step), reduce_ms=reduce_ms,
+               e2e_value=(n_params * e2e_steps / e2e_s.item() / 1e9 if e2e_steps else None), e2e_steps=e2e_steps,
+               h2d_bytes=h2d_bytes, checksum=checksum, optimizer_steps=opt.steps, exchange=exchange,
+               device_error=_native.device_error())
+    del opt, params, grad_sets, flat_p, gflat, host
+    torch.cuda.empty_cache()
+    return out
+
+
+def kernel_records(spec, r, world):
+    """Per-kernel roofline figures from a run_workload result."""
+    peak, _ = measured_hbm_peak()
+    ba, bb = algorithmic_bytes_per_param(spec['dtype'], r['rows_avg'])
+    per_rank = r['n_params'] / world
+    # parameters one rank's launch of each kernel covers: kernel B runs over all of them when window rows are exchanged
+    params_a, params_b = per_rank, (r['n_params'] if (world > 1 and r['exchange'] == 'rows') else per_rank)
+    dt = 'bf16' if spec['dtype'] == torch.bfloat16 else 'f32'
+    kernels = []
+    for name, b, ms, np_k in (('ef_topk_quant', ba, r['t_a'], params_a), ('window_adam', bb, r['t_b'], params_b)):
+        gbs = np_k * b / (ms * 1e-3) / 1e9
+        tr = NCU_TRAFFIC_BYTES_PER_PARAM.get((name, dt))
+        kernels.append({'kernel': name, 'ms': ms, 'algorithmic_bytes': np_k * b, 'achieved_gbs': gbs,
+                        'frac': gbs / peak, 'traffic': None if tr is None else tr * np_k})
+    step_gbs = (params_a * ba + params_b * bb) / ((r['t_a'] + r['t_b']) * 1e-3) / 1e9
+    step = {'achieved_gbs': step_gbs, 'frac': step_gbs / peak, 'frac_of_8tbs_nominal': step_gbs / 8000.0,
+            'algorithmic_bytes_per_param': ba + bb, 'kernel_ms': r['t_a'] + r['t_b'], 'exposed_exchange_ms': r['t_gather']}
+    return kernels, step
+
+
+def roofline_record(kernels):
+    peak, peak_kind = measured_hbm_peak()
+    dom = max(kernels, key=lambda k: k['ms'])
+    return {'bound': 'hbm', 'kernel': dom['kernel'], 'achieved': dom['achieved_gbs'], 'peak': peak, 'unit': 'GB/s',
+            'frac': dom['frac'], 'traffic': dom['traffic'], 'peak_kind': f'of {peak_kind}',
+            'frac_of_8tbs_nominal': dom['achieved_gbs'] / 8000.0}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=10)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--workload', default='llama3_8b', help='llama3_8b | gpt2_flat | flat_<bf16|f32>_<numel> | sweep')
+    ap.add_argument('--grad-sets', type=int, default=2, help='distinct pre-generated gradient sets cycled over the steps')
+    ap.add_argument('--e2e-steps', type=int, default=3)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-extra', action='store_true',
+                    help='only the headline workload: no GPT-2-flat sub-record (N = 1), no parameter-exchange sub-record (N > 1)')
+    ap.add_argument('--no-grad-reduce', dest='time_grad_reduce', action='store_false',
+                    help='N > 1: do not time the gradient reduce-scatter of the shard plan')
+    ap.add_argument('--seed', type=int, default=0)
+    ap.add_argument('--exchange', default='rows', choices=['rows', 'params'],
+                    help='N > 1: what the ranks exchange (window rows, or updated parameters)')
+    ap.add_argument('--sweep-max-log2', type=int, default=31, help='sweep: largest tensor is 2^this elements')
+    args = ap.parse_args()
+    if args.workload == 'sweep':
+        sweep(args)
+        return
+    spec = workload_spec(args.workload)
+    if args.impl == 'reference':
+        reference_arm(args, spec)
+        return
+
+    import torch.distributed as dist
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != args.gpus:
+        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 with torch.distributed.run')
+    assert torch.cuda.is_available(), 'bench.py needs a CUDA device: there is no CPU implementation to time'
+    device = torch.device('cuda', local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+    e2e_steps = max(0, min(args.e2e_steps, steps))
+    exchange = args.exchange if (world > 1 and HYPER['alpha'] == 0) else 'params'
+
+    r = run_workload(spec, args, world, rank, local_rank, exchange, steps, warmup, e2e_steps)
+    extra = {}
+    if not args.no_extra and args.workload == 'llama3_8b':
+        if world == 1:
+            # the single-GPU fp32 configuration (GPT-2-small-sized flat tensor), with its own roofline
+            spec2 = workload_spec('gpt2_flat')
+            r2 = run_workload(spec2, args, 1, rank, local_rank, 'params', steps, warmup, 0)
+            k2, step2 = kernel_records(spec2, r2, 1)
+            extra['configs'] = {'gpt2_flat': {
+                'workload': spec2['label'], 'value': r2['n_params'] * steps / (r2['elapsed_ms'] * 1e-3) / 1e9, 'unit': UNIT,
+                'ms_per_step': r2['elapsed_ms'] / steps, 'dtype': 'f32', 'kernels': k2, 'step_hbm': step2,
+                'roofline': roofline_record(k2), 'gpu_launches': r2['launches'], 'checksum': r2['checksum']}}
+        elif exchange == 'rows':
+            # the dense alternative: both kernels sharded ZeRO-1 style, updated parameters all-gathered
+            r2 = run_workload(spec, args, world, rank, local_rank, 'params', steps, warmup, 0)
+            k2, step2 = kernel_records(spec, r2, world)
+            extra['params_mode'] = {
+                'parallelism': parallelism_label(world, 'params'), 'value': r2['n_params'] * steps / (r2['elapsed_ms'] * 1e-3) / 1e9,
+                'unit': UNIT, 'ms_per_step': r2['elapsed_ms'] / steps, 'kernels': k2, 'step_hbm': step2,
+                'checksum': r2['checksum']}
 
     if rank != 0:
         if world > 1:
@@ -335,45 +535,36 @@ def main():
         return
 
     # ---- roofline of the dominant kernel and the whole step ---------------------------------------------
-    peak, peak_kind = measured_hbm_peak()
-    rows_avg = sum(rows_per_step) / len(rows_per_step)
-    ba, bb = algorithmic_bytes_per_param(spec['dtype'], rows_avg)
-    per_rank_params = n_params / world
-    # parameters one rank's launch of each kernel covers: kernel B runs over all of them when window rows are exchanged
-    params_a, params_b = per_rank_params, (n_params if exchange == 'rows' else per_rank_params)
+    n_params = r['n_params']
+    value = n_params * steps / (r['elapsed_ms'] * 1e-3) / 1e9
+    kernels, step_hbm = kernel_records(spec, r, world)
     dt = 'bf16' if spec['dtype'] == torch.bfloat16 else 'f32'
-    kernels = []
-    for name, b, ms, np_k in (('ef_topk_quant', ba, t_a, params_a), ('window_adam', bb, t_b, params_b)):
-        gbs = np_k * b / (ms * 1e-3) / 1e9
-        tr = NCU_TRAFFIC_BYTES_PER_PARAM.get((name, dt))
-        kernels.append({'kernel': name, 'ms': ms, 'algorithmic_bytes': np_k * b, 'achieved_gbs': gbs,
-                        'frac': gbs / peak, 'traffic': None if tr is None else tr * np_k})
-    dom = max(kernels, key=lambda k: k['ms'])
-    step_gbs = (params_a * ba + params_b * bb) / ((t_a + t_b) * 1e-3) / 1e9
-
     line = {
         'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': steps, 'warmup': warmup,
-        'ms_per_step': elapsed_ms / steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
+        'ms_per_step': r['elapsed_ms'] / steps, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None,
         'dtype': dt, 'data': 'synthetic',
-        'config': {'workload': spec['label'], 'params': n_params, 'parallelism': (f'shard{world}: kernel A sharded, window rows exchanged, kernel B replicated' if exchange == 'rows' else f'zero1-shard{world}+allgather') if world > 1 else 'single',
-                   'l2_policy': 'inputs larger than L2 (GBs per step vs 126 MB)', 'grad_sets': len(grad_sets),
-                   'arithmetic': 'fp32 on bf16/fp32 storage, 4-bit codes', **{k: v for k, v in HYPER.items() if k != 'betas'},
-                   'weight_decay': spec['weight_decay']},
-        'roofline': {'bound': 'hbm', 'kernel': dom['kernel'], 'achieved': dom['achieved_gbs'], 'peak': peak, 'unit': 'GB/s',
-                     'frac': dom['frac'], 'traffic': dom['traffic'], 'peak_kind': f'of {peak_kind}',
-                     'frac_of_8tbs_nominal': dom['achieved_gbs'] / 8000.0},
+        'config': headline_config(spec, n_params, world, exchange, max(1, args.grad_sets)),
+        'roofline': roofline_record(kernels),
         'kernels': kernels,
-        'step_hbm': {'achieved_gbs': step_gbs, 'frac': step_gbs / peak, 'frac_of_8tbs_nominal': step_gbs / 8000.0,
-                     'algorithmic_bytes_per_param': ba + bb, 'kernel_ms': t_a + t_b, 'exposed_exchange_ms': t_gather},
-        'e2e': {'value': e2e_value, 'unit': UNIT, 'h2d_bytes_per_step': h2d_bytes, 'd2h_bytes_per_step': 4, 'steps': e2e_steps,
-                'checksum': checksum},
-        'gpu_launches': launches,
-        'clocks': clocks,
+        'step_hbm': step_hbm,
+        'e2e': {'value': r['e2e_value'], 'unit': UNIT, 'h2d_bytes_per_step': r['h2d_bytes'], 'd2h_bytes_per_step': 8,
+                'steps': e2e_steps},
+        # wrapping 64-bit sum of all parameter bit patterns after `optimizer_steps` steps: identical on every rank
+        # (checked) and for every N exactly when the N-GPU parameters equal the 1-GPU ones bit for bit
+        'param_checksum': {'value': r['checksum'], 'optimizer_steps': r['optimizer_steps']},
+        'gpu_launches': r['launches'],
+        'device_error': r['device_error'],
+        'clocks': r['clocks'],
     }
+    if r['reduce_ms'] is not None:
+        grad_bytes = n_params * (2 if spec['dtype'] == torch.bfloat16 else 4)
+        line['grad_reduce_scatter'] = {'ms': r['reduce_ms'], 'bytes_per_rank_in': grad_bytes * (world - 1) / world,
+                                       'note': 'gradient side of the shard plan, timed on its own, not part of value'}
+    line.update(extra)
     if world == 1 and not args.no_cpu_baseline:
-        rate, threads, sample, ms, n = cpu_oracle_rate(spec, steps=3, warmup=1)
+        rate, threads, sample, ms, n = cpu_oracle_rate(spec, steps=10, warmup=2)
         line['cpu_baseline'] = {'value': rate, 'unit': UNIT, 'cores': threads, 'kind': 'port', 'sample': sample,
-                                'ms_per_step': ms, 'sample_params': n}
+                                'ms_per_step': ms, 'sample_params': n, 'timing': 'median of 10 steps after 2 warm-up steps'}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -50,6 +50,15 @@ int64_t mab_kernel_launch_count(void);
  * value means the step it happened in is incomplete.  No counterpart in the reference. */
 int mab_device_error(void);
 
+/* Clears that flag on the current device.  Synchronises with the device.  No counterpart in the reference. */
+int mab_device_error_clear(void);
+
+/* Runs a one-block kernel whose bounded wait cannot be satisfied (its barrier expects bytes that no copy
+ * delivers): after probe_limit (1..4096) probes it gives up exactly as the step kernels would, so
+ * mab_device_error() reads 1 afterwards.  Nothing faults and the context stays usable; it exists so that
+ * the give-up path can be tested.  No counterpart in the reference. */
+int mab_wait_selftest(int probe_limit, void* stream);
+
 /* ---- device queries ------------------------------------------------------------------- */
 
 /* Replaces ista_daslab_cuda_tools.get_sm_count() (micro_adam.py:40).  < 0 on failure. */
@@ -191,6 +200,9 @@ int mab_fused_window_adam_update(mab_tensor* tensors, int n_tensors, const mab_s
  *    types share a kernel launch, so keep equal types together;
  *  - the first call on a device looks up the array's device address (once per device, with that device
  *    current); make that first call outside any stream capture;
+ *  - `tensors` is copied to the device asynchronously on `stream`; if it lives in page-locked host memory,
+ *    leave it unchanged until the stream has passed this call (pageable memory is staged before the
+ *    call returns);
  *  - all calls on a device share the one array.  Calls on the same stream are ordered and safe; two
  *    calls whose kernels can overlap on the GPU (different streams without an event between them)
  *    race on it.  Nothing in the array has to start at zero: each call overwrites what it uses. */

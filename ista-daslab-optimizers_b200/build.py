@@ -57,8 +57,6 @@ def build(verbose: bool = False, force: bool = False) -> str:
         common += ['-Xptxas', '-v']
     if os.environ.get('MAB_STATS'):
         common += ['-DMAB_STATS']       # development-only tile statistics
-    for flag in os.environ.get('MAB_DEFINES', '').split():
-        common += ['-D' + flag]         # development-only experiment switches
     procs = []
     for src in sources():
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + '.o')

@@ -23,11 +23,12 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
                  ::"r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
 
-// Waits for the phase with the given parity; gives up after ~2^20 probes (each probe itself waits
+// Waits for the phase with the given parity; gives up after `limit` probes (each probe itself waits
 // up to a hardware time limit) and returns false, so that no launch can spin for ever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+constexpr int MBAR_WAIT_PROBES = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = MBAR_WAIT_PROBES) {
     const uint32_t a = smem_addr(bar);
-    for (int it = 0; it < (1 << 20); ++it) {
+    for (int it = 0; it < limit; ++it) {
         uint32_t done;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(done) : "r"(a), "r"(parity) : "memory");

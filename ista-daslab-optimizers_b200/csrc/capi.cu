@@ -55,6 +55,26 @@ extern "C" const char* mab_last_error(void) { return g_error; }
 
 extern "C" int64_t mab_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+extern "C" int mab_device_error(void) {
+    int a = 0, b = 0, c = 0;
+    if (int rc = copy_timeout_f32(&a, false)) return rc;
+    if (int rc = copy_timeout_bf16(&b, false)) return rc;
+    if (int rc = copy_timeout_window(&c, false)) return rc;
+    return (a | b | c) ? 1 : 0;
+}
+
+extern "C" int mab_device_error_clear(void) {
+    int v = 0;
+    if (int rc = copy_timeout_f32(&v, true)) return rc;
+    if (int rc = copy_timeout_bf16(&v, true)) return rc;
+    return copy_timeout_window(&v, true);
+}
+
+extern "C" int mab_wait_selftest(int probe_limit, void* stream) {
+    MAB_REQUIRE(probe_limit >= 1 && probe_limit <= 4096, MAB_ERR_BAD_ARG, "mab_wait_selftest: probe_limit=%d outside [1, 4096]", probe_limit);
+    return launch_wait_selftest(probe_limit, (cudaStream_t)stream);
+}
+
 extern "C" int mab_get_sm_count(void) { return device_sm_count(); }
 
 extern "C" int mab_get_max_floats_for_shared_memory_per_thread_block(void) {
@@ -131,7 +151,7 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
     std::vector<Chunk> chunks;
     static thread_local std::vector<mab_tensor> staged;
     staged.resize(n);
-    const int max_tensors = std::min(WIN_MAX_TENSORS, 512);
+    const int max_tensors = WIN_MAX_TENSORS;              // kernels A and B size their unit-prefix tables by it
     const int64_t unit_cap = (int64_t)1 << 30;
     for (int pos = 0; pos < n;) {
         Chunk c = {pos, 0, 0, 0, tensors[order[pos]].grad_dtype, tensors[order[pos]].param_dtype, 0, 0};
@@ -165,7 +185,7 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
         if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
                                       args->quant_block_size)) return rc;
         for (const Chunk& c : chunks) {
-            if (int rc = launch_window_step(dev + c.first, c.count, c.units_a, c.units_b, c.max_k, c.param_dtype, wa, s)) return rc;
+            if (int rc = launch_window_step(dev + c.first, c.count, c.units_a, c.units_b, c.max_k, c.max_dbs, c.param_dtype, wa, s)) return rc;
         }
     }
     return MAB_OK;
@@ -196,17 +216,17 @@ static __device__ __align__(256) unsigned char g_static_table[MAB_STATIC_MAX_TEN
 
 static int static_table_address(void** out) {
     constexpr int kMaxDevices = 64;
-    static void* cached[kMaxDevices] = {};          // one device address per GPU; racing first calls store the same value
+    static std::atomic<void*> cached[kMaxDevices];   // one device address per GPU; racing first calls store the same value
     int dev = -1;
     MAB_CUDA_TRY(cudaGetDevice(&dev));
     MAB_REQUIRE(dev >= 0 && dev < kMaxDevices, MAB_ERR_LIMIT, "mab_fused_step_static: device ordinal %d beyond %d", dev, kMaxDevices);
-    if (cached[dev] == nullptr) {
-        void* p = nullptr;
+    void* p = cached[dev].load(std::memory_order_relaxed);
+    if (p == nullptr) {
         MAB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_table));
         MAB_REQUIRE(p != nullptr, MAB_ERR_CUDA, "mab_fused_step_static: no device address for the descriptor table");
-        cached[dev] = p;
+        cached[dev].store(p, std::memory_order_relaxed);
     }
-    *out = cached[dev];
+    *out = p;
     return MAB_OK;
 }
 
@@ -270,7 +290,7 @@ extern "C" int mab_fused_step_static(mab_tensor* tensors, int n, const mab_step_
     }
     for (int first = 0; first < n;) {
         const int end = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
-        if (int rc = launch_window_step(dev + first, end - first, ua, ub, mk, tensors[first].param_dtype, wa, s)) return rc;
+        if (int rc = launch_window_step(dev + first, end - first, ua, ub, mk, md, tensors[first].param_dtype, wa, s)) return rc;
         first = end;
     }
     return MAB_OK;

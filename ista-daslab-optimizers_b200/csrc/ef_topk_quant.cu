@@ -16,7 +16,7 @@
 
 namespace mab {
 
-constexpr int A_MAX_TENSORS = 512;
+constexpr int A_MAX_TENSORS = WIN_MAX_TENSORS;   // one limit for every kernel of a fused launch
 
 // a = round_to_grad_dtype(g + x) for an octet.
 __device__ __forceinline__ void add_round(const float (&g)[8], const float (&x)[8], float (&a)[8], const float*) {
@@ -379,16 +379,13 @@ int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total
     return MAB_OK;
 }
 
-}  // namespace mab
-
-extern "C" int mab_device_error(void) {
-    int v = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(&v, mab::g_copy_timeout, sizeof(v));
-    if (e != cudaSuccess) return mab::cuda_fail(e, "mab_device_error");
-    int v2 = 0;
-    if (int rc = mab::read_copy_timeout_bf16(&v2)) return rc;
-    return (v | v2) ? 1 : 0;
+int copy_timeout_f32(int* out, bool clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_copy_timeout, sizeof(int));
+    if (e == cudaSuccess && clear) { const int z = 0; e = cudaMemcpyToSymbol(g_copy_timeout, &z, sizeof(int)); }
+    return e == cudaSuccess ? MAB_OK : cuda_fail(e, "mab_device_error");
 }
+
+}  // namespace mab
 
 #ifdef MAB_STATS
 extern "C" int mab_debug_stats(unsigned long long* out32, int reset) {

@@ -30,7 +30,7 @@ constexpr int S_WPT = SEL_WORDS / S_NT;      // bitmap words per thread: 4
 constexpr int S_CAND_CAP = 1536;
 constexpr int S_WLIST = 128;                 // octets with a candidate, per warp
 constexpr int S_QTAB = 512;                  // quantisation blocks whose constants fit the tables
-constexpr int S_MAX_TENSORS = 512;
+constexpr int S_MAX_TENSORS = WIN_MAX_TENSORS;   // one limit for every kernel of a fused launch
 static_assert(S_WPT == 4, "a thread owns four consecutive bitmap words");
 static_assert(S_QTAB == 2 * S_NT, "a thread builds the constants of two quantisation blocks");
 
@@ -147,9 +147,7 @@ __device__ __forceinline__ void store_code_word(uint8_t* ef_g, bool aligned4, in
     for (int b = 0; b < 4; ++b) if (o * 8 + 2 * b < n) ef_g[o * 4 + b] = (uint8_t)(w >> (8 * b));
 }
 
-#ifndef S_GROUP
-#define S_GROUP 2
-#endif
+constexpr int S_GROUP = 2;                   // octets whose instructions the compiler may interleave (register pressure)
 constexpr int S_FULL = 14;                   // 29 056 values = 3632 octets: every thread has 14 whole octets, some a 15th
 
 // One octet of a = bf16(g + Qinv(e)) in place (positions >= n of a ragged tile stay zero); returns the
@@ -740,8 +738,9 @@ extern "C" int mab_debug_stats_c(unsigned long long* out16, int reset) {
 namespace mab {
 #endif
 
-int read_copy_timeout_bf16(int* out) {
+int copy_timeout_bf16(int* out, bool clear) {
     cudaError_t e = cudaMemcpyFromSymbol(out, g_copy_timeout_bf16, sizeof(int));
+    if (e == cudaSuccess && clear) { const int z = 0; e = cudaMemcpyToSymbol(g_copy_timeout_bf16, &z, sizeof(int)); }
     return e == cudaSuccess ? MAB_OK : cuda_fail(e, "mab_device_error");
 }
 

@@ -23,9 +23,10 @@ __device__ __forceinline__ int find_tensor(const int* first, int n, int unit) {
 
 // window_adam.cu
 int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double beta2, double eps, float alpha, int qbs);
-int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_k,
+int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_k, int max_dbs,
                        int param_dtype, const WindowArgs& a, cudaStream_t s);
 int units_b_of(const mab_tensor& t);
+int launch_wait_selftest(int probe_limit, cudaStream_t s);
 
 // ef_topk_quant.cu
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
@@ -34,6 +35,11 @@ int units_a_of(const mab_tensor& t);
 
 // ef_topk_quant_bf16.cu: returns 1 (without launching) when two CTAs of its shared memory do not fit an SM
 int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s);
-int read_copy_timeout_bf16(int* out);
+
+// Each kernel file keeps its own "a bounded wait gave up" flag (no relocatable device code): these read
+// it into *out and optionally clear it.
+int copy_timeout_f32(int* out, bool clear);      // ef_topk_quant.cu
+int copy_timeout_bf16(int* out, bool clear);     // ef_topk_quant_bf16.cu
+int copy_timeout_window(int* out, bool clear);   // window_adam.cu
 
 }  // namespace mab

@@ -287,6 +287,7 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
 constexpr int WT_THREADS = 256;
 constexpr int WT_WORDS = 1024;            // bitmap words (32768 positions)
 constexpr int WT_MAX_ENTRIES = 16384;     // window entries of one block the compact arrays may hold
+constexpr int WT_NO_SLOT = 0xFFFF;        // slot of a window entry whose index lies outside the block (slots stay below 32768)
 
 // Bytes one row's slice of I (or V) occupies in the raw staging area: the slice is copied from the
 // 16-byte boundary below its first element, in whole 16-byte pieces.
@@ -322,6 +323,126 @@ __device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src_gmem
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src_gmem) : "memory");
 }
 
+// Shared-memory arrays of the window phases of one tile.
+struct WindowTileSmem {
+    float2*        mv;        // (first moment | update, second moment) per slot
+    unsigned char* raw;       // rows x {I slice, V slice}, rstride bytes each
+    uint32_t*      bitmap;    // touched positions
+    uint16_t*      prefix;    // touched positions in lower bitmap words
+    uint16_t*      spos;      // position of each slot
+    int            rstride;
+    __device__ WindowTileSmem(unsigned char* base, int rows, int max_k) {
+        const int ecap = (rows * max_k + 3) & ~3;
+        rstride = wt_row_stride(max_k);
+        mv = reinterpret_cast<float2*>(base);
+        raw = reinterpret_cast<unsigned char*>(mv + ecap);
+        bitmap = reinterpret_cast<uint32_t*>(raw + rows * 2 * rstride);
+        prefix = reinterpret_cast<uint16_t*>(bitmap + WT_WORDS);
+        spos = prefix + WT_WORDS;
+    }
+};
+
+// Phases 1-4 of a tile, by the NT threads of the CTA: stages the `rows` window rows of block `blk`, numbers
+// the touched positions (slots, in ascending position) and accumulates both moments row after row into
+// w.mv[slot].  Returns the number of touched positions.  Ends with a barrier.
+template <int NT>
+__device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk, int n_blk, int kcnt, const WindowArgs& a,
+                                                   const WindowTileSmem& w, int* s_scan, int* s_pos_off, int* s_val_off) {
+    const int t = threadIdx.x;
+    const int rows = a.rows;
+    const int64_t koff = (int64_t)blk * T.k_block_size_many;
+    const int64_t pitch = row_pitch_of(T);
+    const uintptr_t I_blk = reinterpret_cast<uintptr_t>(T.I + koff), V_blk = reinterpret_cast<uintptr_t>(T.V + koff);
+    const uintptr_t I_lo = reinterpret_cast<uintptr_t>(T.I), I_hi = reinterpret_cast<uintptr_t>(T.I + (int64_t)a.m * pitch);
+    const uintptr_t V_lo = reinterpret_cast<uintptr_t>(T.V), V_hi = reinterpret_cast<uintptr_t>(T.V + (int64_t)a.m * pitch);
+    const int E = rows * kcnt;
+    const float inv_kcnt = 1.0f / (float)kcnt;
+    const int chunks_per_row = w.rstride >> 4;
+    // 1. stage the window entries: every row's slice of I and of V is copied asynchronously in
+    //    16-byte pieces from the 16-byte boundary below its first element; meanwhile clear the
+    //    bitmap and the compact moments
+    if (t < rows) {
+        s_pos_off[t] = (2 * t) * w.rstride + (int)((I_blk + (uintptr_t)t * pitch * 2) & 15);
+        s_val_off[t] = (2 * t + 1) * w.rstride + (int)((V_blk + (uintptr_t)t * pitch * 2) & 15);
+    }
+    for (int ra = t >> 6; ra < rows * 2; ra += NT >> 6) {                         // ra = 2 * row + array; 64 threads per slice
+        const int r = ra >> 1;
+        const bool isV = ra & 1;
+        const uintptr_t seg = (isV ? V_blk : I_blk) + (uintptr_t)r * pitch * 2;
+        const uintptr_t seg_end = seg + 2u * kcnt;
+        const uintptr_t first = seg & ~(uintptr_t)15;
+        const uintptr_t lo = isV ? V_lo : I_lo, hi = isV ? V_hi : I_hi;
+        unsigned char* dst_row = w.raw + ra * w.rstride;
+        for (int c = t & 63; c < chunks_per_row; c += 64) {
+            const uintptr_t src = first + 16u * c;
+            if (src < seg_end) {
+                unsigned char* dst = dst_row + 16 * c;
+                if (src >= lo && src + 16 <= hi) cp_async_16(dst, reinterpret_cast<const void*>(src));
+                else                                         // a piece that sticks out of the array: element by element
+                    for (int b = 0; b < 16; b += 2)
+                        if (src + b >= lo && src + b + 2 <= hi)
+                            *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
+            }
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = t; i < WT_WORDS; i += NT) w.bitmap[i] = 0u;
+    for (int i = t; i < E; i += NT) w.mv[i] = make_float2(0.0f, 0.0f);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    // entry i = (row r, column j): its position sits at raw + 2r * rstride + (address of the row's slice & 15) + 2j
+    auto pos_ptr = [&](int i) -> uint16_t* {
+        const int r = (int)(((float)i + 0.5f) * inv_kcnt), j = i - r * kcnt;
+        return reinterpret_cast<uint16_t*>(w.raw + s_pos_off[r]) + j;
+    };
+    // 2. mark touched positions (an index outside the block - only a damaged checkpoint can hold one - is
+    //    ignored, here and below)
+    for (int i = t; i < E; i += NT) {
+        const uint32_t pos = *pos_ptr(i);
+        if (pos < (uint32_t)n_blk) atomicOr(&w.bitmap[pos >> 5], 1u << (pos & 31));
+    }
+    __syncthreads();
+    // 3. number them: prefix[word] = touched positions in words below
+    constexpr int WPT = WT_WORDS / NT;
+    int cnt[WPT], local = 0;
+#pragma unroll
+    for (int i = 0; i < WPT; ++i) { cnt[i] = __popc(w.bitmap[t * WPT + i]); local += cnt[i]; }
+    int touched;
+    int run = block_exclusive_scan(local, s_scan, touched);
+#pragma unroll
+    for (int i = 0; i < WPT; ++i) { w.prefix[t * WPT + i] = (uint16_t)run; run += cnt[i]; }
+    __syncthreads();
+    // 4. positions -> slots (in place), then accumulate row after row
+    for (int i = t; i < E; i += NT) {
+        uint16_t* pp = pos_ptr(i);
+        const uint32_t pos = *pp;
+        if (pos < (uint32_t)n_blk) {
+            const uint32_t slot = w.prefix[pos >> 5] + __popc(w.bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u));
+            *pp = (uint16_t)slot;
+            w.spos[slot] = (uint16_t)pos;                    // entries of one position write the same value
+        } else {
+            *pp = WT_NO_SLOT;
+        }
+    }
+    __syncthreads();
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r]);
+        const uint16_t* val_r = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r]);
+        const float w1 = a.w1[r], w2 = a.w2[r];
+        for (int j = t; j < kcnt; j += NT) {
+            const int slot = slot_r[j];
+            if (slot == WT_NO_SLOT) continue;
+            const float val = bf16_bits_to_f32(val_r[j]);
+            float2 acc = w.mv[slot];
+            acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
+            w.mv[slot] = acc;
+        }
+        __syncthreads();
+    }
+    return touched;
+}
+
 template <typename TP, int MODE, bool ALPHA>
 __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  int max_k, const WindowArgs& a) {
@@ -330,20 +451,13 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     __shared__ int s_scan[36];
     __shared__ int s_pos_off[MAB_MAX_WINDOW], s_val_off[MAB_MAX_WINDOW];   // byte offsets of each row's first position / value in raw
     const int rows = a.rows;
-    const int ecap = (rows * max_k + 3) & ~3;
-    const int rstride = wt_row_stride(max_k);
-    float2* mv = reinterpret_cast<float2*>(smem_raw);                        // (first moment | update, second moment) per slot
-    unsigned char* raw = reinterpret_cast<unsigned char*>(mv + ecap);       // rows x {I slice, V slice}, rstride bytes each
-    uint32_t* bitmap = reinterpret_cast<uint32_t*>(raw + rows * 2 * rstride);
-    uint16_t* prefix = reinterpret_cast<uint16_t*>(bitmap + WT_WORDS);
-    uint16_t* spos = prefix + WT_WORDS;                                      // position of each slot
+    const WindowTileSmem w(smem_raw, rows, max_k);
     const int t = threadIdx.x;
 
     for (int i = t; i < n_tensors; i += WT_THREADS) s_first[i] = tensors[i].first_unit_a;
     if (t == 0) s_first[n_tensors] = total_units;
     __syncthreads();
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
-    const int chunks_per_row = rstride >> 4;
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int ti = find_tensor(s_first, n_tensors, unit);
@@ -359,106 +473,19 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
                 const int nti = find_tensor(s_first, n_tensors, nu);
                 prefetch_window_rows(tensors[nti], nu - s_first[nti], rows);
             }
+            // this block's parameters travel to L2 while the window is worked on
+            prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
         }
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
-        const int64_t koff = (int64_t)blk * T.k_block_size_many;
-        const int64_t pitch = row_pitch_of(T);
-        const uintptr_t I_blk = reinterpret_cast<uintptr_t>(T.I + koff), V_blk = reinterpret_cast<uintptr_t>(T.V + koff);
-        const uintptr_t I_lo = reinterpret_cast<uintptr_t>(T.I), I_hi = reinterpret_cast<uintptr_t>(T.I + (int64_t)a.m * pitch);
-        const uintptr_t V_lo = reinterpret_cast<uintptr_t>(T.V), V_hi = reinterpret_cast<uintptr_t>(T.V + (int64_t)a.m * pitch);
-        const int E = rows * kcnt;
-        const float inv_kcnt = 1.0f / (float)kcnt;
         const bool g_bf16 = (T.grad_dtype == MAB_BF16);
 
         MAB_BTICK_DECL
-        // 1. stage the window entries: every row's slice of I and of V is copied asynchronously in
-        //    16-byte pieces from the 16-byte boundary below its first element; meanwhile clear the
-        //    bitmap and the compact moments
-        if (t < rows) {
-            s_pos_off[t] = (2 * t) * rstride + (int)((I_blk + (uintptr_t)t * pitch * 2) & 15);
-            s_val_off[t] = (2 * t + 1) * rstride + (int)((V_blk + (uintptr_t)t * pitch * 2) & 15);
-        }
-        for (int ra = t >> 6; ra < rows * 2; ra += WT_THREADS >> 6) {               // ra = 2 * row + array; 64 threads per slice
-            const int r = ra >> 1;
-            const bool isV = ra & 1;
-            const uintptr_t seg = (isV ? V_blk : I_blk) + (uintptr_t)r * pitch * 2;
-            const uintptr_t seg_end = seg + 2u * kcnt;
-            const uintptr_t first = seg & ~(uintptr_t)15;
-            const uintptr_t lo = isV ? V_lo : I_lo, hi = isV ? V_hi : I_hi;
-            unsigned char* dst_row = raw + ra * rstride;
-            for (int c = t & 63; c < chunks_per_row; c += 64) {
-                const uintptr_t src = first + 16u * c;
-                if (src < seg_end) {
-                    unsigned char* dst = dst_row + 16 * c;
-                    if (src >= lo && src + 16 <= hi) cp_async_16(dst, reinterpret_cast<const void*>(src));
-                    else                                         // a piece that sticks out of the array: element by element
-                        for (int b = 0; b < 16; b += 2)
-                            if (src + b >= lo && src + b + 2 <= hi)
-                                *reinterpret_cast<uint16_t*>(dst + b) = *reinterpret_cast<const uint16_t*>(src + b);
-                }
-            }
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        // this block's parameters travel to L2 while the window is worked on, behind the window rows
-        // (asked for any earlier, other CTAs' traffic pushes them out again before they are used)
-        if (MODE == MODE_STEP)
-            prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
-        for (int i = t; i < WT_WORDS; i += WT_THREADS) bitmap[i] = 0u;
-        for (int i = t; i < E; i += WT_THREADS) mv[i] = make_float2(0.0f, 0.0f);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
-        MAB_BTICK(0);
-        // entry i = (row r, column j): its position sits at raw + 2r * rstride + (address of the row's slice & 15) + 2j
-        auto pos_ptr = [&](int i) -> uint16_t* {
-            const int r = (int)(((float)i + 0.5f) * inv_kcnt), j = i - r * kcnt;
-            return reinterpret_cast<uint16_t*>(raw + s_pos_off[r]) + j;
-        };
-        // 2. mark touched positions
-        for (int i = t; i < E; i += WT_THREADS) {
-            const uint32_t pos = *pos_ptr(i);
-            atomicOr(&bitmap[pos >> 5], 1u << (pos & 31));
-        }
-        __syncthreads();
-        MAB_BTICK(1);
-        // 3. number them: prefix[w] = touched positions in words below w
-        int cnt[WT_WORDS / WT_THREADS], local = 0;
-#pragma unroll
-        for (int i = 0; i < WT_WORDS / WT_THREADS; ++i) { cnt[i] = __popc(bitmap[t * (WT_WORDS / WT_THREADS) + i]); local += cnt[i]; }
-        int touched;
-        int run = block_exclusive_scan(local, s_scan, touched);
-#pragma unroll
-        for (int i = 0; i < WT_WORDS / WT_THREADS; ++i) { prefix[t * (WT_WORDS / WT_THREADS) + i] = (uint16_t)run; run += cnt[i]; }
-        __syncthreads();
-        MAB_BTICK(2);
-        // 4. positions -> slots (in place), then accumulate row after row
-        for (int i = t; i < E; i += WT_THREADS) {
-            uint16_t* pp = pos_ptr(i);
-            const uint32_t pos = *pp;
-            const uint32_t slot = prefix[pos >> 5] + __popc(bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u));
-            *pp = (uint16_t)slot;
-            spos[slot] = (uint16_t)pos;                        // entries of one position write the same value
-        }
-        __syncthreads();
-        MAB_BTICK(3);
-        for (int r = 0; r < rows; ++r) {
-            const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(raw + s_pos_off[r]);
-            const uint16_t* val_r = reinterpret_cast<const uint16_t*>(raw + s_val_off[r]);
-            const float w1 = a.w1[r], w2 = a.w2[r];
-            for (int j = t; j < kcnt; j += WT_THREADS) {
-                const int slot = slot_r[j];
-                const float val = bf16_bits_to_f32(val_r[j]);
-                float2 acc = mv[slot];
-                acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
-                acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
-                mv[slot] = acc;
-            }
-            __syncthreads();
-        }
+        const int touched = window_tile_moments<WT_THREADS>(T, blk, n_blk, kcnt, a, w, s_scan, s_pos_off, s_val_off);
         MAB_BTICK(4);
         // 5. moments -> update (rounded to the gradient's element type), slot by slot
         for (int s = t; s < touched; s += WT_THREADS) {
-            const float2 acc = mv[s];
-            mv[s].x = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
+            const float2 acc = w.mv[s];
+            w.mv[s].x = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
         }
         __syncthreads();
         MAB_BTICK(5);
@@ -474,12 +501,12 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
             TP* p = reinterpret_cast<TP*>(T.param) + blk_base;
             const float neg_lr = T.neg_lr_f32;
             for (int s2 = t; s2 < touched; s2 += WT_THREADS) {
-                const int pos = spos[s2];
-                Elem<TP>::store(p, pos, __fmaf_rn(neg_lr, mv[s2].x, Elem<TP>::load(p, pos)));
+                const int pos = w.spos[s2];
+                Elem<TP>::store(p, pos, __fmaf_rn(neg_lr, w.mv[s2].x, Elem<TP>::load(p, pos)));
             }
         } else {
             // 6. stream the whole block; each octet finds its updates through the bitmap
-            const SparseU src{bitmap, prefix, mv};
+            const SparseU src{w.bitmap, w.prefix, w.mv};
             stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk);
         }
         MAB_BTICK(7);
@@ -504,6 +531,140 @@ __global__ void __launch_bounds__(WT_THREADS)
 window_tile_single_kernel(const __grid_constant__ mab_tensor t, int total_units, int max_k,
                           const __grid_constant__ WindowArgs a) {
     window_tile_body<TP, MODE, ALPHA>(&t, 1, total_units, max_k, a);
+}
+
+// ------------------------------------------------------------------------------------ resident-tile kernel
+//
+// The step without the alpha term on bf16 parameters: the block's parameters are walked once.  One
+// bulk copy (the 1-D copy engine) brings them into shared memory while the window phases run; the
+// weight decay and the updates of the touched positions are applied there, and one bulk copy writes
+// the block back while the CTA already works on its next block.  512 threads, two CTAs per SM.
+//
+// round_bf16(p * decay) == p for every bf16 p when 0 <= 1 - decay <= 2^-10: the product differs from p
+// by less than a quarter of the distance to the neighbouring bf16 value, for normal and subnormal p
+// alike.  The decay pass is skipped for such a tensor (lr * weight_decay = 1e-4 is the usual case);
+// the result is bit for bit the one the pass would produce.
+
+constexpr int WR_THREADS = 512;
+
+// Set when a wait on the copy engine gave up; read through mab_device_error() together with the other kernels' flags.
+__device__ int g_copy_timeout_window;
+
+__device__ __forceinline__ bool decay_is_identity_bf16(float decay) {
+    return decay <= 1.0f && (1.0f - decay) <= 0.0009765625f;
+}
+
+__global__ void __launch_bounds__(WR_THREADS, 2)
+window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int max_k, int tile_bytes,
+                       const __grid_constant__ WindowArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];                 // [tile][window arrays]
+    __shared__ int s_first[WIN_MAX_TENSORS + 1];
+    __shared__ int s_scan[36];
+    __shared__ int s_pos_off[MAB_MAX_WINDOW], s_val_off[MAB_MAX_WINDOW];
+    __shared__ __align__(8) uint64_t s_bar;
+    uint16_t* tile = reinterpret_cast<uint16_t*>(smem_raw);
+    uint4* tile4 = reinterpret_cast<uint4*>(smem_raw);
+    const int rows = a.rows;
+    const WindowTileSmem w(smem_raw + tile_bytes, rows, max_k);
+    const int t = threadIdx.x;
+
+    for (int i = t; i < n_tensors; i += WR_THREADS) s_first[i] = tensors[i].first_unit_a;
+    if (t == 0) { s_first[n_tensors] = total_units; mbar_init(&s_bar, 1); }
+    __syncthreads();
+    const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
+    uint32_t parity = 0;
+    bool store_in_flight = false;                                               // thread 0 only
+
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+        const int ti = find_tensor(s_first, n_tensors, unit);
+        const mab_tensor& T = tensors[ti];
+        const int blk = unit - s_first[ti];
+        const int dbs = T.d_block_size, nfull = T.topk_full_blocks_count;
+        const int64_t blk_base = (int64_t)blk * dbs;
+        const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
+        uint16_t* p = reinterpret_cast<uint16_t*>(T.param) + blk_base;
+        const bool bulk = (n_blk & 7) == 0 && aligned16(p);                     // the copy engine moves whole 16-byte pieces
+        const int n_oct = (n_blk + 7) >> 3;
+
+        MAB_BTICK_DECL
+        // the block's parameters start travelling; the previous block's store must have left the tile first
+        if (t == 0) {
+            if (store_in_flight) { bulk_wait_read(); store_in_flight = false; }
+            if (bulk) {
+                fence_async_smem();
+                mbar_arrive_expect_tx(&s_bar, (uint32_t)n_blk * 2u);
+                bulk_g2s(tile, p, (uint32_t)n_blk * 2u, &s_bar);
+            }
+        }
+        if (unit + (int)gridDim.x < total_units) {                              // the next unit's window rows: into L2
+            const int nu = unit + gridDim.x;
+            const int nti = find_tensor(s_first, n_tensors, nu);
+            prefetch_window_rows(tensors[nti], nu - s_first[nti], rows);
+        }
+        const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
+        const bool g_bf16 = (T.grad_dtype == MAB_BF16);
+        const int touched = window_tile_moments<WR_THREADS>(T, blk, n_blk, kcnt, a, w, s_scan, s_pos_off, s_val_off);
+        MAB_BTICK(4);
+
+        // the tile: wait for the bulk copy, or fetch a ragged block (a tensor's last one, an unaligned slice) with plain loads
+        if (bulk) {
+            const bool ok = mbar_wait(&s_bar, parity);
+            parity ^= 1u;
+            if (__syncthreads_or(!ok)) {
+                if (t == 0) atomicExch(&g_copy_timeout_window, 1);
+                return;
+            }
+        } else {
+            if (t == 0 && store_in_flight) { bulk_wait_read(); store_in_flight = false; }
+            __syncthreads();
+            for (int i = t; i < n_blk; i += WR_THREADS) tile[i] = p[i];
+            __syncthreads();
+        }
+        MAB_BTICK(5);
+        // weight decay over the whole tile, in shared memory
+        const float decay = T.decay_f32;
+        if (T.weight_decay > 0.0 && !decay_is_identity_bf16(decay)) {
+            const float2 decay2 = make_float2(decay, decay);
+            for (int o = t; o < n_oct; o += WR_THREADS) {
+                const uint4 v = tile4[o];
+                const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+                uint32_t out[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const float2 x = __fmul2_rn(make_float2(__uint_as_float(in[b] << 16), __uint_as_float(in[b] & 0xFFFF0000u)), decay2);
+                    out[b] = cvt_bf16x2_rne(x.x, x.y);
+                }
+                tile4[o] = make_uint4(out[0], out[1], out[2], out[3]);         // (positions past n_blk of a ragged tile are never stored)
+            }
+            __syncthreads();
+        }
+        MAB_BTICK(6);
+        // moments -> update (rounded to the gradient's element type) -> parameter, touched positions only:
+        // fma(-lr, 0, x) == x, so the untouched elements are already final
+        const float neg_lr = T.neg_lr_f32;
+        for (int s = t; s < touched; s += WR_THREADS) {
+            const float2 acc = w.mv[s];
+            const float u = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
+            const int pos = w.spos[s];
+            tile[pos] = f32_to_bf16_bits_rne(__fmaf_rn(neg_lr, u, bf16_bits_to_f32(tile[pos])));
+        }
+        MAB_BTICK(7);
+        // the tile goes back
+        if (bulk) {
+            fence_async_smem();                                                 // this thread's writes, before the copy engine reads them
+            __syncthreads();
+            if (t == 0) { bulk_s2g(p, tile, (uint32_t)n_blk * 2u); store_in_flight = true; }
+        } else {
+            __syncthreads();
+            for (int i = t; i < n_blk; i += WR_THREADS) p[i] = tile[i];
+            __syncthreads();
+        }
+        MAB_BTICK(8);
+#ifdef MAB_STATS
+        if (threadIdx.x == 0) atomicAdd(&g_stats_b[15], 1ull);
+#endif
+    }
+    if (t == 0 && store_in_flight) bulk_wait_all();                            // shared memory must outlive the copy engine's reads
 }
 
 // ------------------------------------------------------------------------------------ wide kernel
@@ -628,11 +789,59 @@ int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double b
     return MAB_OK;
 }
 
-int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_k,
+// Shared memory of one CTA of the resident-tile kernel, or 0 when two such CTAs do not fit an SM.
+static int resident_smem_bytes(int rows, int max_k, int max_dbs, int* tile_bytes) {
+    *tile_bytes = (max_dbs * 2 + 127) & ~127;
+    if ((int64_t)rows * max_k > WT_MAX_ENTRIES) return 0;
+    const int smem = *tile_bytes + wt_smem_bytes(rows, max_k);
+    const int static_and_reserved = 6 * 1024;                 // the kernel's static arrays + the per-CTA reservation
+    return 2 * (smem + static_and_reserved) <= device_max_optin_smem() + 1024 ? smem : 0;
+}
+
+int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_tile, int units_wide, int max_k, int max_dbs,
                        int param_dtype, const WindowArgs& a, cudaStream_t s) {
     if (param_dtype == MAB_F32)
         return launch_window<float, MODE_STEP>(dev_tensors, nullptr, n_tensors, units_tile, units_wide, max_k, a, s);
+    int tile_bytes = 0;
+    const int smem = (a.alpha == 0.0f) ? resident_smem_bytes(a.rows, max_k, max_dbs, &tile_bytes) : 0;
+    if (smem > 0) {
+        const int grid = (int)std::min<int64_t>(units_tile, (int64_t)device_sm_count() * 2);
+        MAB_CUDA_TRY(cudaFuncSetAttribute(window_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        window_resident_kernel<<<grid, WR_THREADS, smem, s>>>(dev_tensors, n_tensors, units_tile, max_k, tile_bytes, a);
+        count_launch();
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return cuda_fail(e, "window_resident_kernel launch");
+        return MAB_OK;
+    }
     return launch_window<uint16_t, MODE_STEP>(dev_tensors, nullptr, n_tensors, units_tile, units_wide, max_k, a, s);
+}
+
+// The give-up path of the bounded waits, exercised without any fault: the barrier is told to expect
+// 16 bytes that no copy delivers, the wait runs out after `probe_limit` probes, and the kernel reports
+// it through the same flag and the same early return the step kernels use.
+__global__ void wait_selftest_kernel(int probe_limit) {
+    __shared__ __align__(8) uint64_t s_bar;
+    if (threadIdx.x == 0) mbar_init(&s_bar, 1);
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_arrive_expect_tx(&s_bar, 16u);
+    const bool ok = mbar_wait(&s_bar, 0u, probe_limit);
+    if (__syncthreads_or(!ok)) {
+        if (threadIdx.x == 0) atomicExch(&g_copy_timeout_window, 1);
+        return;
+    }
+}
+
+int launch_wait_selftest(int probe_limit, cudaStream_t s) {
+    wait_selftest_kernel<<<1, 64, 0, s>>>(probe_limit);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MAB_OK : cuda_fail(e, "wait_selftest_kernel launch");
+}
+
+int copy_timeout_window(int* out, bool clear) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_copy_timeout_window, sizeof(int));
+    if (e == cudaSuccess && clear) { const int z = 0; e = cudaMemcpyToSymbol(g_copy_timeout_window, &z, sizeof(int)); }
+    return e == cudaSuccess ? MAB_OK : cuda_fail(e, "mab_device_error");
 }
 
 int units_b_of(const mab_tensor& t) {

@@ -57,6 +57,8 @@ SIGNATURES = {
     'mab_last_error': (c_char_p, []),
     'mab_kernel_launch_count': (c_int64, []),
     'mab_device_error': (c_int, []),
+    'mab_device_error_clear': (c_int, []),
+    'mab_wait_selftest': (c_int, [c_int, c_void_p]),
     'mab_get_sm_count': (c_int, []),
     'mab_get_max_floats_for_shared_memory_per_thread_block': (c_int, []),
     'mab_asymm_block_quant_inv': (c_int, [c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p]),
@@ -134,6 +136,10 @@ def device_error() -> int:
     if v < 0:
         check(v, 'device_error')
     return v
+
+
+def device_error_clear() -> None:
+    check(load().mab_device_error_clear(), 'device_error_clear')
 
 
 def get_sm_count() -> int:

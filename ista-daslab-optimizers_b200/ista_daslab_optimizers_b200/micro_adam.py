@@ -135,13 +135,71 @@ class MicroAdam(torch.optim.Optimizer):
         sd['steps'] = self.steps
         return sd
 
+    # element type every tensor of the per-parameter state must keep (micro_adam.py:86-94)
+    _STATE_DTYPES = {'I': torch.int16, 'V': torch.bfloat16, 'error': torch.uint8,
+                     'min_vals': torch.bfloat16, 'max_vals': torch.bfloat16}
+
     def load_state_dict(self, state_dict):
+        """Restores a state written by `state_dict()` of this class or of the reference class.
+
+        `torch.optim.Optimizer.load_state_dict` casts every state tensor to the parameter's element type,
+        which would turn the 4-bit codes, the int16 indices and the bf16 statistics into floats that the
+        kernels then misread.  The tensors are therefore taken from the incoming dictionary again with the
+        element types they were saved with (only the device changes), and checked: wrong element type or
+        shape, or a window index outside its block, raises instead of reaching a kernel.  `I` saved in another
+        element type (checkpoint pipelines that cast everything, micro_adam.py:175-178) is accepted if every
+        value is an integer inside the block."""
         state_dict = dict(state_dict)
         steps = state_dict.pop('steps', None)
         super().load_state_dict(state_dict)
+        saved_ids = [i for g in state_dict['param_groups'] for i in g['params']]
+        params = [p for g in self.param_groups for p in g['params']]
+        for sid, p in zip(saved_ids, params):
+            saved = state_dict['state'].get(sid)
+            if not saved or 'I' not in saved:
+                continue
+            st = self.state[p]
+            for key, want in self._STATE_DTYPES.items():
+                src = saved[key]
+                if not torch.is_tensor(src):
+                    raise TypeError(f"optimizer state '{key}' is not a tensor")
+                if key == 'I' and src.dtype != want:
+                    as_int = src.to(torch.int16)
+                    if not torch.equal(as_int.to(src.dtype), src):
+                        raise ValueError("optimizer state 'I' holds values that are not 16-bit integers")
+                    src = as_int
+                if src.dtype != want:
+                    raise TypeError(f"optimizer state '{key}' has element type {src.dtype}, expected {want}")
+                st[key] = src.detach().to(device=p.device, copy=True)
+            d, k, nq = int(st['d']), int(st['k']), int(st['quant_full_blocks_count'])
+            shapes = {'I': (self.m, k), 'V': (self.m, k), 'error': ((d + 1) // 2,), 'min_vals': (nq + 1,), 'max_vals': (nq + 1,)}
+            for key, shape in shapes.items():
+                if tuple(st[key].shape) != shape:
+                    raise ValueError(f"optimizer state '{key}' has shape {tuple(st[key].shape)}, expected {shape}")
+            self._check_window_indices(st)
+            if 'quant_err' in saved and torch.is_tensor(saved['quant_err']):
+                st['quant_err'] = saved['quant_err'].detach().to(device=p.device, dtype=p.dtype, copy=True)
+            if not (0 <= int(st['index']) < self.m):
+                raise ValueError(f"optimizer state 'index' = {st['index']} outside [0, {self.m})")
         if steps is not None:
             self.steps = int(steps)
         self._entries_key = None
+
+    @staticmethod
+    def _check_window_indices(st):
+        """Every stored index must lie inside its top-k block (the update kernel uses it as an offset)."""
+        I = st['I']
+        if I.numel() == 0:
+            return
+        k_index, dbs = int(st['k_index']), int(st['d_block_size'])
+        tail = int(st['d']) - int(st['d_index_topk']) if int(st['k_block_size_few']) > 0 else 0
+        bad = bool((I < 0).any())
+        if k_index > 0:
+            bad |= bool((I[:, :k_index] >= dbs).any())
+        if I.shape[1] > k_index:
+            bad |= bool((I[:, k_index:] >= max(tail, 1)).any())
+        if bad:
+            raise ValueError("optimizer state 'I' holds an index outside its top-k block")
 
     # ------------------------------------------------------------------------------ step
     @torch.no_grad()

@@ -12,10 +12,11 @@ Two ways to exchange (`exchange=`):
 
 * 'params' (any alpha): the owner runs both kernels on its slices and the updated parameter ranges
   travel, (N-1)/N of all parameter bytes into every GPU per step;
-* 'rows' (alpha = 0): only kernel A (error feedback, top-k) is sharded.  The window rows of all
-  tensors sit side by side in one buffer per rank, every rank sends the columns of the row it
-  just produced (4 bytes per selected value, 0.04 bytes per parameter at k = 1 %), and every rank
-  then runs kernel B over all parameters.  The error-feedback state stays sharded, the window
+* 'rows' (alpha = 0): only kernel A (error feedback, top-k) is sharded.  The window of all tensors
+  sits in one buffer per rank with one equally wide region per rank in every row; every rank fills
+  its region of the row a step produces (4 bytes per selected value, 0.04 bytes per parameter at
+  k = 1 %), one in-place all-gather completes the row, and every rank then runs kernel B over all
+  parameters.  The error-feedback state stays sharded, the window
   (0.4 bytes per parameter at m = 10, k = 1 %) is replicated, and no parameter crosses a link.
 
 A cut inside a tensor is made only on a top-k block boundary that is also a quantisation block
@@ -114,30 +115,6 @@ def block_geometry(d: int, d_block_size: int, k_init: float) -> dict:
                 k=k_many * nfull + k_few)
 
 
-def plan_row_columns(numels: Sequence[int], plan: Sequence[Piece], d_block_size: int, k_init: float, world_size: int):
-    """Where the window rows of all tensors sit in one [m, sum k] buffer: (first column of every tensor and the
-    total, first column of every piece of the plan, the contiguous column range of every rank)."""
-    geos = [block_geometry(n, d_block_size, k_init) for n in numels]
-    col = [0]
-    for g in geos:
-        col.append(col[-1] + g['k'])
-    piece_col = {}
-    per_rank = [[] for _ in range(world_size)]
-    for pc in plan:
-        if pc.hi > pc.lo:
-            g = geos[pc.index]
-            c0 = col[pc.index] + (pc.lo // g['d_block_size']) * g['k_many']
-            piece_col[(pc.index, pc.lo)] = c0
-            per_rank[pc.rank].append((c0, c0 + block_geometry(pc.hi - pc.lo, d_block_size, k_init)['k']))
-    rank_cols = []
-    for cols in per_rank:
-        for (a0, a1), (b0, b1) in zip(cols, cols[1:]):
-            if a1 != b0:
-                raise AssertionError("a rank's window columns must be contiguous")
-        rank_cols.append((cols[0][0], cols[-1][1]) if cols else (0, 0))
-    return col, piece_col, rank_cols
-
-
 class ShardedMicroAdam(MicroAdam):
     """MicroAdam whose state and update are sharded over the ranks of `process_group`.
 
@@ -229,80 +206,99 @@ class ShardedMicroAdam(MicroAdam):
         return block_geometry(d, self.d_block_size, self.k_init)
 
     def _rows_setup(self):
-        """State of the 'rows' mode: one I and one V buffer [m, sum of k] for all tensors, error feedback for
-        the owned slices only; per-parameter state keeps the reference's key names (I, V are views)."""
+        """State of the 'rows' mode.
+
+        One int16 buffer holds the whole window, laid out [m rows][world regions][I | V][width] with one region per
+        rank: a rank's pieces write their columns side by side into its region (indices in the I half, bf16 value
+        bits in the V half).  Regions have one width (the widest rank's column count, padded to 128 bytes), so the
+        row a step produces is exchanged by one in-place all-gather over that row.  Error feedback and block
+        statistics exist for the owned pieces only; every rank describes every piece to kernel B."""
         params = self._all_params
         dev = params[0].device
-        geos = [self._geometry(p.numel()) for p in params]
-        self._col, piece_col, self._rank_cols = plan_row_columns([p.numel() for p in params], self.plan, self.d_block_size,
-                                                                 self.k_init, self.world_size)
-        self._pitch = self._col[-1] + 64                     # slack: staging reads whole 16-byte pieces
+        W = self.world_size
+        pieces = [pc for pc in self.plan if pc.hi > pc.lo]
+        cols = [0] * W
+        self._rows_pieces = []                                 # (piece, geometry, first column inside the owner's region)
+        for pc in pieces:
+            g = self._geometry(pc.hi - pc.lo)
+            self._rows_pieces.append((pc, g, cols[pc.rank]))
+            cols[pc.rank] += g['k']
+        self._rank_cols = cols
+        self._width = -(-(max(cols) + 8) // 64) * 64           # elements per half region
+        self._pitch = W * 2 * self._width                      # elements between consecutive rows
         if self._pitch >= 2 ** 31:
             raise ValueError('too many window columns for one buffer')
-        self._I_flat = torch.zeros(self.m, self._pitch, dtype=torch.int16, device=dev)
-        self._V_flat = torch.zeros(self.m, self._pitch, dtype=torch.bfloat16, device=dev)
+        # 64 elements of slack behind the last row: kernel B stages whole 16-byte pieces around a slice
+        self._window = torch.zeros(self.m * self._pitch + 64, dtype=torch.int16, device=dev)
         self._dummy = torch.zeros(64, dtype=torch.uint8, device=dev)
         self._ring = 0
-        mine = {pc.index: pc for pc in self.plan if pc.rank == self.rank}
-        self._rows_items = []
-        for i, (p, g) in enumerate(zip(params, geos)):
+        self._rows_state = {}                                  # (parameter index, lo) -> error feedback of an owned piece
+        for pc, g, col in self._rows_pieces:
+            p = params[pc.index]
+            if pc.rank != self.rank:
+                continue
+            nq, _ = block_split(g['d'], self.quant_block_size)
+            base = pc.rank * 2 * self._width + col
+            rows = self._window[:self.m * self._pitch].view(self.m, self._pitch)
             st = self.state[p]
-            c0 = self._col[i]
             st.update(d=g['d'], d_block_size=g['d_block_size'], topk_full_blocks_count=g['nfull'], k=g['k'],
                       k_block_size_many=g['k_many'], k_block_size_few=g['k_few'], index=0,
-                      I=self._I_flat[:, c0:c0 + g['k']], V=self._V_flat[:, c0:c0 + g['k']])
-            item = dict(p=p, full=g, col=c0, piece=None)
-            pc = mine.get(i)
-            if pc is not None and pc.hi > pc.lo:
-                sg = self._geometry(pc.hi - pc.lo)
-                nq, _ = block_split(sg['d'], self.quant_block_size)
-                st['shard_lo'], st['shard_hi'] = pc.lo, pc.hi
-                st['error'] = torch.zeros((sg['d'] + 1) // 2, dtype=torch.uint8, device=dev)
-                st['min_vals'] = torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev)
-                st['max_vals'] = torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev)
-                item['piece'] = (pc.lo, pc.hi, sg, piece_col[(pc.index, pc.lo)])
-            self._rows_items.append(item)
+                      shard_lo=pc.lo, shard_hi=pc.hi,
+                      I=rows[:, base:base + g['k']], V=rows[:, base + self._width:base + self._width + g['k']].view(torch.bfloat16),
+                      error=torch.zeros((g['d'] + 1) // 2, dtype=torch.uint8, device=dev),
+                      min_vals=torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev),
+                      max_vals=torch.zeros(nq + 1, dtype=torch.bfloat16, device=dev))
+            self._rows_state[(pc.index, pc.lo)] = st
         self._rows_descs = None
 
     def _rows_fill(self):
-        """Descriptor arrays of the two kernels: owned slices for kernel A, whole tensors for kernel B."""
-        items = [it for it in self._rows_items if it['p'].grad is not None]
-        key = tuple((id(it['p']), it['p'].grad.dtype) for it in items)
-        if self._rows_descs is None or self._rows_descs[0] != key:
-            a_items = [it for it in items if it['piece'] is not None]
-            da, db = (N.MabTensor * max(1, len(a_items)))(), (N.MabTensor * max(1, len(items)))()
-            for d, it in zip(da, a_items):
-                lo, hi, sg, col = it['piece']
-                st = self.state[it['p']]
+        """Descriptor arrays of the two kernels: owned pieces for kernel A, every piece of every rank for kernel B."""
+        params = self._all_params
+        a_pieces = [x for x in self._rows_pieces if x[0].rank == self.rank]
+        for pc, _, _ in a_pieces:
+            if params[pc.index].grad is None:
+                raise RuntimeError(f"exchange='rows': parameter {pc.index} has no gradient on rank {self.rank}, which owns "
+                                   f"elements [{pc.lo}, {pc.hi}) of it; every rank must provide the gradients of its own slices "
+                                   "on every step (the window advances for all tensors together)")
+        gdt = tuple((params[pc.index].grad.dtype if params[pc.index].grad is not None else params[pc.index].dtype)
+                    for pc, _, _ in self._rows_pieces)
+        if self._rows_descs is None or self._rows_descs[0] != gdt:
+            da, db = (N.MabTensor * max(1, len(a_pieces)))(), (N.MabTensor * max(1, len(self._rows_pieces)))()
+            wptr = self._window.data_ptr()
+            for descs, its in ((da, a_pieces), (db, self._rows_pieces)):
+                for d, (pc, g, col) in zip(descs, its):
+                    base = pc.rank * 2 * self._width + col
+                    d.I, d.V = wptr + 2 * base, wptr + 2 * (base + self._width)
+                    d.d, d.k, d.d_block_size = g['d'], g['k'], g['d_block_size']
+                    d.topk_full_blocks_count, d.k_block_size_many, d.k_block_size_few = g['nfull'], g['k_many'], g['k_few']
+                    d.row_pitch = self._pitch
+            for d, (pc, g, col) in zip(da, a_pieces):
+                st = self._rows_state[(pc.index, pc.lo)]
                 d.error, d.min_vals, d.max_vals = st['error'].data_ptr(), st['min_vals'].data_ptr(), st['max_vals'].data_ptr()
-                d.I, d.V = self._I_flat.data_ptr() + 2 * col, self._V_flat.data_ptr() + 2 * col
-                d.d, d.k, d.d_block_size = sg['d'], sg['k'], sg['d_block_size']
-                d.topk_full_blocks_count, d.k_block_size_many, d.k_block_size_few = sg['nfull'], sg['k_many'], sg['k_few']
-                d.row_pitch = self._pitch
-            for d, it in zip(db, items):
-                g = it['full']
+            for d in db:
                 d.error = d.min_vals = d.max_vals = self._dummy.data_ptr()      # not read when alpha == 0
-                d.I, d.V = self._I_flat.data_ptr() + 2 * it['col'], self._V_flat.data_ptr() + 2 * it['col']
-                d.d, d.k, d.d_block_size = g['d'], g['k'], g['d_block_size']
-                d.topk_full_blocks_count, d.k_block_size_many, d.k_block_size_few = g['nfull'], g['k_many'], g['k_few']
-                d.row_pitch = self._pitch
-            self._rows_descs = (key, a_items, da, items, db)
-        _, a_items, da, items, db = self._rows_descs
+            self._rows_descs = (gdt, a_pieces, da, db)
+        _, a_pieces, da, db = self._rows_descs
         group_of = {id(p): g for g in self.param_groups for p in g['params']}
-        for descs, its, sliced in ((da, a_items, True), (db, items, False)):
-            for d, it in zip(descs, its):
-                p, g = it['p'], it['p'].grad
-                if not (p.is_contiguous() and g.is_contiguous()):
-                    raise N.NativeError('parameters and gradients must be contiguous')
+        for descs, its, with_grad in ((da, a_pieces, True), (db, self._rows_pieces, False)):
+            for d, (pc, g, col), in zip(descs, its):
+                p = params[pc.index]
                 if not p.is_cuda:
                     raise N.NativeError(f'parameter on {p.device}: MicroAdam for B200 has no CPU implementation')
-                lo = it['piece'][0] if sliced else 0
+                if not p.is_contiguous() or (p.grad is not None and not p.grad.is_contiguous()):
+                    raise N.NativeError('parameters and gradients must be contiguous')
                 grp = group_of[id(p)]
-                d.param, d.grad = p.data_ptr() + lo * p.element_size(), g.data_ptr() + lo * g.element_size()
-                d.param_dtype, d.grad_dtype = N.dtype_code(p), N.dtype_code(g)
+                d.param = p.data_ptr() + pc.lo * p.element_size()
+                d.param_dtype = N.dtype_code(p)
+                if p.grad is not None:
+                    d.grad = p.grad.data_ptr() + pc.lo * p.grad.element_size()
+                    d.grad_dtype = N.dtype_code(p.grad)
+                else:                                          # kernel B only needs the element type the update is rounded to
+                    d.grad = d.param
+                    d.grad_dtype = d.param_dtype
                 d.ring_index = self._ring
                 d.lr, d.weight_decay = float(grp['lr']), float(grp.get('weight_decay', self.weight_decay))
-        return a_items, da, items, db
+        return a_pieces, da, db
 
     def _rows_call(self, fn_name, descs, n):
         if n == 0:
@@ -318,27 +314,30 @@ class ShardedMicroAdam(MicroAdam):
             N.check(getattr(lib, fn_name)(descs, n, ctypes.byref(args), ws.data_ptr(), ws.numel(), N.current_stream(device)), fn_name)
 
     def rows_phase_a(self):
-        """Kernel A on the owned slices: writes this rank's columns of row `ring` of I and V."""
-        a_items, da, _, _ = self._rows_fill()
-        self._rows_call('mab_fused_ef_topk_quant', da, len(a_items))
+        """Kernel A on the owned pieces: writes this rank's region of row `ring` of the window."""
+        a_pieces, da, _ = self._rows_fill()
+        self._rows_call('mab_fused_ef_topk_quant', da, len(a_pieces))
 
-    def row_views(self) -> List[List[torch.Tensor]]:
-        """Per rank, the columns of the current row of I and of V it owns, as contiguous byte views
-        (NCCL moves no int16)."""
-        return [[self._I_flat[self._ring, c0:c1].view(torch.uint8), self._V_flat[self._ring, c0:c1].view(torch.uint8)]
-                if c1 > c0 else [] for c0, c1 in self._rank_cols]
+    def current_row(self) -> torch.Tensor:
+        """The row of the window this step writes, [world, 2 * width] int16: region r is rank r's to fill."""
+        return self._window[self._ring * self._pitch:(self._ring + 1) * self._pitch].view(self.world_size, 2 * self._width)
+
+    def rows_exchange(self) -> int:
+        """Every rank's region of the current row travels to all others: one in-place all-gather.  Returns the bytes
+        this rank received."""
+        return gather_row_regions(self.current_row(), self.rank, self.process_group)
 
     def rows_phase_b(self):
         """Kernel B over all parameters, then the ring advances."""
-        _, _, items, db = self._rows_fill()
-        self._rows_call('mab_fused_window_adam_update', db, len(items))
+        _, _, db = self._rows_fill()
+        self._rows_call('mab_fused_window_adam_update', db, len(self._rows_pieces))
         self._ring = (self._ring + 1) % self.m
-        for it in items:
-            self.state[it['p']]['index'] = self._ring
+        for st in self._rows_state.values():
+            st['index'] = self._ring
 
     def rows_prepare(self):
         """Allocates the state of the 'rows' mode (done by the first step otherwise)."""
-        if not hasattr(self, '_rows_items'):
+        if not hasattr(self, '_rows_pieces'):
             self._rows_ws = {}
             self._rows_setup()
 
@@ -352,13 +351,73 @@ class ShardedMicroAdam(MicroAdam):
         if ev:
             ev[1].record()
         if self.gather:
-            self.last_gather_bytes = exchange_pieces(self.row_views(), self.rank, self.process_group)
+            self.last_gather_bytes = self.rows_exchange()
         if ev:
             ev[2].record()
         self.rows_phase_b()
         if ev:
             ev[3].record()
             self.kernel_events.append(('rows', ev))
+
+    # ---------------------------------------------------------------------------- checkpoint of the 'rows' mode
+    def state_dict(self):
+        """'rows' mode: the replicated window, the ring position, the step counter and the error feedback of the
+        owned pieces, keyed by (parameter index, first element); a checkpoint belongs to one (rank, world size)."""
+        if self.exchange != 'rows':
+            return super().state_dict()
+        self.rows_prepare()
+        return {'exchange': 'rows', 'rank': self.rank, 'world_size': self.world_size, 'steps': self.steps, 'ring': self._ring,
+                'm': self.m, 'width': self._width, 'window': self._window.clone(),
+                'pieces': {key: {k: st[k].clone() for k in ('error', 'min_vals', 'max_vals')} for key, st in self._rows_state.items()},
+                'param_groups': super().state_dict()['param_groups']}
+
+    def load_state_dict(self, state_dict):
+        if self.exchange != 'rows':
+            return super().load_state_dict(state_dict)
+        if state_dict.get('exchange') != 'rows':
+            raise ValueError("this optimizer exchanges window rows; the checkpoint was not written in that mode")
+        self.rows_prepare()
+        if (state_dict['rank'], state_dict['world_size'], state_dict['m'], state_dict['width']) != (self.rank, self.world_size, self.m, self._width):
+            raise ValueError('checkpoint of another rank, world size or window geometry')
+        if set(state_dict['pieces']) != set(self._rows_state):
+            raise ValueError('checkpoint holds other pieces than this rank owns')
+        if not (0 <= int(state_dict['ring']) < self.m):
+            raise ValueError(f"ring position {state_dict['ring']} outside [0, {self.m})")
+        win = state_dict['window']
+        if win.dtype != torch.int16 or win.shape != self._window.shape:
+            raise TypeError('window of the checkpoint has another element type or shape')
+        self._check_rows_window(win)
+        for key, saved in state_dict['pieces'].items():
+            st = self._rows_state[key]
+            for k in ('error', 'min_vals', 'max_vals'):
+                if saved[k].dtype != st[k].dtype or saved[k].shape != st[k].shape:
+                    raise TypeError(f"'{k}' of piece {key} has another element type or shape")
+        self._window.copy_(win)                                # in place: the descriptors and the state views stay valid
+        for key, saved in state_dict['pieces'].items():
+            for k in ('error', 'min_vals', 'max_vals'):
+                self._rows_state[key][k].copy_(saved[k])
+        self._ring = int(state_dict['ring'])
+        for st in self._rows_state.values():
+            st['index'] = self._ring
+        self.steps = int(state_dict['steps'])
+        for g, saved in zip(self.param_groups, state_dict['param_groups']):
+            g.update({k: v for k, v in saved.items() if k != 'params'})
+
+    def _check_rows_window(self, win: torch.Tensor):
+        """Every index of every piece (all ranks: kernel B reads them all) must lie inside its block."""
+        rows = win[:self.m * self._pitch].view(self.m, self._pitch)
+        for pc, g, col in self._rows_pieces:
+            base = pc.rank * 2 * self._width + col
+            I = rows[:, base:base + g['k']]
+            k_index = g['nfull'] * g['k_many']
+            tail = g['d'] - g['nfull'] * g['d_block_size']
+            bad = bool((I < 0).any())
+            if k_index > 0:
+                bad |= bool((I[:, :k_index] >= g['d_block_size']).any())
+            if g['k'] > k_index:
+                bad |= bool((I[:, k_index:] >= max(tail, 1)).any())
+            if bad:
+                raise ValueError(f'window of the checkpoint holds an index outside its top-k block (parameter {pc.index})')
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -433,18 +492,24 @@ def build_gather_views(plan: Sequence[Piece], params: Sequence[torch.Tensor], wo
 
 def reduce_to_owners(plan: Sequence[Piece], tensors: Sequence[torch.Tensor], rank: int, world_size: int, group=None,
                      average: bool = True) -> int:
-    """Sums (averages) every planned range of `tensors` over the ranks into its owner, in place (one reduce per
-    owned view, all in flight together).  Returns the bytes this rank owns."""
+    """Sums (averages) every planned range of `tensors` over the ranks into its owner, in place: a reduce-scatter
+    with unequal pieces.  When every rank's ranges merge into one view (tensors that are slices of one flat
+    buffer) and the backend is NCCL, that is one `reduce_scatter` call whose per-rank inputs are the views
+    themselves (nothing is copied or padded); otherwise one reduce per owned view, all in flight together.
+    Returns the bytes this rank owns."""
     if world_size == 1:
         return 0
     views = build_gather_views(plan, tensors, world_size)
-    works = []
-    for r, vs in enumerate(views):
-        dst = dist.get_global_rank(group, r) if group is not None else r
-        for v in vs:
-            works.append(dist.reduce(v, dst=dst, op=dist.ReduceOp.SUM, group=group, async_op=True))
-    for w in works:
-        w.wait()
+    if dist.get_backend(group) == 'nccl' and all(len(vs) == 1 for vs in views):
+        dist.reduce_scatter(views[rank][0], [vs[0] for vs in views], op=dist.ReduceOp.SUM, group=group)
+    else:
+        works = []
+        for r, vs in enumerate(views):
+            dst = dist.get_global_rank(group, r) if group is not None else r
+            for v in vs:
+                works.append(dist.reduce(v, dst=dst, op=dist.ReduceOp.SUM, group=group, async_op=True))
+        for w in works:
+            w.wait()
     if average:
         for v in views[rank]:
             v.div_(world_size)
@@ -479,6 +544,17 @@ def exchange_pieces(views: List[List[torch.Tensor]], rank: int, group=None) -> i
     for w in works:
         w.wait()
     return received
+
+
+def gather_row_regions(row: torch.Tensor, rank: int, group=None) -> int:
+    """`row` is [world, n] and contiguous, region `rank` filled in: all-gathers the regions in place (NCCL's
+    in-place convention: the send buffer is the rank's own slot of the receive buffer).  Returns the bytes received."""
+    row = row.view(torch.uint8)                                # the collectives move no int16
+    mine = row[rank]
+    if dist.get_backend(group) != 'nccl':
+        mine = mine.clone()
+    dist.all_gather_into_tensor(row.view(-1), mine, group=group)
+    return (row.shape[0] - 1) * mine.numel()
 
 
 def flatten_parameters(params: Sequence[torch.nn.Parameter]) -> torch.Tensor:

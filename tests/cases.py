@@ -64,7 +64,7 @@ class Case:
 
 
 CASES: Dict[str, Case] = {c.name: c for c in [
-    # BASELINE config 1: one fp32 parameter [1048576], 12 steps so that the m=10 window wraps
+    # the reference's own CPU-runnable configuration: one fp32 parameter [1048576], 12 steps so that the m=10 window wraps
     Case('c1_fp32_1m', [(1048576,)], torch.float32, 12),
     # small mixed shapes, heavy-tailed gradients with exact ties, a zero tensor, alpha and weight decay
     Case('mixed_fp32_alpha', [(7,), (65,), (64, 64), (333, 77), (100001,), (256, 256, 3, 3), (4096,)], torch.float32, 12,
@@ -80,7 +80,21 @@ CASES: Dict[str, Case] = {c.name: c for c in [
     Case('alpha_m2', [(70000,), (4096,)], torch.float32, 4, alpha=-2, weight_decay=0.1),
     # bf16 with a quantisation block other than 64: the general decode / statistics / encode code of the bf16 kernel
     Case('bf16_qbs32', [(70000,), (4096,), (29056 + 32 * 7,)], torch.bfloat16, 5, qbs=32, weight_decay=0.1, grad_sigma=1e-4),
+    # windows too large for the compact per-tile arrays of the update kernel (m = 20 rows of 5 % of a block):
+    # the wide variant of the fused step, with and without weight decay, with the alpha term, fp32 and bf16
+    Case('wide_fp32', [(29056 * 2 + 640,), (4096,), (70000,)], torch.float32, 22, m=20, k_init=0.05),
+    Case('wide_bf16_wd', [(29056 * 2 + 640,), (4096,)], torch.bfloat16, 14, m=20, k_init=0.05, weight_decay=0.1, grad_sigma=1e-4),
+    Case('wide_fp32_alpha', [(29056 + 64 * 9,), (300, 200)], torch.float32, 14, m=20, k_init=0.05, alpha=0.5, weight_decay=0.1,
+         grad_kind='student_t3_ties'),
+    # few rows of few entries (m = 5, 0.5 % of a block)
+    Case('narrow_m5', [(29056 * 3 + 8,), (1000,)], torch.float32, 7, m=5, k_init=0.005, weight_decay=0.1),
+    Case('narrow_m5_bf16', [(29056 * 3 + 8,), (1000,)], torch.bfloat16, 7, m=5, k_init=0.005, weight_decay=0.1, grad_sigma=1e-4),
 ]}
+
+
+# the case behind tests/golden/reference_state_3steps.pt (a reference-written checkpoint): a tensor with a short
+# last block, a single-block tensor and a 2-D one, with weight decay
+CKPT_CASE = Case('ckpt_fp32', [(29056 + 640,), (2048,), (100, 70)], torch.float32, 6, weight_decay=0.1)
 
 
 def _h(*tensors: torch.Tensor) -> str:
@@ -111,6 +125,7 @@ def param_sample(p: torch.Tensor) -> List[float]:
 class Trace:
     digests: List[List[str]] = field(default_factory=list)       # [step][tensor]
     samples: List[List[List[float]]] = field(default_factory=list)  # [step][tensor][i]
+    params: List[List[torch.Tensor]] = field(default_factory=list)  # [step][tensor]: every element, float32 on the CPU (keep_params)
 
 
 class Adapter:
@@ -121,12 +136,15 @@ class Adapter:
     def param(self, i: int) -> torch.Tensor: ...
 
 
-def run_case(case: Case, make: Callable[[Case, List[torch.Tensor]], Adapter]) -> Trace:
+def run_case(case: Case, make: Callable[[Case, List[torch.Tensor]], Adapter], keep_params: bool = False) -> Trace:
+    """Runs the case; with keep_params the trace also holds every parameter element after every step."""
     params = case.params()
     impl = make(case, params)
     tr = Trace()
     for t in range(case.steps):
         impl.step(case.grads(t))
+        if keep_params:
+            tr.params.append([impl.param(i).detach().float().cpu().clone() for i in range(len(case.shapes))])
         dg, sm = [], []
         for i in range(len(case.shapes)):
             st = impl.state(i)
@@ -136,6 +154,15 @@ def run_case(case: Case, make: Callable[[Case, List[torch.Tensor]], Adapter]) ->
         tr.digests.append(dg)
         tr.samples.append(sm)
     return tr
+
+
+def assert_params_close(case: Case, got: Trace, want: Trace):
+    """Every parameter element after every step: rel 1e-5 (fp32) / 1e-2 (bf16), the tolerance the path's specification states."""
+    tol = 1e-5 if case.dtype == torch.float32 else 1e-2
+    assert len(got.params) == len(want.params) == case.steps
+    for step, (mine, theirs) in enumerate(zip(got.params, want.params)):
+        for i, (a, b) in enumerate(zip(mine, theirs)):
+            torch.testing.assert_close(a, b, rtol=tol, atol=1e-9, msg=lambda m: f'step {step}, tensor {i}: {m}')
 
 
 class OracleAdapter(Adapter):

@@ -1,4 +1,4 @@
-"""Full-size runs (BASELINE config 2: 124,439,808 fp32 elements; config 4's largest: 2^31 elements)
+"""Full-size runs (the GPT-2-small-sized flat tensor, 124,439,808 fp32 elements; the roofline sweep's largest, 2^31 elements)
 checked through properties that need no CPU oracle: sortedness and range of the window indices,
 exactness of the selection (every selected magnitude >= every unselected one in its block), the
 window values, exact block statistics and the code round trip of the residual, and the closed

@@ -141,3 +141,44 @@ def test_device_queries(N):
     assert N.get_sm_count() == torch.cuda.get_device_properties(0).multi_processor_count
     floats = N.get_max_floats_for_shared_memory_per_thread_block()
     assert floats * 4 == torch.cuda.get_device_properties(0).shared_memory_per_block_optin
+
+
+def test_bounded_wait_gives_up_and_reports(N):
+    """The give-up path of the kernels' bounded waits, run without any fault: a one-block kernel waits on a barrier
+    that expects bytes no copy delivers, gives up after a few probes and raises the device flag; the context stays
+    usable and the flag can be cleared."""
+    torch.cuda.synchronize()
+    N.device_error_clear()
+    assert N.device_error() == 0
+    N.check(N.load().mab_wait_selftest(4, None), 'mab_wait_selftest')
+    assert N.device_error() == 1
+    N.device_error_clear()
+    assert N.device_error() == 0
+    x = torch.arange(10, device='cuda').sum().item()          # the context still works
+    assert x == 45
+    assert N.load().mab_wait_selftest(0, None) == -1             # limit outside [1, 4096]
+
+
+@pytest.mark.parametrize('lr,wd', [(1e-3, 0.1), (1e-2, 0.09), (1e-2, 0.1), (0.05, 0.5)])
+def test_weight_decay_on_every_bf16_value(N, lr, wd):
+    """The fused step skips the decay pass over bf16 parameters when 0 <= lr * wd <= 2^-10, because
+    bf16(p * (1 - lr * wd)) == p for every bf16 p then; with a larger product it multiplies.  Either way the
+    untouched elements must hold exactly what `p.mul_(1 - lr * wd)` gives: checked on all finite bf16 values."""
+    from ista_daslab_optimizers_b200 import MicroAdam
+    patterns = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    finite = patterns[torch.isfinite(patterns.float())]
+    vals = torch.cat([finite, finite[:29056 * 3 - finite.numel()]]).cuda()     # three full top-k blocks
+    p = torch.nn.Parameter(vals.clone())
+    opt = MicroAdam([p], m=10, lr=lr, quant_block_size=64, k_init=0.01, weight_decay=wd)
+    p.grad = torch.empty_like(p).normal_(0, 1e-4, generator=torch.Generator(device='cuda').manual_seed(3))
+    opt.step()
+    assert all(e.fused for e in opt._entries)
+    want = vals.clone().mul_(1 - lr * wd)
+    st = opt.state[p]
+    touched = torch.zeros(p.numel(), dtype=torch.bool, device='cuda')
+    idx = st['I'][0].long() + (torch.arange(st['k'], device='cuda') // st['k_block_size_many']) * st['d_block_size']
+    touched[idx] = True
+    assert int(touched.sum()) == st['k']
+    got = p.detach()
+    assert torch.equal(got[~touched].view(torch.int16), want[~touched].view(torch.int16))
+    assert not torch.equal(got[touched].view(torch.int16), want[touched].view(torch.int16))

@@ -123,29 +123,42 @@ def test_reduce_gradients_gloo_world2():
     mp.spawn(_reduce_worker, args=(2, 29500 + random.randrange(2000), numels), nprocs=2, join=True)
 
 
-def test_row_column_plan_properties():
-    """Window-row layout of the 'rows' exchange: tensors side by side, a piece's columns are the columns of its
-    blocks in the whole tensor's row, a rank's columns are one contiguous range, ranks tile the row."""
-    from ista_daslab_optimizers_b200.sharding import block_geometry, plan_row_columns
+def test_piece_geometry_matches_the_whole_tensor():
+    """Kernel B of the 'rows' exchange describes every piece of the plan as a tensor of its own: a piece's own
+    block geometry must select, block for block, what the whole tensor's geometry selects there."""
+    from ista_daslab_optimizers_b200.sharding import block_geometry
     from ista_daslab_optimizers_b200 import synthetic as S
     shapes = S.llama3_8b_shapes()
     lists = [[5000, 3 * DBS + 100, 64, 2 * DBS, DBS, DBS + 1], [int(torch.Size(s).numel()) for s in shapes][:40]]
     for numels in lists:
         for world in (1, 2, 3, 8):
             plan = plan_shards(numels, DBS, 64, world)
-            col, piece_col, rank_cols = plan_row_columns(numels, plan, DBS, 0.01, world)
-            assert col[0] == 0 and all(col[i + 1] - col[i] == block_geometry(n, DBS, 0.01)['k'] for i, n in enumerate(numels))
-            pos = 0
-            for r, (c0, c1) in enumerate(rank_cols):                  # ranks tile [0, sum k) in order
-                if c1 > c0:
-                    assert c0 == pos
-                    pos = c1
-            assert pos == col[-1]
-            for pc in plan:
-                g = block_geometry(numels[pc.index], DBS, 0.01)
-                sg = block_geometry(pc.hi - pc.lo, DBS, 0.01)
-                c0 = piece_col[(pc.index, pc.lo)]
-                assert c0 == col[pc.index] + (pc.lo // g['d_block_size']) * g['k_many']
-                # the slice's own geometry selects as many values per block as the whole tensor does for those blocks
-                end_col = col[pc.index] + (g['k'] if pc.hi == numels[pc.index] else (pc.hi // g['d_block_size']) * g['k_many'])
-                assert c0 + sg['k'] == end_col, (numels[pc.index], pc)
+            for idx, n in enumerate(numels):
+                g = block_geometry(n, DBS, 0.01)
+                pieces = [pc for pc in plan if pc.index == idx]
+                assert sum(block_geometry(pc.hi - pc.lo, DBS, 0.01)['k'] for pc in pieces) == g['k']
+                for pc in pieces:
+                    sg = block_geometry(pc.hi - pc.lo, DBS, 0.01)
+                    assert pc.lo % g['d_block_size'] == 0
+                    first_col = (pc.lo // g['d_block_size']) * g['k_many']
+                    end_col = g['k'] if pc.hi == n else (pc.hi // g['d_block_size']) * g['k_many']
+                    assert first_col + sg['k'] == end_col, (n, pc)
+
+
+def _gather_rows_worker(rank, world, port):
+    from ista_daslab_optimizers_b200.sharding import gather_row_regions
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        row = torch.full((world, 192), -1, dtype=torch.int16)
+        row[rank] = torch.arange(192, dtype=torch.int16) + 1000 * rank
+        got = gather_row_regions(row, rank)
+        assert got == (world - 1) * 192 * 2
+        for r in range(world):
+            assert torch.equal(row[r], torch.arange(192, dtype=torch.int16) + 1000 * r)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_row_regions_gloo_world2():
+    mp.spawn(_gather_rows_worker, args=(2, 29500 + random.randrange(2000)), nprocs=2, join=True)

@@ -50,43 +50,107 @@ def test_sharded_equals_unsharded(name, world):
             assert torch.equal(bits(full.param(pc.index).view(-1)[pc.lo:pc.hi]), bits(params[pc.index].data.view(-1)[pc.lo:pc.hi]))
 
 
-@pytest.mark.parametrize('world', [1, 2, 3])
-@pytest.mark.parametrize('name', ['bf16_wd', 'c1_fp32_1m'])
-def test_row_exchange_equals_unsharded(name, world):
-    """exchange='rows': kernel A sharded, window rows exchanged (copied by hand between the emulated
-    ranks here), kernel B on every rank over all parameters: every rank ends with the unsharded result."""
+def make_rows_ranks(case, world, **extra):
     from ista_daslab_optimizers_b200.sharding import ShardedMicroAdam
-    case = cases.CASES[name]
-    full = cases.CudaAdapter(case, case.params())
     kw = dict(m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init, alpha=case.alpha, betas=case.betas,
               weight_decay=case.weight_decay, eps=case.eps, d_block_size=case.d_block_size)
     ranks = []
     for r in range(world):
         params = [torch.nn.Parameter(p.cuda()) for p in case.params()]
-        ranks.append((params, ShardedMicroAdam(params, rank=r, world_size=world, gather=False, exchange='rows', **kw)))
+        ranks.append((params, ShardedMicroAdam(params, rank=r, world_size=world, gather=False, exchange='rows', **kw, **extra)))
+    return ranks
+
+
+def rows_step(ranks, grads, skip_grad=None):
+    """One step of every emulated rank; the all-gather of the new row is done by hand (region r copied from rank r)."""
+    for r, (params, opt) in enumerate(ranks):
+        for i, (p, g) in enumerate(zip(params, grads)):
+            p.grad = None if skip_grad and (r, i) in skip_grad else g.cuda()
+        opt.steps += 1
+        opt.rows_prepare()
+        opt.rows_phase_a()
+    for r_src, (_, src) in enumerate(ranks):
+        for r_dst, (_, dst) in enumerate(ranks):
+            if r_dst != r_src:
+                dst.current_row()[r_src].copy_(src.current_row()[r_src])
+    for _, opt in ranks:
+        opt.rows_phase_b()
+
+
+def assert_rows_ranks_equal_unsharded(case, full, ranks, t):
+    for params, opt in ranks:
+        for i, p in enumerate(params):
+            assert torch.equal(bits(full.param(i)), bits(p.data)), (t, i)
+    for pc in ranks[0][1].plan:
+        params, opt = ranks[pc.rank]
+        su, sr = full.state(pc.index), opt.state[params[pc.index]]
+        row = (su['index'] - 1) % case.m
+        c0 = (pc.lo // su['d_block_size']) * su['k_block_size_many']
+        assert sr['index'] == su['index']
+        assert torch.equal(su['I'][row, c0:c0 + sr['k']], sr['I'][row]), (t, pc)
+        assert torch.equal(bits(su['V'][row, c0:c0 + sr['k']]), bits(sr['V'][row])), (t, pc)
+        assert torch.equal(su['error'][pc.lo // 2:(pc.hi + 1) // 2], sr['error'])
+    # the window is replicated: every rank holds the same buffer
+    for _, opt in ranks[1:]:
+        assert torch.equal(opt._window, ranks[0][1]._window)
+
+
+@pytest.mark.parametrize('world', [1, 2, 3])
+@pytest.mark.parametrize('name', ['bf16_wd', 'c1_fp32_1m'])
+def test_row_exchange_equals_unsharded(name, world):
+    """exchange='rows': kernel A sharded, window rows exchanged (copied by hand between the emulated
+    ranks here), kernel B on every rank over all parameters: every rank ends with the unsharded result."""
+    case = cases.CASES[name]
+    full = cases.CudaAdapter(case, case.params())
+    ranks = make_rows_ranks(case, world)
     for t in range(case.m + 2):
         grads = case.grads(t)
         full.step(grads)
-        for params, opt in ranks:
-            for p, g in zip(params, grads):
-                p.grad = g.cuda()
-            opt.steps += 1
-            opt.rows_prepare()
-            opt.rows_phase_a()
-        for r_src, (_, src) in enumerate(ranks):
-            for r_dst, (_, dst) in enumerate(ranks):
-                if r_dst != r_src:
-                    for a, b in zip(src.row_views()[r_src], dst.row_views()[r_src]):
-                        b.copy_(a)
-        for params, opt in ranks:
-            opt.rows_phase_b()
-            for i, p in enumerate(params):
-                su, sr = full.state(i), opt.state[p]
-                row = (su['index'] - 1) % case.m
-                assert torch.equal(su['I'][row], sr['I'][row]), (t, i)
-                assert torch.equal(bits(su['V'][row]), bits(sr['V'][row])), (t, i)
-                assert torch.equal(bits(full.param(i)), bits(p.data)), (t, i)
-        for pc in ranks[0][1].plan:
-            params, opt = ranks[pc.rank]
-            su, sr = full.state(pc.index), opt.state[params[pc.index]]
-            assert torch.equal(su['error'][pc.lo // 2:(pc.hi + 1) // 2], sr['error'])
+        rows_step(ranks, grads)
+        assert_rows_ranks_equal_unsharded(case, full, ranks, t)
+
+
+def test_row_exchange_needs_gradients_of_owned_slices_only():
+    """A rank may lack the gradient of a tensor it owns nothing of (kernel B still updates that tensor from the
+    exchanged rows); lacking the gradient of an owned slice is an error, not a silent divergence."""
+    case = cases.CASES['bf16_wd']
+    full = cases.CudaAdapter(case, case.params())
+    ranks = make_rows_ranks(case, 2)
+    plan = ranks[0][1].plan
+    owners = {i: {pc.rank for pc in plan if pc.index == i} for i in range(len(case.shapes))}
+    not_owned = {(r, i) for r in range(2) for i in owners if r not in owners[i]}
+    assert not_owned
+    for t in range(3):
+        grads = case.grads(t)
+        full.step(grads)
+        rows_step(ranks, grads, skip_grad=not_owned)
+        assert_rows_ranks_equal_unsharded(case, full, ranks, t)
+    r, i = next((r, i) for i in owners for r in owners[i])
+    with pytest.raises(RuntimeError, match='no gradient'):
+        rows_step(ranks, case.grads(3), skip_grad={(r, i)})
+
+
+def test_row_exchange_checkpoint_resume():
+    """'rows' mode: save after 3 steps, load into fresh optimizers (fresh parameters restored by the caller),
+    3 more steps: bit-equal with the uninterrupted unsharded run."""
+    case = cases.CASES['bf16_wd']
+    full = cases.CudaAdapter(case, case.params())
+    ranks = make_rows_ranks(case, 2)
+    for t in range(3):
+        grads = case.grads(t)
+        full.step(grads)
+        rows_step(ranks, grads)
+    saved = [(opt.state_dict(), [p.detach().clone() for p in params]) for params, opt in ranks]
+    assert all(sd['ring'] == 3 and sd['steps'] == 3 for sd, _ in saved)
+    fresh = make_rows_ranks(case, 2)
+    for (params, opt), (sd, values) in zip(fresh, saved):
+        for p, v in zip(params, values):
+            p.data.copy_(v)
+        opt.load_state_dict(sd)
+    with pytest.raises(ValueError):
+        fresh[0][1].load_state_dict(saved[1][0])          # the other rank's checkpoint
+    for t in range(3, 6):
+        grads = case.grads(t)
+        full.step(grads)
+        rows_step(fresh, grads)
+        assert_rows_ranks_equal_unsharded(case, full, fresh, t)

@@ -27,11 +27,21 @@ def check_trace(case, tr, ref_digests, ref_samples):
 @pytest.mark.parametrize('name', list(cases.CASES))
 def test_step_matches_golden_and_oracle(name, use_fused, golden):
     case = cases.CASES[name]
-    tr = cases.run_case(case, lambda c, p: cases.CudaAdapter(c, p, use_fused=use_fused))
+    tr = cases.run_case(case, lambda c, p: cases.CudaAdapter(c, p, use_fused=use_fused), keep_params=True)
     g = golden['cases'][name]
     check_trace(case, tr, g['digests'], [[decode_samples(s) for s in step] for step in g['samples']])
-    ref = cases.run_case(case, cases.OracleAdapter)
+    ref = cases.run_case(case, cases.OracleAdapter, keep_params=True)
     check_trace(case, tr, ref.digests, ref.samples)
+    cases.assert_params_close(case, tr, ref)          # every element of every parameter, after every step
+
+
+def test_wide_cases_take_the_wide_update_kernel():
+    """The cases named wide_* must exceed what the per-tile arrays of the update kernel hold, or they test nothing new."""
+    import math
+    for name in ('wide_fp32', 'wide_bf16_wd', 'wide_fp32_alpha'):
+        case = cases.CASES[name]
+        k_many = max(math.ceil(min(int(torch.Size(s).numel()), case.d_block_size) * case.k_init) for s in case.shapes)
+        assert min(case.steps, case.m) * k_many > 16384, name
 
 
 def test_no_kernel_gave_up_a_wait():

@@ -7,9 +7,6 @@ itself (parameters, gradients, optimizer state).  This test drives that entry po
 ABI exactly as such a host would - no workspace tensor is created - and checks it against
 mab_fused_step on identical inputs, for two steps in a row (the second call reuses the built-in
 array, which still holds the first call's table).
-
-The file name makes pytest collect it last, so a run that stops at the first failure has already
-run every other test.
 """
 import ctypes
 
@@ -60,6 +57,45 @@ def test_static_table_step_equals_workspace_step(name):
                 assert torch.equal(a[key].view(torch.uint8) if a[key].dtype != torch.uint8 else a[key],
                                    b[key].view(torch.uint8) if b[key].dtype != torch.uint8 else b[key]), (t, i, key)
             torch.testing.assert_close(new.param(i).float(), ref.param(i).float(), rtol=tol, atol=1e-9)
+    assert N.device_error() == 0
+
+
+def _tiny_optimizer(dtypes, numel, seed):
+    """An optimizer over len(dtypes) tensors of `numel` elements (tensor i of element type dtypes[i]) with gradients."""
+    from ista_daslab_optimizers_b200 import MicroAdam
+    gen = torch.Generator(device='cuda').manual_seed(seed)
+    params = [torch.nn.Parameter(torch.empty(numel, device='cuda').normal_(0, 0.02, generator=gen).to(dt)) for dt in dtypes]
+    grads = [torch.empty(numel, device='cuda').normal_(0, 1e-3, generator=gen).to(dt) for dt in dtypes]
+    opt = MicroAdam(params, m=4, lr=1e-3, quant_block_size=64, k_init=0.05, weight_decay=0.1)
+    return opt, params, grads
+
+
+@pytest.mark.parametrize('layout', ['mixed_types', 'many_tensors'])
+def test_static_table_splits_a_call_into_runs(layout):
+    """One call whose tensors change element type back and forth, and one with more tensors of one type than a
+    launch takes (512): the entry point cuts both into several launches per kernel; results equal mab_fused_step's."""
+    from ista_daslab_optimizers_b200 import _native as N
+    if layout == 'mixed_types':
+        dtypes = [torch.float32, torch.float32, torch.bfloat16, torch.float32, torch.bfloat16, torch.bfloat16, torch.float32]
+        numel = 70000
+    else:
+        dtypes = [torch.float32] * 700
+        numel = 257
+    ref_opt, ref_params, grads = _tiny_optimizer(dtypes, numel, seed=5)
+    new_opt, new_params, _ = _tiny_optimizer(dtypes, numel, seed=5)
+    for t in range(2):
+        for p, q, g in zip(ref_params, new_params, grads):
+            p.grad = g
+            q.grad = g
+        ref_opt.step()
+        static_step(new_opt, N)
+        torch.cuda.synchronize()
+        for i, (p, q) in enumerate(zip(ref_params, new_params)):
+            a, b = ref_opt.state[p], new_opt.state[q]
+            for key in ('I', 'V', 'error', 'min_vals', 'max_vals'):
+                assert torch.equal(a[key].view(torch.uint8) if a[key].dtype != torch.uint8 else a[key],
+                                   b[key].view(torch.uint8) if b[key].dtype != torch.uint8 else b[key]), (t, i, key)
+            assert torch.equal(p.detach(), q.detach()), (t, i)
     assert N.device_error() == 0
 
 
