@@ -115,6 +115,24 @@ int mab_block_topk(int64_t d, int64_t d_block_size, int64_t k_block_size_many, i
 int mab_quant_stats(int64_t d, int64_t quant_block_size, uint16_t* min_vals, uint16_t* max_vals,
                     const void* x, int x_dtype, void* stream);
 
+/* ---- other consumers of the (I, V) ring buffer ---------------------------------------------------- */
+
+/* out[r] = sum_j V[r, j] * g[(j / k_block_size) * d_block_size + I[r, j]] for r < rows: the scalar products of a
+ * dense vector with every sparse row.  I is int16 [rows, k], V is [rows, k] of v_dtype, out is float [rows].
+ * Replaces ista_daslab_cuda_sparse_mfac.SP (sparse_mfac/sparse_core_mfac_w_ef.py:188-203); fp32 accumulation in
+ * a fixed order. */
+int mab_sparse_rows_dot(int64_t d, int64_t rows, int64_t k, int64_t d_block_size, int64_t k_block_size,
+                        const void* g, int g_dtype, const int16_t* I, const void* V, int v_dtype, float* out,
+                        void* stream);
+
+/* out[(j / k_block_size) * d_block_size + I[r, j]] += M[r] * V[r, j] over r < rows, j < k: the linear combination of
+ * the sparse rows with float coefficients M [rows], added to out [d] (the caller zeroes it first).
+ * Replaces ista_daslab_cuda_sparse_mfac.LCG (sparse_mfac/sparse_core_mfac_w_ef.py:205-221); rows are accumulated in
+ * fp32 in row order. */
+int mab_sparse_rows_combine(int64_t d, int64_t rows, int64_t k, int64_t d_block_size, int64_t k_block_size,
+                            const float* M, const int16_t* I, const void* V, int v_dtype, void* out, int out_dtype,
+                            void* stream);
+
 /* ---- fused step over a list of tensors ------------------------------------------------------ */
 
 /* One parameter tensor of the step.  State buffers have the shapes micro_adam.py:86-94 gives them. */

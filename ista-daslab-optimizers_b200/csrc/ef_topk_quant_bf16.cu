@@ -13,6 +13,15 @@
 // blocks t, t + 256; no shuffles).  For quant_block_size 64 the block tables fit the scratch; other
 // block sizes take general per-block code in the same kernel.
 //
+// Regular tiles (whole blocks of 64, every thread with 14 whole octets, all blocks with a finite
+// positive step) take a leaner route: the decode writes a into the tile with the octets of every
+// 128-byte row (= one quantisation block) permuted by the row number (octet o sits at o ^ ((o >> 3) & 7)),
+// so that afterwards a thread can own whole blocks - consecutive lanes own consecutive blocks and read
+// different banks - and computes a block's statistics, its constants and its 32 code bytes from
+// registers, with no tables and no shuffles.  The selection addresses the tile through the same
+// permutation.  Everything else (other block sizes, ragged tiles, degenerate blocks) keeps the
+// linear layout and the general code.
+//
 // Results are bit-identical to the register-resident kernel in ef_topk_quant.cu (same arithmetic,
 // same tie rule); that kernel keeps serving fp32 gradients.
 #include "common.cuh"
@@ -147,14 +156,47 @@ __device__ __forceinline__ void store_code_word(uint8_t* ef_g, bool aligned4, in
     for (int b = 0; b < 4; ++b) if (o * 8 + 2 * b < n) ef_g[o * 4 + b] = (uint8_t)(w >> (8 * b));
 }
 
+// Where octet o of the tile sits: rows of 8 octets are permuted by the row number on regular tiles.
+__device__ __forceinline__ int phys_oct(int o, bool swz) { return swz ? (o ^ ((o >> 3) & 7)) : o; }
+__device__ __forceinline__ int phys_pos(int pos, bool swz) { return (phys_oct(pos >> 3, swz) << 3) | (pos & 7); }
+
+// Codes of one octet of bf16 values r (statistics = their exact block minimum and maximum, u in
+// [2^-100, 2^100]): the defining floor(RN(RN((r - mn) / u) + 0.5)) itself, two elements per instruction and
+// without the division and conversion instructions.  The IEEE quotient comes from the correctly rounded
+// reciprocal r0 = RN(1 / u): q = RN(d * r0) is within 1.5 ulp of d / u, one residual correction
+// q <- RN(q + RN(d - q * u) * r0) (the residual is exact in an FMA) makes it faithful, and a second one
+// makes it the correctly rounded quotient (Markstein's theorem on the final step of a division).  Values far
+// below half a step, where the residual could underflow, get code 0 from any quotient below 0.5.
+// floor: adding 2^23 with rounding down leaves the integer in the low mantissa bits.
+__device__ __forceinline__ uint32_t encode_octet_div(const uint4& v, float2 nmn2, float2 r02, float2 nu2) {
+    const float2 half2 = make_float2(0.5f, 0.5f), magic2 = make_float2(8388608.0f, 8388608.0f);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t y[8];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const float2 r = make_float2(__uint_as_float(w[p] << 16), __uint_as_float(w[p] & 0xFFFF0000u));
+        const float2 d = __fadd2_rn(r, nmn2);                               // r - mn
+        float2 q = __fmul2_rn(d, r02);
+        q = __ffma2_rn(__ffma2_rn(q, nu2, d), r02, q);
+        q = __ffma2_rn(__ffma2_rn(q, nu2, d), r02, q);                      // RN(d / u)
+        const float2 f = __fadd2_rd(__fadd2_rn(q, half2), magic2);          // 2^23 + floor(q + 0.5)
+        y[2 * p] = __float_as_uint(f.x); y[2 * p + 1] = __float_as_uint(f.y);
+    }
+    // byte 0 of every float is the code; even elements go to the high nibbles
+    const uint32_t ev = __byte_perm(__byte_perm(y[0], y[2], 0x0040), __byte_perm(y[4], y[6], 0x0040), 0x5410);
+    const uint32_t od = __byte_perm(__byte_perm(y[1], y[3], 0x0040), __byte_perm(y[5], y[7], 0x0040), 0x5410);
+    return (ev << 4) | od;
+}
+
 constexpr int S_GROUP = 2;                   // octets whose instructions the compiler may interleave (register pressure)
 constexpr int S_FULL = 14;                   // 29 056 values = 3632 octets: every thread has 14 whole octets, some a 15th
 
 // One octet of a = bf16(g + Qinv(e)) in place (positions >= n of a ragged tile stay zero); returns the
 // largest |a| of the octet.
 // RAGGED = false promises a whole octet; `commit` = false computes but leaves the tile as it is.
+// The result goes to octet o_out of the tile (o itself, or its permuted place on a regular tile).
 template <bool FAST, bool RAGGED>
-__device__ __forceinline__ float dequant_octet(uint4* tile4, int o, int n, uint32_t codes, const QParams& q, const DecodeConsts& dc, bool commit) {
+__device__ __forceinline__ float dequant_octet(uint4* tile4, int o, int o_out, int n, uint32_t codes, const QParams& q, const DecodeConsts& dc, bool commit) {
     float gv[8], x[8];
     unpack8(tile4[o], gv);
     if (FAST) decode_octet_fast(codes, dc, x);
@@ -173,7 +215,7 @@ __device__ __forceinline__ float dequant_octet(uint4* tile4, int o, int n, uint3
             if (e0 + 1 >= n) ow[p] = (e0 >= n) ? 0u : (ow[p] & 0xFFFFu);
         }
     }
-    if (commit) tile4[o] = out;
+    if (commit) tile4[o_out] = out;
     const uint32_t m2 = maxabs_bf16x2(maxabs_bf16x2(ow[0], ow[1]), maxabs_bf16x2(ow[2], ow[3]));
     return fmaxf(fabsf(__uint_as_float(m2 << 16)), fabsf(__uint_as_float(m2 & 0xFFFF0000u)));
 }
@@ -195,7 +237,7 @@ __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, b
             const float2 c = ss.qt.mu[o >> 3];
             const QParams q = {c.x, c.y};
             const DecodeConsts dc = decode_consts(q);
-            const float m = dequant_octet<true, false>(tile4, o, n, cw[j], q, dc, dc.fast);
+            const float m = dequant_octet<true, false>(tile4, o, o, n, cw[j], q, dc, dc.fast);
             omax[j] = dc.fast ? m : 0.0f;
             slow |= dc.fast ? 0u : (1u << j);
         } else if (o < n_oct) {
@@ -204,7 +246,7 @@ __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, b
             else q = qparams(mn_g[o >> cshift], mx_g[o >> cshift]);
             const DecodeConsts dc = decode_consts(q);
             if (!dc.fast) slow |= 1u << j;
-            else omax[j] = dequant_octet<true, true>(tile4, o, n, cw[j], q, dc, true);
+            else omax[j] = dequant_octet<true, true>(tile4, o, o, n, cw[j], q, dc, true);
         }
     }
     if (slow) {
@@ -213,8 +255,86 @@ __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, b
             if ((slow >> j) & 1u) {
                 const int o = t + j * S_NT;
                 const QParams q = qparams(mn_g[o >> cshift], mx_g[o >> cshift]);
-                omax[j] = dequant_octet<false, true>(tile4, o, n, cw[j], q, decode_consts(q), true);
+                omax[j] = dequant_octet<false, true>(tile4, o, o, n, cw[j], q, decode_consts(q), true);
             }
+        }
+    }
+}
+
+// The same on a regular tile (see the head of the file): every block's decode is the fast one, the
+// first S_FULL octets of every thread exist, and octet o is written to its permuted place.  The 8
+// lanes that hold a 128-byte row read it in one instruction and write it in a later one, so the
+// permutation inside the row happens in place.
+__device__ __forceinline__ void dequant_phase_regular(uint4* tile4, const SmemSel& ss, int n_oct, const uint32_t (&cw)[S_SLOTS], float (&omax)[S_SLOTS]) {
+    const int t = threadIdx.x;
+    const int t_out = t ^ ((t >> 3) & 7);                   // phys_oct(t + j * S_NT) = t_out + j * S_NT
+#pragma unroll
+    for (int j = 0; j < S_SLOTS; ++j) {
+        omax[j] = 0.0f;
+        const int o = t + j * S_NT;
+        if (j < S_FULL || o < n_oct) {
+            if (j < S_FULL && j % S_GROUP == 0) asm volatile("" ::: "memory");
+            const float2 c = ss.qt.mu[o >> 3];
+            const QParams q = {c.x, c.y};
+            omax[j] = dequant_octet<true, false>(tile4, o, t_out + j * S_NT, 0, cw[j], q, decode_consts(q), true);
+        }
+    }
+}
+
+// Codes of one block of a regular tile with the scalar form of the quantiser: the rare blocks whose step is
+// zero (all values equal), subnormal or infinite.  Kept out of line so that the common path stays small.
+__device__ __noinline__ void encode_block_exact(const uint4* row, int key, uint16_t mn_b, uint16_t mx_b, uint8_t* dst) {
+    const QParams q2 = qparams(mn_b, mx_b);
+    for (int c = 0; c < 8; ++c) {
+        float r[8];
+        unpack8(row[c ^ key], r);
+        reinterpret_cast<uint32_t*>(dst)[c] = encode_octet_exact(r, q2, 8);
+    }
+}
+
+// Statistics and codes of the residual on a regular tile: thread t owns blocks t, t + S_NT, ...; a
+// block is one 128-byte row of the tile whose octet c sits at c ^ (row & 7), and row & 7 = t & 7.
+// Writes the block's bf16 minimum / maximum and its 32 code bytes (ef_out is 4-byte aligned).
+__device__ __forceinline__ void stats_encode_regular(const uint4* tile4, int n_qb, uint16_t* mn_out, uint16_t* mx_out, uint8_t* ef_out, bool ef_al16) {
+    const int t = threadIdx.x;
+    const int key = t & 7;
+    for (int b = t; b < n_qb; b += S_NT) {
+        const uint4* row = tile4 + (b << 3);
+        uint32_t hi2 = 0xFF80FF80u, lo2 = 0x7F807F80u;      // running packed max (from -inf) and min (from +inf)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const uint4 v = row[c ^ key];
+            hi2 = max_bf16x2(max_bf16x2(hi2, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
+            lo2 = min_bf16x2(min_bf16x2(lo2, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
+        }
+        hi2 = max_bf16x2(hi2, hi2 >> 16);
+        lo2 = min_bf16x2(lo2, lo2 >> 16);
+        const uint16_t mn_b = (uint16_t)(lo2 & 0xFFFFu), mx_b = (uint16_t)(hi2 & 0xFFFFu);
+        mn_out[b] = mn_b; mx_out[b] = mx_b;
+        const QParams q2 = qparams(mn_b, mx_b);
+        uint8_t* dst = ef_out + ((size_t)b << 5);
+        if (!(q2.u >= CODEC_U_MIN && q2.u <= CODEC_U_MAX)) {   // all-equal block (u == 0), subnormal or infinite step
+            encode_block_exact(row, key, mn_b, mx_b, dst);
+            continue;
+        }
+        const float r0 = __frcp_rn(q2.u);
+        const float2 nmn2 = make_float2(-q2.mn, -q2.mn), r02 = make_float2(r0, r0), nu2 = make_float2(-q2.u, -q2.u);
+        uint4 lo4, hi4;
+        lo4.x = encode_octet_div(row[0 ^ key], nmn2, r02, nu2);
+        lo4.y = encode_octet_div(row[1 ^ key], nmn2, r02, nu2);
+        lo4.z = encode_octet_div(row[2 ^ key], nmn2, r02, nu2);
+        lo4.w = encode_octet_div(row[3 ^ key], nmn2, r02, nu2);
+        hi4.x = encode_octet_div(row[4 ^ key], nmn2, r02, nu2);
+        hi4.y = encode_octet_div(row[5 ^ key], nmn2, r02, nu2);
+        hi4.z = encode_octet_div(row[6 ^ key], nmn2, r02, nu2);
+        hi4.w = encode_octet_div(row[7 ^ key], nmn2, r02, nu2);
+        if (ef_al16) {
+            reinterpret_cast<uint4*>(dst)[0] = lo4;
+            reinterpret_cast<uint4*>(dst)[1] = hi4;
+        } else {
+            uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
+            d32[0] = lo4.x; d32[1] = lo4.y; d32[2] = lo4.z; d32[3] = lo4.w;
+            d32[4] = hi4.x; d32[5] = hi4.y; d32[6] = hi4.z; d32[7] = hi4.w;
         }
     }
 }
@@ -258,12 +378,13 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
     SmemSel& ss = *reinterpret_cast<SmemSel*>(smem_raw + ((stage_elems * 2 + 127) & ~127));
     const int t = threadIdx.x, lane = lane_id(), warp = warp_id();
     for (int i = t; i < n_tensors; i += S_NT) s_first[i] = tensors[i].first_unit_a;
-    if (t == 0) { s_first[n_tensors] = total_units; mbar_init(&s_bar, 1); }
+    if (t == 0) { s_first[n_tensors] = total_units; mbar_init(&s_bar, 1); ss.ctrl[5] = 0; ss.ctrl[6] = 0; }
     __syncthreads();
     const int cshift = qshift - 3;              // octets per quantisation block, as a shift
     const int cpq = 1 << cshift;
     uint32_t parity = 0;
     int guess = 0;
+    int tile_no = 0;                            // tiles this CTA has worked on: selects one of two "a block needs the slow decode" flags
     int ti_next = -1;                           // tensor of the next unit, found while prefetching it
     const uint16_t* g_next = nullptr;           // ... and its gradient tile, so that its copy can start before its descriptor is read again
     int n_next = 0;
@@ -300,7 +421,9 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         MAB_CTICK_DECL
         // ---- bring the tile in; meanwhile codes -> registers, decode constants -> table ---------------------
         // (selection scratch is cleared here: the barrier that ends the load publishes it)
-        if (t == 0) { ss.kmax = 0; ss.n_member = 0; ss.n_cand = 0; ss.ctrl[4] = 0; }
+        const int slow_slot = 5 + (tile_no & 1);             // set during this tile's load; the other one is cleared for the next tile
+        ++tile_no;
+        if (t == 0) { ss.kmax = 0; ss.n_member = 0; ss.n_cand = 0; ss.ctrl[4] = 0; ss.ctrl[slow_slot ^ 3] = 0; }
         if (t < 64) ss.rot[t] = 0;
         ss.hist[t] = 0;
         reinterpret_cast<uint4*>(ss.sel_bm)[t] = make_uint4(0u, 0u, 0u, 0u);
@@ -332,8 +455,10 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             const int b0 = t, b1 = t + S_NT;
             const uint16_t mn0 = b0 < n_qb ? mn_g[b0] : (uint16_t)0, mx0 = b0 < n_qb ? mx_g[b0] : (uint16_t)0;
             const uint16_t mn1 = b1 < n_qb ? mn_g[b1] : (uint16_t)0, mx1 = b1 < n_qb ? mx_g[b1] : (uint16_t)0;
-            if (b0 < n_qb) { const QParams q = qparams(mn0, mx0); ss.qt.mu[b0] = make_float2(q.mn, q.u); }
-            if (b1 < n_qb) { const QParams q = qparams(mn1, mx1); ss.qt.mu[b1] = make_float2(q.mn, q.u); }
+            bool slow = false;
+            if (b0 < n_qb) { const QParams q = qparams(mn0, mx0); ss.qt.mu[b0] = make_float2(q.mn, q.u); slow |= !decode_consts(q).fast; }
+            if (b1 < n_qb) { const QParams q = qparams(mn1, mx1); ss.qt.mu[b1] = make_float2(q.mn, q.u); slow |= !decode_consts(q).fast; }
+            if (slow) ss.ctrl[slow_slot] = 1;
         }
         if (staged) {
             const bool ok = mbar_wait(&s_bar, parity);
@@ -369,7 +494,9 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
 
         // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
         float omax[S_SLOTS];
-        if (tables && (n & 7) == 0 && n_oct >= S_FULL * S_NT) dequant_phase<S_FULL>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax);
+        // regular tile: whole blocks of 64, 14 whole octets per thread, aligned codes, every block with the fast decode
+        const bool swz = tables && (n & 63) == 0 && n_oct >= S_FULL * S_NT && ef_al4 && ss.ctrl[slow_slot] == 0;
+        if (swz) dequant_phase_regular(tile4, ss, n_oct, cw, omax);
         else dequant_phase<0>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax);
 
         MAB_CTICK(1);
@@ -447,7 +574,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                         const int e = e0 + h * 32 + lane;
                         if (e < n_w) {
                             o2[h] = wlist[e];
-                            const uint4 v = tile4[o2[h]];
+                            const uint4 v = tile4[phys_oct(o2[h], swz)];
                             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                             for (int p = 0; p < 4; ++p) {
@@ -463,7 +590,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                         while (mask) {
                             const uint32_t pos = (o2[h] << 3) + (__ffs(mask) - 1);
                             mask &= mask - 1;
-                            if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(tile[pos] & 0x7FFFu) << 16) | (0xFFFFu - pos);
+                            if (slot < S_CAND_CAP) ss.cand[slot] = ((uint32_t)(tile[phys_pos(pos, swz)] & 0x7FFFu) << 16) | (0xFFFFu - pos);
                             ++slot;
                         }
                     }
@@ -577,7 +704,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                     const int o = (t * S_WPT + i) * 4 + b;
                     if (o < n_oct) {
                         float v[8];
-                        unpack8(tile4[o], v);
+                        unpack8(tile4[phys_oct(o, swz)], v);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) {
                             const bool valid = o * 8 + e < n;     // padding never competes, whatever the threshold
@@ -598,9 +725,10 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                 if (c >= Tc_sel) {
                     const uint32_t q = 0xFFFFu - (c & 0xFFFFu), w = q >> 5;
                     const int rank = ss.sel_before[w] + __popc(ss.sel_bm[w] & ((1u << (q & 31)) - 1u));
+                    const int at = phys_pos(q, swz);
                     i_out[rank] = (int16_t)q;
-                    v_out[rank] = tile[q];
-                    tile[q] = 0;
+                    v_out[rank] = tile[at];
+                    tile[at] = 0;
                 }
             }
         } else {
@@ -613,9 +741,10 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
                     const int b = __ffs(sel) - 1;
                     sel &= sel - 1;
                     const int q = (w0 + i) * 32 + b;
+                    const int at = phys_pos(q, swz);
                     i_out[p] = (int16_t)q;
-                    v_out[p++] = tile[q];
-                    tile[q] = 0;
+                    v_out[p++] = tile[at];
+                    tile[at] = 0;
                 }
             }
         }
@@ -625,7 +754,10 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // ---- statistics and codes of the residual ----------------------------------------------------------
         uint16_t* mn_out = T.min_vals + qb0;
         uint16_t* mx_out = T.max_vals + qb0;
-        if (tables && (n & 63) == 0) {
+        if (swz) {
+            stats_encode_regular(tile4, n_qb, mn_out, mx_out, ef_out, (reinterpret_cast<uintptr_t>(ef_out) & 15) == 0);
+            __syncthreads();                                 // the tile is overwritten by the next load
+        } else if (tables && (n & 63) == 0) {
             // whole blocks of 64: statistics block by block (a thread's 8 octets, rotated so that a warp's
             // 16-byte reads spread over the banks), constants to the tables, then codes octet by octet
             for (int b = t; b < n_qb; b += S_NT) {
@@ -647,8 +779,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             }
             __syncthreads();
             uint32_t redo = 0u;                              // octets too close to a code boundary, or of a degenerate block
-            if ((n & 7) == 0 && n_oct >= S_FULL * S_NT && ef_al4) encode_phase<S_FULL>(tile4, ss, ef_out, ef_al4, n, n_oct, redo);
-            else encode_phase<0>(tile4, ss, ef_out, ef_al4, n, n_oct, redo);
+            encode_phase<0>(tile4, ss, ef_out, ef_al4, n, n_oct, redo);
             while (redo) {
                 const int j = __ffs(redo) - 1;
                 redo &= redo - 1;

@@ -307,12 +307,13 @@ __device__ __forceinline__ float adam_update_fast(float m, float v, float inv_bc
 }
 
 // Asks L2 for one unit's slices of the valid window rows: one thread per row slice of I or V.
-__device__ __forceinline__ void prefetch_window_rows(const mab_tensor& T, int blk, int rows) {
-    if ((int)threadIdx.x < 2 * rows) {
+// `who` = index of the calling thread among those that ask (the first 2 * rows of them do).
+__device__ __forceinline__ void prefetch_window_rows(const mab_tensor& T, int blk, int rows, int who) {
+    if (who < 2 * rows) {
         const int kcnt = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
-        const int r = threadIdx.x >> 1;
-        const int64_t off = (int64_t)blk * T.k_block_size_many + (int64_t)r * T.k;
-        const uintptr_t base = (threadIdx.x & 1) ? reinterpret_cast<uintptr_t>(T.V + off) : reinterpret_cast<uintptr_t>(T.I + off);
+        const int r = who >> 1;
+        const int64_t off = (int64_t)blk * T.k_block_size_many + (int64_t)r * row_pitch_of(T);
+        const uintptr_t base = (who & 1) ? reinterpret_cast<uintptr_t>(T.V + off) : reinterpret_cast<uintptr_t>(T.I + off);
         const uintptr_t end = base + 2u * kcnt;
         for (uintptr_t line = base & ~(uintptr_t)127; line < end; line += 128)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
@@ -358,6 +359,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     const int E = rows * kcnt;
     const float inv_kcnt = 1.0f / (float)kcnt;
     const int chunks_per_row = w.rstride >> 4;
+    MAB_BTICK_DECL
     // 1. stage the window entries: every row's slice of I and of V is copied asynchronously in
     //    16-byte pieces from the 16-byte boundary below its first element; meanwhile clear the
     //    bitmap and the compact moments
@@ -390,6 +392,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     for (int i = t; i < E; i += NT) w.mv[i] = make_float2(0.0f, 0.0f);
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    MAB_BTICK(0);
     // entry i = (row r, column j): its position sits at raw + 2r * rstride + (address of the row's slice & 15) + 2j
     auto pos_ptr = [&](int i) -> uint16_t* {
         const int r = (int)(((float)i + 0.5f) * inv_kcnt), j = i - r * kcnt;
@@ -402,6 +405,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
         if (pos < (uint32_t)n_blk) atomicOr(&w.bitmap[pos >> 5], 1u << (pos & 31));
     }
     __syncthreads();
+    MAB_BTICK(1);
     // 3. number them: prefix[word] = touched positions in words below
     constexpr int WPT = WT_WORDS / NT;
     int cnt[WPT], local = 0;
@@ -412,6 +416,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
 #pragma unroll
     for (int i = 0; i < WPT; ++i) { w.prefix[t * WPT + i] = (uint16_t)run; run += cnt[i]; }
     __syncthreads();
+    MAB_BTICK(2);
     // 4. positions -> slots (in place), then accumulate row after row
     for (int i = t; i < E; i += NT) {
         uint16_t* pp = pos_ptr(i);
@@ -425,6 +430,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
         }
     }
     __syncthreads();
+    MAB_BTICK(3);
     for (int r = 0; r < rows; ++r) {
         const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r]);
         const uint16_t* val_r = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r]);
@@ -440,13 +446,14 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
         }
         __syncthreads();
     }
+    MAB_BTICK(4);
     return touched;
 }
 
 template <typename TP, int MODE, bool ALPHA>
 __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  int max_k, const WindowArgs& a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_first[WIN_MAX_TENSORS + 1];
     __shared__ int s_scan[36];
     __shared__ int s_pos_off[MAB_MAX_WINDOW], s_val_off[MAB_MAX_WINDOW];   // byte offsets of each row's first position / value in raw
@@ -471,7 +478,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
             if (unit + (int)gridDim.x < total_units) {
                 const int nu = unit + gridDim.x;
                 const int nti = find_tensor(s_first, n_tensors, nu);
-                prefetch_window_rows(tensors[nti], nu - s_first[nti], rows);
+                prefetch_window_rows(tensors[nti], nu - s_first[nti], rows, threadIdx.x);
             }
             // this block's parameters travel to L2 while the window is worked on
             prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
@@ -481,7 +488,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
 
         MAB_BTICK_DECL
         const int touched = window_tile_moments<WT_THREADS>(T, blk, n_blk, kcnt, a, w, s_scan, s_pos_off, s_val_off);
-        MAB_BTICK(4);
+        MAB_BTICK(9);
         // 5. moments -> update (rounded to the gradient's element type), slot by slot
         for (int s = t; s < touched; s += WT_THREADS) {
             const float2 acc = w.mv[s];
@@ -599,12 +606,12 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
         if (unit + (int)gridDim.x < total_units) {                              // the next unit's window rows: into L2
             const int nu = unit + gridDim.x;
             const int nti = find_tensor(s_first, n_tensors, nu);
-            prefetch_window_rows(tensors[nti], nu - s_first[nti], rows);
+            prefetch_window_rows(tensors[nti], nu - s_first[nti], rows, threadIdx.x);
         }
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
         const bool g_bf16 = (T.grad_dtype == MAB_BF16);
         const int touched = window_tile_moments<WR_THREADS>(T, blk, n_blk, kcnt, a, w, s_scan, s_pos_off, s_val_off);
-        MAB_BTICK(4);
+        MAB_BTICK(9);
 
         // the tile: wait for the bulk copy, or fetch a ragged block (a tensor's last one, an unaligned slice) with plain loads
         if (bulk) {
@@ -673,7 +680,7 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
 template <typename TP, int MODE, bool ALPHA>
 __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  const WindowArgs& a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ int s_first[WIN_MAX_TENSORS + 1];
     WindowSmem sm(smem_raw);
     for (int i = threadIdx.x; i < n_tensors; i += WIN_THREADS) s_first[i] = tensors[i].first_unit_b;
@@ -726,8 +733,10 @@ template <typename TP, int MODE, bool ALPHA>
 static int launch_window_impl(const mab_tensor* dev_tensors, const mab_tensor* single, int n_tensors, int units_tile,
                               int units_wide, int max_k, const WindowArgs& a, cudaStream_t s) {
     const int sms = device_sm_count();
-    if ((int64_t)a.rows * max_k <= WT_MAX_ENTRIES) {
-        const int smem = wt_smem_bytes(a.rows, max_k);
+    // the tile variant while its compact arrays fit one CTA's shared memory (next to the kernel's static arrays)
+    const int smem_tile = (int64_t)a.rows * max_k <= WT_MAX_ENTRIES ? wt_smem_bytes(a.rows, max_k) : 0;
+    if (smem_tile > 0 && smem_tile + 4096 <= device_max_optin_smem()) {
+        const int smem = smem_tile;
         const int per_sm = std::max(1, std::min(8, (227 * 1024) / (smem + 3072)));
         const int grid = (int)std::min<int64_t>(units_tile, (int64_t)sms * per_sm);
         if (single) {

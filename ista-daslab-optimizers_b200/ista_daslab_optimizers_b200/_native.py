@@ -69,6 +69,8 @@ SIGNATURES = {
                                              c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     'mab_block_topk': (c_int, [c_int64, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p]),
     'mab_quant_stats': (c_int, [c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    'mab_sparse_rows_dot': (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    'mab_sparse_rows_combine': (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     'mab_fused_step_workspace_bytes': (c_int64, [c_int]),
     'mab_fused_supported': (c_int, [POINTER(MabTensor), POINTER(MabStepArgs)]),
     'mab_fused_step': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),
@@ -198,3 +200,19 @@ def block_topk(d, d_block_size, k_block_size_many, k_block_size_few, x, indices_
 def quant_stats(d, quant_block_size, min_vals, max_vals, x):
     _run(x, 'quant_stats', load().mab_quant_stats, d, quant_block_size, dev_ptr(min_vals, 'min_vals'),
          dev_ptr(max_vals, 'max_vals'), dev_ptr(x, 'x'), dtype_code(x))
+
+
+def sparse_rows_dot(d, rows, k, d_block_size, k_block_size, g, I, V, out):
+    """out[r] = <row r of the sparse buffer, g> (ista_daslab_cuda_sparse_mfac.SP, sparse_core_mfac_w_ef.py:188-203)."""
+    if out.dtype != torch.float32:
+        raise NativeError('sparse_rows_dot writes float32 scalar products')
+    _run(g, 'sparse_rows_dot', load().mab_sparse_rows_dot, d, rows, k, d_block_size, k_block_size, dev_ptr(g, 'g'), dtype_code(g),
+         dev_ptr(I, 'I'), dev_ptr(V, 'V'), dtype_code(V), dev_ptr(out, 'out'))
+
+
+def sparse_rows_combine(d, rows, k, d_block_size, k_block_size, M, I, V, out):
+    """out += sum_r M[r] * row r of the sparse buffer (ista_daslab_cuda_sparse_mfac.LCG, sparse_core_mfac_w_ef.py:205-221)."""
+    if M.dtype != torch.float32:
+        raise NativeError('sparse_rows_combine takes float32 coefficients')
+    _run(out, 'sparse_rows_combine', load().mab_sparse_rows_combine, d, rows, k, d_block_size, k_block_size, dev_ptr(M, 'M'),
+         dev_ptr(I, 'I'), dev_ptr(V, 'V'), dtype_code(V), dev_ptr(out, 'out'), dtype_code(out))

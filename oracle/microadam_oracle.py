@@ -218,6 +218,26 @@ def zerorize_block_components(x, indices, d, k, d_block_size, k_block_size):
     x[_global_index(indices, d_block_size, k_block_size)] = 0
 
 
+# ----------------------------------------------------------------------------- other consumers of (I, V)
+
+def sparse_rows_dot(d, rows, k, d_block_size, k_block_size, g, I, V, out):
+    """out[r] = sum_j V[r, j] * g[(j // k_block_size) * d_block_size + I[r, j]]
+    (native SP, sparse_mfac/sparse_core_mfac_w_ef.py:188-203).  Checked to a tolerance (the sum order is free)."""
+    for r in range(rows):
+        gi = _global_index(I[r], d_block_size, k_block_size)
+        out[r] = torch.dot(V[r].double(), g[gi].double()).float()
+
+
+def sparse_rows_combine(d, rows, k, d_block_size, k_block_size, M, I, V, out):
+    """out[...] += sum_r M[r] * V[r, :] at the rows' positions, rows in order, fp32
+    (native LCG, sparse_mfac/sparse_core_mfac_w_ef.py:205-221)."""
+    acc = torch.zeros(d, dtype=torch.float32)
+    for r in range(rows):
+        gi = _global_index(I[r], d_block_size, k_block_size)
+        acc[gi] = torch.add(acc[gi], torch.mul(V[r].float(), M[r]))
+    out.copy_(torch.add(out.float(), acc))
+
+
 # ----------------------------------------------------------------------------- window / Adam
 
 def adam_tables(steps: int, m: int, beta1: float, beta2: float):

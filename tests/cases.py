@@ -156,13 +156,24 @@ def run_case(case: Case, make: Callable[[Case, List[torch.Tensor]], Adapter], ke
     return tr
 
 
+def param_tolerances(dtype: torch.dtype, lr: float):
+    """(rtol, atol) for parameters: rel 1e-5 (fp32) / 1e-2 (bf16), the tolerance the path's specification states.
+    A new parameter is p - lr * u, so where |p| is close to lr * |u| the result is what is left of a cancellation
+    and its error is relative to the operands, not to the result: atol = rtol * lr * 4, 4 standing for the largest
+    |u| (an Adam update is bounded by (1 - beta1) / sqrt(1 - beta2) = 3.2 for the default betas).  (It shows on a
+    few elements per million: torch's CPU kernels round the scalar of add_(.., alpha=-lr) to bf16 for bf16 tensors,
+    torch's CUDA kernels and this library keep it in fp32, and p = bf16(lr) then gives 0 against -5e-7.)"""
+    rtol = 1e-5 if dtype == torch.float32 else 1e-2
+    return rtol, rtol * lr * 4
+
+
 def assert_params_close(case: Case, got: Trace, want: Trace):
-    """Every parameter element after every step: rel 1e-5 (fp32) / 1e-2 (bf16), the tolerance the path's specification states."""
-    tol = 1e-5 if case.dtype == torch.float32 else 1e-2
+    """Every parameter element after every step."""
+    rtol, atol = param_tolerances(case.dtype, case.lr)
     assert len(got.params) == len(want.params) == case.steps
     for step, (mine, theirs) in enumerate(zip(got.params, want.params)):
         for i, (a, b) in enumerate(zip(mine, theirs)):
-            torch.testing.assert_close(a, b, rtol=tol, atol=1e-9, msg=lambda m: f'step {step}, tensor {i}: {m}')
+            torch.testing.assert_close(a, b, rtol=rtol, atol=atol, msg=lambda m: f'step {step}, tensor {i}: {m}')
 
 
 class OracleAdapter(Adapter):

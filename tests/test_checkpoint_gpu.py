@@ -66,14 +66,14 @@ def test_reference_written_checkpoint_loads_and_continues():
         st = fx['state_dict']['state'][i]
         ref.state[i] = dict(geo=Geometry.make(p.numel(), case.d_block_size, case.k_init, case.qbs), index=st['index'],
                             **{k: st[k].clone() for k in STATE_DTYPES})
-    tol = 1e-5
+    rtol, atol = cases.param_tolerances(case.dtype, case.lr)
     for t in range(3, 6):
         grads = case.grads(t)
         gpu.step(grads)
         ref.step([g.clone() for g in grads])
         for i in range(len(case.shapes)):
             assert_same_state(gpu.state(i), ref.state[i])
-            torch.testing.assert_close(gpu.param(i).cpu(), cpu_params[i], rtol=tol, atol=1e-9)
+            torch.testing.assert_close(gpu.param(i).cpu(), cpu_params[i], rtol=rtol, atol=atol)
 
 
 def test_indices_saved_in_another_element_type_are_restored():

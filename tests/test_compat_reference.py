@@ -42,7 +42,7 @@ def test_unmodified_reference_file_runs_on_the_kernels(name):
     opt = Ref(params, m=case.m, lr=case.lr, quant_block_size=case.qbs, k_init=case.k_init, alpha=case.alpha,
               betas=case.betas, weight_decay=case.weight_decay, eps=case.eps)
     oracle = cases.OracleAdapter(case, case.params())
-    tol = 1e-5 if case.dtype == torch.float32 else 1e-2
+    rtol, atol = cases.param_tolerances(case.dtype, case.lr)
     for t in range(3):
         grads = case.grads(t)
         for p, g in zip(params, grads):
@@ -59,4 +59,4 @@ def test_unmodified_reference_file_runs_on_the_kernels(name):
             if a['k_block_size_few'] > 0:
                 assert torch.equal(got[a['k_index']:].sort().values, want[a['k_index']:])
             assert torch.equal(a['error'].cpu(), b['error'])
-            torch.testing.assert_close(p.detach().cpu().float(), oracle.param(i).float(), rtol=tol, atol=1e-9)
+            torch.testing.assert_close(p.detach().cpu().float(), oracle.param(i).float(), rtol=rtol, atol=atol)

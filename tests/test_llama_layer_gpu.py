@@ -10,6 +10,8 @@ for bit and every parameter element to the bf16 tolerance.
 import pytest
 import torch
 
+import cases
+
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336), (4096,), (4096,)]
@@ -45,6 +47,7 @@ def test_llama_layer_matches_oracle():
             used = (p.numel() + qbs - 1) // qbs
             for key in ('min_vals', 'max_vals'):
                 assert torch.equal(a[key][:used].cpu().view(torch.int16), b[key][:used].view(torch.int16)), (t, i, key)
-            torch.testing.assert_close(p.detach().cpu().float(), cpu_params[i].float(), rtol=1e-2, atol=1e-9,
+            rtol, atol = cases.param_tolerances(torch.bfloat16, HYPER['lr'])
+            torch.testing.assert_close(p.detach().cpu().float(), cpu_params[i].float(), rtol=rtol, atol=atol,
                                        msg=lambda m: f'step {t}, tensor {i}: {m}')
     assert _native.device_error() == 0

@@ -137,6 +137,37 @@ def test_compute_microadam_update(N, dtype, m, k_init):
             assert ((out == 0) == (outg.cpu() == 0)).all()
 
 
+@pytest.mark.parametrize('vdtype', [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize('gdtype', [torch.float32, torch.bfloat16])
+def test_sparse_rows_dot_and_combine(N, gdtype, vdtype):
+    """The Sparse M-FAC consumers of the ring buffer (scalar products with every row, linear combination of the rows)."""
+    m, k_init = 6, 0.02
+    for d in [100, 4096, DBS, 2 * DBS + 777]:
+        geo = O.Geometry.make(d, DBS, k_init, 64)
+        I = torch.zeros(m, geo.k, dtype=torch.int16)
+        V = torch.zeros(m, geo.k, dtype=vdtype)
+        for r in range(m):
+            a = S.normal_tensor(13, 100 * d + r, d, 1.0)
+            O.block_topk(a, geo, I[r])
+            O.copy_values(d, geo.k, geo.d_block_size, geo.k_block_size_many, I[r], a, V[r], O.D2K)
+        g = S.normal_tensor(14, d, d, 1.0).to(gdtype)
+        for rows in (1, m):
+            sp = torch.zeros(rows)
+            O.sparse_rows_dot(d, rows, geo.k, geo.d_block_size, geo.k_block_size_many, g, I, V, sp)
+            spg = torch.full((rows,), 7.0, device='cuda')
+            N.sparse_rows_dot(d, rows, geo.k, geo.d_block_size, geo.k_block_size_many, g.cuda(), I.cuda(), V.cuda(), spg)
+            torch.testing.assert_close(spg.cpu(), sp, rtol=1e-4, atol=1e-4 * float(V.float().abs().max()))
+            spg2 = torch.zeros(rows, device='cuda')
+            N.sparse_rows_dot(d, rows, geo.k, geo.d_block_size, geo.k_block_size_many, g.cuda(), I.cuda(), V.cuda(), spg2)
+            assert torch.equal(spg, spg2)                           # fixed summation order
+            M = S.normal_tensor(15, rows, rows, 1.0)
+            out = S.normal_tensor(16, d, d, 1.0).to(gdtype)
+            outg = out.cuda()
+            O.sparse_rows_combine(d, rows, geo.k, geo.d_block_size, geo.k_block_size_many, M, I, V, out)
+            N.sparse_rows_combine(d, rows, geo.k, geo.d_block_size, geo.k_block_size_many, M.cuda(), I.cuda(), V.cuda(), outg)
+            assert torch.equal(bits(out), bits(outg)), (d, rows)    # same operations in the same order: bit-exact
+
+
 def test_device_queries(N):
     assert N.get_sm_count() == torch.cuda.get_device_properties(0).multi_processor_count
     floats = N.get_max_floats_for_shared_memory_per_thread_block()

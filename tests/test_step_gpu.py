@@ -147,3 +147,42 @@ def test_logging_probes_report_the_reference_quantities():
         a, b = plain.state(i), probed.state(i)
         assert torch.equal(a['I'], b['I']) and torch.equal(a['error'], b['error'])
         torch.testing.assert_close(plain.param(i).float(), probed.param(i).float(), rtol=1e-2, atol=1e-9)
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_flat_shards_cut_at_arbitrary_elements(dtype):
+    """FSDP-style use (micro_adam.py:158-160 sizes the state lazily so that it fits whatever shard a rank holds): the
+    parameters handed to the optimizer are slices [lo, hi) of one flat buffer, cut at arbitrary elements, so their
+    storage starts at odd offsets (2-byte alignment only for bf16) and top-k blocks are counted from the shard's
+    start.  Every shard must behave exactly like a tensor of its own: compared with the oracle on the same slices."""
+    from ista_daslab_optimizers_b200 import MicroAdam, _native
+    from oracle.microadam_oracle import MicroAdamOracle
+    total = 3 * 29056 + 12345
+    cuts = [0, 1, 29056 + 3, 2 * 29056 + 1001, total]                 # shards of 1, 29058, 30054 and 40464 elements
+    gen = torch.Generator().manual_seed(11)
+    flat = (torch.randn(total, generator=gen) * 0.02).to(dtype)
+    hyper = dict(m=10, lr=1e-3, quant_block_size=64, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0.1, eps=1e-8)
+    flat_gpu = flat.cuda()
+    grad_gpu = torch.zeros_like(flat_gpu)
+    shards = [torch.nn.Parameter(flat_gpu[a:b]) for a, b in zip(cuts, cuts[1:])]
+    for p, (a, b) in zip(shards, zip(cuts, cuts[1:])):
+        p.grad = grad_gpu[a:b]
+    opt = MicroAdam(shards, **hyper)
+    cpu_shards = [flat[a:b].clone() for a, b in zip(cuts, cuts[1:])]
+    ref = MicroAdamOracle(cpu_shards, d_block_size=opt.d_block_size, **hyper)
+    rtol, atol = cases.param_tolerances(dtype, hyper['lr'])
+    for t in range(12):
+        g = (torch.randn(total, generator=gen) * 1e-3).to(dtype)
+        grad_gpu.copy_(g)
+        opt.step()
+        ref.step([g[a:b].clone() for a, b in zip(cuts, cuts[1:])])
+        for i, p in enumerate(shards):
+            a, b = opt.state[p], ref.state[i]
+            row = (a['index'] - 1) % hyper['m']
+            assert torch.equal(a['I'][row].cpu(), b['I'][row]), (t, i)
+            assert torch.equal(a['V'][row].cpu().view(torch.int16), b['V'][row].view(torch.int16)), (t, i)
+            assert torch.equal(a['error'].cpu(), b['error']), (t, i)
+            used = (p.numel() + 63) // 64
+            assert torch.equal(a['min_vals'][:used].cpu().view(torch.int16), b['min_vals'][:used].view(torch.int16)), (t, i)
+            torch.testing.assert_close(p.detach().cpu().float(), cpu_shards[i].float(), rtol=rtol, atol=atol)
+    assert _native.device_error() == 0

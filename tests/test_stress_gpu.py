@@ -5,10 +5,12 @@ all-zero first gradient, m = 10, k_init = 0.01, alpha = 0.5, 12 steps.
 
 Two checks.  All 300 tensors: the fused kernels against the operator-level kernels (two independent
 implementations of the step in this library), state bit for bit, parameters to the fp32 tolerance.  An
-unclipped subset of 40 of them: the fused kernels against the CPU oracle."""
+unclipped subset of 12 of them (about 250 M elements, what the CPU oracle finishes in a minute): the fused kernels
+against the CPU oracle."""
 import pytest
 import torch
 
+import cases
 from ista_daslab_optimizers_b200 import synthetic as S
 
 pytestmark = pytest.mark.gpu
@@ -60,15 +62,16 @@ def test_stress_all_300_tensors_fused_equals_operator_level():
             assert not bad, (t, bad[:10])
     assert all(e.fused for e in fused._entries) and not any(e.fused for e in plain._entries)
     for i, (a, b) in enumerate(zip(pa, pb)):
-        torch.testing.assert_close(a.detach(), b.detach(), rtol=1e-5, atol=1e-9, msg=lambda m: f'tensor {i}: {m}')
+        rtol, atol = cases.param_tolerances(torch.float32, HYPER['lr'])
+        torch.testing.assert_close(a.detach(), b.detach(), rtol=rtol, atol=atol, msg=lambda m: f'tensor {i}: {m}')
     assert _native.device_error() == 0
 
 
 def test_stress_unclipped_subset_matches_oracle():
     from ista_daslab_optimizers_b200 import MicroAdam
     from oracle.microadam_oracle import MicroAdamOracle
-    shapes = S.stress_shapes(0, count=300)[100:140]
-    zero = set(range(0, 40, 10))
+    shapes = S.stress_shapes(0, count=300)[98:110]          # includes one of the conv-like [256, 256, 3, 3] tensors
+    zero = {0, 7}
     gen = torch.Generator(device='cuda').manual_seed(1)
     params = [torch.nn.Parameter(torch.zeros(s, device='cuda') if i in zero else torch.empty(s, device='cuda').normal_(0, 0.02, generator=gen))
               for i, s in enumerate(shapes)]
@@ -86,4 +89,5 @@ def test_stress_unclipped_subset_matches_oracle():
             a, b = opt.state[p], ref.state[i]
             gpu_state = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in a.items() if k in ('I', 'V', 'error', 'min_vals', 'max_vals', 'index')}
             assert state_equal(gpu_state, b, qbs, p.numel()), (t, i)
-            torch.testing.assert_close(p.detach().cpu(), cpu_params[i], rtol=1e-5, atol=1e-9, msg=lambda m: f'step {t}, tensor {i}: {m}')
+            rtol, atol = cases.param_tolerances(torch.float32, HYPER['lr'])
+            torch.testing.assert_close(p.detach().cpu(), cpu_params[i], rtol=rtol, atol=atol, msg=lambda m: f'step {t}, tensor {i}: {m}')
