@@ -310,9 +310,10 @@ def whole_buffer_checksum(flat_p):
     return int(words.sum(dtype=torch.int64).item())
 
 
-def run_workload(spec, args, world, rank, local_rank, exchange, steps, warmup, e2e_steps):
+def run_workload(spec, args, world, rank, local_rank, exchange, steps, warmup, e2e_steps, plain_tail_steps=0):
     """Builds the synthetic model, runs warm-up + timed steps + the end-to-end steps and returns the measurements
-    (max over ranks) as a dictionary."""
+    (max over ranks) as a dictionary.  `plain_tail_steps` more steps on the end-to-end steps' gradients (already
+    on the device) follow, so that a run without end-to-end steps ends on the same step count and parameters."""
     import torch.distributed as dist
     from ista_daslab_optimizers_b200 import _native
     device = torch.device('cuda', local_rank)
@@ -416,6 +417,9 @@ def run_workload(spec, args, world, rank, local_rank, exchange, steps, warmup, e
         checksum = whole_buffer_checksum(flat_p)                       # 8-byte device-to-host read, synchronises
     barrier()
     e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
+    for _ in range(plain_tail_steps):
+        opt.step()
+        checksum = None
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     if checksum is None:
@@ -522,12 +526,15 @@ def main():
                 'roofline': roofline_record(k2), 'gpu_launches': r2['launches'], 'checksum': r2['checksum']}}
         elif exchange == 'rows':
             # the dense alternative: both kernels sharded ZeRO-1 style, updated parameters all-gathered
-            r2 = run_workload(spec, args, world, rank, local_rank, 'params', steps, warmup, 0)
+            r2 = run_workload(spec, args, world, rank, local_rank, 'params', steps, warmup, 0, plain_tail_steps=e2e_steps)
             k2, step2 = kernel_records(spec, r2, world)
             extra['params_mode'] = {
                 'parallelism': parallelism_label(world, 'params'), 'value': r2['n_params'] * steps / (r2['elapsed_ms'] * 1e-3) / 1e9,
                 'unit': UNIT, 'ms_per_step': r2['elapsed_ms'] / steps, 'kernels': k2, 'step_hbm': step2,
-                'checksum': r2['checksum']}
+                'param_checksum': {'value': r2['checksum'], 'optimizer_steps': r2['optimizer_steps']}}
+            if r2['checksum'] != r['checksum']:
+                raise SystemExit(f"rank {rank}: the two exchange modes ended with different parameters "
+                                 f"({r['checksum']} vs {r2['checksum']})")
 
     if rank != 0:
         if world > 1:

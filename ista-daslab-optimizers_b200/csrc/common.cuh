@@ -31,10 +31,10 @@ static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b;
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
 
 __device__ __forceinline__ uint16_t f32_to_bf16_bits_rne(float f) {
-    // finite inputs and infinities; NaN is outside the contract of the step
-    uint32_t u = __float_as_uint(f);
-    u += 0x7FFFu + ((u >> 16) & 1u);
-    return static_cast<uint16_t>(u >> 16);
+    // one conversion instruction; finite inputs and infinities (NaN is outside the contract of the step)
+    uint16_t r;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+    return r;
 }
 
 template <typename T> struct Elem;

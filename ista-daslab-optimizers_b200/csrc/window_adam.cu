@@ -287,6 +287,7 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
 constexpr int WT_THREADS = 256;
 constexpr int WT_WORDS = 1024;            // bitmap words (32768 positions)
 constexpr int WT_MAX_ENTRIES = 16384;     // window entries of one block the compact arrays may hold
+constexpr int WT_KEEP = 6;                // window entries a thread keeps in registers between marking and numbering
 constexpr int WT_NO_SLOT = 0xFFFF;        // slot of a window entry whose index lies outside the block (slots stay below 32768)
 
 // Bytes one row's slice of I (or V) occupies in the raw staging area: the slice is copied from the
@@ -357,7 +358,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     const uintptr_t I_lo = reinterpret_cast<uintptr_t>(T.I), I_hi = reinterpret_cast<uintptr_t>(T.I + (int64_t)a.m * pitch);
     const uintptr_t V_lo = reinterpret_cast<uintptr_t>(T.V), V_hi = reinterpret_cast<uintptr_t>(T.V + (int64_t)a.m * pitch);
     const int E = rows * kcnt;
-    const float inv_kcnt = 1.0f / (float)kcnt;
+    const uint32_t div_kcnt = kcnt > 1 ? 0xFFFFFFFFu / (uint32_t)kcnt + 1u : 0u;   // i / kcnt == umulhi(i, div_kcnt) while i * kcnt < 2^32
     const int chunks_per_row = w.rstride >> 4;
     MAB_BTICK_DECL
     // 1. stage the window entries: every row's slice of I and of V is copied asynchronously in
@@ -395,12 +396,24 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     MAB_BTICK(0);
     // entry i = (row r, column j): its position sits at raw + 2r * rstride + (address of the row's slice & 15) + 2j
     auto pos_ptr = [&](int i) -> uint16_t* {
-        const int r = (int)(((float)i + 0.5f) * inv_kcnt), j = i - r * kcnt;
+        const int r = kcnt > 1 ? (int)__umulhi((uint32_t)i, div_kcnt) : i, j = i - r * kcnt;
         return reinterpret_cast<uint16_t*>(w.raw + s_pos_off[r]) + j;
     };
     // 2. mark touched positions (an index outside the block - only a damaged checkpoint can hold one - is
-    //    ignored, here and below)
-    for (int i = t; i < E; i += NT) {
+    //    ignored, here and below).  A thread's first entries stay in registers for step 4.
+    constexpr int KEEP = NT >= 512 ? WT_KEEP : 1;             // (the 256-thread variants have no registers to spare)
+    uint16_t* kept_ptr[KEEP];
+    uint32_t kept_pos[KEEP];
+#pragma unroll
+    for (int it = 0; it < KEEP; ++it) {
+        const int i = t + it * NT;
+        kept_ptr[it] = pos_ptr(min(i, E - 1));
+        kept_pos[it] = i < E ? (uint32_t)*kept_ptr[it] : 0xFFFFFFFFu;
+    }
+#pragma unroll
+    for (int it = 0; it < KEEP; ++it)
+        if (kept_pos[it] < (uint32_t)n_blk) atomicOr(&w.bitmap[kept_pos[it] >> 5], 1u << (kept_pos[it] & 31));
+    for (int i = t + KEEP * NT; i < E; i += NT) {
         const uint32_t pos = *pos_ptr(i);
         if (pos < (uint32_t)n_blk) atomicOr(&w.bitmap[pos >> 5], 1u << (pos & 31));
     }
@@ -418,9 +431,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     __syncthreads();
     MAB_BTICK(2);
     // 4. positions -> slots (in place), then accumulate row after row
-    for (int i = t; i < E; i += NT) {
-        uint16_t* pp = pos_ptr(i);
-        const uint32_t pos = *pp;
+    auto to_slot = [&](uint16_t* pp, uint32_t pos) {
         if (pos < (uint32_t)n_blk) {
             const uint32_t slot = w.prefix[pos >> 5] + __popc(w.bitmap[pos >> 5] & ((1u << (pos & 31)) - 1u));
             *pp = (uint16_t)slot;
@@ -428,23 +439,34 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
         } else {
             *pp = WT_NO_SLOT;
         }
+    };
+#pragma unroll
+    for (int it = 0; it < KEEP; ++it)
+        if (kept_pos[it] != 0xFFFFFFFFu) to_slot(kept_ptr[it], kept_pos[it]);
+    for (int i = t + KEEP * NT; i < E; i += NT) {
+        uint16_t* pp = pos_ptr(i);
+        to_slot(pp, *pp);
     }
     __syncthreads();
     MAB_BTICK(3);
-    for (int r = 0; r < rows; ++r) {
-        const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r]);
-        const uint16_t* val_r = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r]);
-        const float w1 = a.w1[r], w2 = a.w2[r];
-        for (int j = t; j < kcnt; j += NT) {
-            const int slot = slot_r[j];
-            if (slot == WT_NO_SLOT) continue;
-            const float val = bf16_bits_to_f32(val_r[j]);
-            float2 acc = w.mv[slot];
-            acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
-            acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
-            w.mv[slot] = acc;
+    if ((t & ~31) < kcnt) {                                   // whole warps decide, so that every warp meets the barriers in one piece
+        for (int r = 0; r < rows; ++r) {
+            const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r]);
+            const uint16_t* val_r = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r]);
+            const float w1 = a.w1[r], w2 = a.w2[r];
+            for (int j = t; j < kcnt; j += NT) {
+                const int slot = slot_r[j];
+                if (slot == WT_NO_SLOT) continue;
+                const float val = bf16_bits_to_f32(val_r[j]);
+                float2 acc = w.mv[slot];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
+                w.mv[slot] = acc;
+            }
+            __syncthreads();
         }
-        __syncthreads();
+    } else {
+        for (int r = 0; r < rows; ++r) __syncthreads();      // warps beyond the row length only keep the barriers company
     }
     MAB_BTICK(4);
     return touched;
@@ -466,8 +488,9 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     __syncthreads();
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
 
+    int ti = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
-        const int ti = find_tensor(s_first, n_tensors, unit);
+        if (unit >= s_first[ti + 1]) ti = find_tensor(s_first, n_tensors, unit);   // (units ascend: mostly the same tensor as before)
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
         const int dbs = T.d_block_size, nfull = T.topk_full_blocks_count;
@@ -475,9 +498,9 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         const int n_blk = (int)min((int64_t)dbs, T.d - blk_base);
         if (MODE == MODE_STEP) {
             // the next unit's window rows are small and are asked into L2 now
-            if (unit + (int)gridDim.x < total_units) {
+            if (unit + (int)gridDim.x < total_units && (int)threadIdx.x < 2 * rows) {
                 const int nu = unit + gridDim.x;
-                const int nti = find_tensor(s_first, n_tensors, nu);
+                const int nti = nu < s_first[ti + 1] ? ti : find_tensor(s_first, n_tensors, nu);
                 prefetch_window_rows(tensors[nti], nu - s_first[nti], rows, threadIdx.x);
             }
             // this block's parameters travel to L2 while the window is worked on
@@ -582,8 +605,9 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
     uint32_t parity = 0;
     bool store_in_flight = false;                                               // thread 0 only
 
+    int ti = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
-        const int ti = find_tensor(s_first, n_tensors, unit);
+        if (unit >= s_first[ti + 1]) ti = find_tensor(s_first, n_tensors, unit);   // (units ascend: mostly the same tensor as before)
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
         const int dbs = T.d_block_size, nfull = T.topk_full_blocks_count;
@@ -603,9 +627,9 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
                 bulk_g2s(tile, p, (uint32_t)n_blk * 2u, &s_bar);
             }
         }
-        if (unit + (int)gridDim.x < total_units) {                              // the next unit's window rows: into L2
+        if (unit + (int)gridDim.x < total_units && t < 2 * rows) {              // the next unit's window rows: into L2
             const int nu = unit + gridDim.x;
-            const int nti = find_tensor(s_first, n_tensors, nu);
+            const int nti = nu < s_first[ti + 1] ? ti : find_tensor(s_first, n_tensors, nu);
             prefetch_window_rows(tensors[nti], nu - s_first[nti], rows, threadIdx.x);
         }
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
