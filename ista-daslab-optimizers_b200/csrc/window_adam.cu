@@ -450,20 +450,48 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     __syncthreads();
     MAB_BTICK(3);
     if ((t & ~31) < kcnt) {                                   // whole warps decide, so that every warp meets the barriers in one piece
-        for (int r = 0; r < rows; ++r) {
-            const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r]);
-            const uint16_t* val_r = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r]);
-            const float w1 = a.w1[r], w2 = a.w2[r];
-            for (int j = t; j < kcnt; j += NT) {
-                const int slot = slot_r[j];
-                if (slot == WT_NO_SLOT) continue;
-                const float val = bf16_bits_to_f32(val_r[j]);
-                float2 acc = w.mv[slot];
-                acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
-                acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
-                w.mv[slot] = acc;
+        if (kcnt <= NT) {
+            // one entry per thread and row: the next row's slot and value are fetched before the barrier of the current one
+            const bool on = t < kcnt;
+            int slot = WT_NO_SLOT;
+            uint32_t vbits = 0;
+            if (on) {
+                slot = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[0])[t];
+                vbits = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[0])[t];
             }
-            __syncthreads();
+            for (int r = 0; r < rows; ++r) {
+                int slot_n = WT_NO_SLOT;
+                uint32_t vbits_n = 0;
+                if (on && r + 1 < rows) {
+                    slot_n = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r + 1])[t];
+                    vbits_n = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r + 1])[t];
+                }
+                if (slot != WT_NO_SLOT) {
+                    const float val = __uint_as_float(vbits << 16);
+                    float2 acc = w.mv[slot];
+                    acc.x = __fadd_rn(acc.x, __fmul_rn(val, a.w1[r]));
+                    acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), a.w2[r]));
+                    w.mv[slot] = acc;
+                }
+                __syncthreads();
+                slot = slot_n; vbits = vbits_n;
+            }
+        } else {
+            for (int r = 0; r < rows; ++r) {
+                const uint16_t* slot_r = reinterpret_cast<const uint16_t*>(w.raw + s_pos_off[r]);
+                const uint16_t* val_r = reinterpret_cast<const uint16_t*>(w.raw + s_val_off[r]);
+                const float w1 = a.w1[r], w2 = a.w2[r];
+                for (int j = t; j < kcnt; j += NT) {
+                    const int slot = slot_r[j];
+                    if (slot == WT_NO_SLOT) continue;
+                    const float val = bf16_bits_to_f32(val_r[j]);
+                    float2 acc = w.mv[slot];
+                    acc.x = __fadd_rn(acc.x, __fmul_rn(val, w1));
+                    acc.y = __fadd_rn(acc.y, __fmul_rn(__fmul_rn(val, val), w2));
+                    w.mv[slot] = acc;
+                }
+                __syncthreads();
+            }
         }
     } else {
         for (int r = 0; r < rows; ++r) __syncthreads();      // warps beyond the row length only keep the barriers company
