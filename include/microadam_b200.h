@@ -162,6 +162,9 @@ typedef struct mab_tensor {
     float     neg_lr_f32;        /* f32(-lr)                                                    */
     int32_t   first_unit_a;      /* first work unit (top-k block) of this tensor in kernel A    */
     int32_t   first_unit_b;      /* first work unit (block sub-range) of this tensor in kernel B */
+    /* alpha == -2 only (else NULL) */
+    void*     quant_err;         /* [d], param_dtype: st['quant_err'] (micro_adam.py:67-68); kernel A leaves the
+                                    residual a in it, kernel B turns it into a - Qinv(e)            */
 } mab_tensor;
 
 /* Scalars of one step, the same for every tensor. */
@@ -169,7 +172,7 @@ typedef struct mab_step_args {
     int64_t steps;               /* 1-based step counter (self.steps after the increment)        */
     int32_t m;                   /* window rows                                                   */
     int32_t quant_block_size;
-    float   alpha;               /* 0 <= alpha < 1                                                */
+    float   alpha;               /* 0 <= alpha < 1, or -2 (micro_adam.py:238-273)                 */
     int32_t reserved0;
     double  beta1, beta2, eps;
 } mab_step_args;
@@ -178,14 +181,18 @@ typedef struct mab_step_args {
 int64_t mab_fused_step_workspace_bytes(int n_tensors);
 
 /* 1 if the fused kernels cover this geometry (quant_block_size a power of two in [8, 128] that
- * divides d_block_size, d_block_size <= 32768, supported dtypes, aligned pointers), else 0. */
+ * divides d_block_size, d_block_size <= 32768, supported dtypes, aligned pointers; alpha in [0, 1), or
+ * alpha == -2 with quant_err and equal gradient / parameter element types), else 0. */
 int mab_fused_supported(const mab_tensor* t, const mab_step_args* args);
 
-/* The whole step of micro_adam.py:146-328 (alpha >= 0) for n_tensors tensors in two kernels:
+/* The whole step of micro_adam.py:146-328 for n_tensors tensors in two kernels:
  *   A  dequantise EF + add gradient, block top-k into row ring_index of I / V, zero the selected
  *      entries, block min / max, requantise EF                      (micro_adam.py:190-231)
  *   B  window -> Adam update, weight decay, alpha EF integration, parameter update, EF shrink
  *                                                                   (micro_adam.py:234-235, 276-316)
+ * alpha == -2 (micro_adam.py:238-273; gradient and parameter of one element type, quant_err given): A also
+ * writes the residual a to quant_err, and B applies p <- decay(p) - a + Qinv(e) before the update and leaves
+ * a - Qinv(e) in quant_err.
  * `tensors` is host memory; it is copied to `workspace` (device, >= workspace_bytes) on `stream`
  * and its first_unit_* fields are overwritten.  Every tensor must satisfy mab_fused_supported. */
 int mab_fused_step(mab_tensor* tensors, int n_tensors, const mab_step_args* args,

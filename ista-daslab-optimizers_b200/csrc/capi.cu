@@ -97,7 +97,10 @@ static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
     if (t->grad_dtype != MAB_F32 && t->grad_dtype != MAB_BF16) return "grad dtype is neither f32 nor bf16";
     const int qbs = a->quant_block_size;
     if (!is_pow2(qbs) || qbs < 8 || qbs > 128) return "quant_block_size is not a power of two in [8, 128]";
-    if (!(a->alpha >= 0.0f && a->alpha < 1.0f)) return "alpha outside [0, 1)";
+    if (a->alpha == -2.0f) {
+        if (!t->quant_err) return "alpha == -2 needs quant_err";
+        if (t->param_dtype != t->grad_dtype) return "alpha == -2 needs gradient and parameter of one element type";
+    } else if (!(a->alpha >= 0.0f && a->alpha < 1.0f)) return "alpha outside [0, 1) and not -2";
     if (a->m < 1 || a->m > MAB_MAX_WINDOW) return "window rows outside [1, MAB_MAX_WINDOW]";
     if (t->d_block_size <= 0 || t->d_block_size > SEL_MAX_TILE) return "d_block_size outside (0, 32768]";
     const int64_t nfull = t->topk_full_blocks_count;
@@ -113,7 +116,8 @@ static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
     if (t->ring_index < 0 || t->ring_index >= a->m) return "ring_index outside [0, m)";
     const size_t pe = t->param_dtype == MAB_F32 ? 4 : 2, ge = t->grad_dtype == MAB_F32 ? 4 : 2;
     if (!aligned_to(t->param, pe) || !aligned_to(t->grad, ge) || !aligned_to(t->min_vals, 2) ||
-        !aligned_to(t->max_vals, 2) || !aligned_to(t->I, 2) || !aligned_to(t->V, 2)) return "buffer not aligned to its element size";
+        !aligned_to(t->max_vals, 2) || !aligned_to(t->I, 2) || !aligned_to(t->V, 2) ||
+        (t->quant_err && !aligned_to(t->quant_err, pe))) return "buffer not aligned to its element size";
     return nullptr;
 }
 

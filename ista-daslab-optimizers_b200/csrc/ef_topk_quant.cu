@@ -309,6 +309,10 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 for (int e = 0; e < 8; ++e)
                     if (sel & (1u << e)) { v_out[p++] = f32_to_bf16_bits_rne(a[j][e]); a[j][e] = 0.0f; }
             }
+            if (T.quant_err != nullptr && cnt > 0) {      // alpha == -2: the residual a also goes to the caller's buffer
+                TG* qe = reinterpret_cast<TG*>(T.quant_err) + base + o * 8;
+                for (int e = 0; e < min(cnt, 8); ++e) Elem<TG>::store(qe, e, a[j][e]);
+            }
             float lo = INFINITY, hi = -INFINITY;
             if (cnt >= 8) {
                 octet_min_max(a[j], lo, hi);

@@ -495,7 +495,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
         float omax[S_SLOTS];
         // regular tile: whole blocks of 64, 14 whole octets per thread, aligned codes, every block with the fast decode
-        const bool swz = tables && (n & 63) == 0 && n_oct >= S_FULL * S_NT && ef_al4 && ss.ctrl[slow_slot] == 0;
+        const bool swz = tables && (n & 63) == 0 && n_oct >= S_FULL * S_NT && ef_al4 && ss.ctrl[slow_slot] == 0 && T.quant_err == nullptr;
         if (swz) dequant_phase_regular(tile4, ss, n_oct, cw, omax);
         else dequant_phase<0>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax);
 
@@ -750,6 +750,15 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         }
         __syncthreads();
 
+        if (T.quant_err != nullptr) {
+            // alpha == -2: the residual a also goes to the caller's buffer (same element type as the gradient; linear tile)
+            uint16_t* qe = reinterpret_cast<uint16_t*>(T.quant_err) + base;
+            const bool vec = aligned16(qe);
+            for (int o = t; o < n_oct; o += S_NT) {
+                if (vec && o * 8 + 8 <= n) reinterpret_cast<uint4*>(qe)[o] = tile4[o];
+                else for (int e = o * 8; e < min(o * 8 + 8, n); ++e) qe[e] = tile[e];
+            }
+        }
         MAB_CTICK(4);
         // ---- statistics and codes of the residual ----------------------------------------------------------
         uint16_t* mn_out = T.min_vals + qb0;

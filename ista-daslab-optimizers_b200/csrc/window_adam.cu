@@ -170,9 +170,9 @@ __device__ __forceinline__ float round_as(float v, bool bf16) {
 
 // Streams tensor elements [e0, e0 + len) against their updates (already rounded to the gradient's
 // element type), which `src` delivers octet by octet.  e0 is a multiple of 8 (and of
-// quant_block_size when alpha > 0).  NT threads, all of them must call.  ALPHA selects the
-// alpha > 0 form at compile time (it needs many more registers).
-template <typename TP, int MODE, int NT, bool ALPHA, typename USrc>
+// quant_block_size when alpha > 0).  NT threads, all of them must call.  ALPHA selects the form at
+// compile time: 0 = no alpha term, 1 = alpha > 0 (it needs many more registers), 2 = alpha == -2.
+template <typename TP, int MODE, int NT, int ALPHA, typename USrc>
 __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowArgs& a, const USrc& src, int64_t e0, int len) {
     TP* p = reinterpret_cast<TP*>(T.param) + e0;
     const bool vec = aligned16(p);                        // octets stay 16-byte aligned from here
@@ -188,7 +188,7 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
     }
     const float decay = T.decay_f32, neg_lr = T.neg_lr_f32;
     const bool do_decay = T.weight_decay > 0.0;
-    if (!ALPHA) {
+    if (ALPHA == 0) {
         const float2 decay2 = make_float2(decay, decay), neg_lr2 = make_float2(neg_lr, neg_lr);
         constexpr int B = (sizeof(TP) == 2) ? 4 : 2;          // octets per thread and batch
         const int full_oct = vec ? (len >> 3) : 0;           // octets that can move as 16-byte vectors
@@ -228,8 +228,42 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
         }
         return;
     }
-    // alpha > 0: u += alpha * Qinv(e); p update; e <- Q((1 - alpha) * Qinv(e)) with fresh statistics
     const bool g_bf16 = (T.grad_dtype == MAB_BF16);
+    if (ALPHA == 2) {
+        // alpha == -2 (micro_adam.py:238-273), with a = the residual kernel A left in quant_err and e = the new codes:
+        //   p <- decay(p);  p <- p - a;  p <- p + Qinv(e);  quant_err <- a - Qinv(e);  then p <- p - lr * u
+        TP* qe = reinterpret_cast<TP*>(T.quant_err) + e0;
+        const bool vec_q = aligned16(qe);
+        for (int o = threadIdx.x; o < n_oct; o += NT) {
+            const int n = min(8, len - o * 8);
+            const int64_t ge = e0 + (int64_t)o * 8;
+            const int64_t qb = ge / a.qbs;
+            const QParams q = qparams(T.min_vals[qb], T.max_vals[qb]);
+            uint32_t codes = 0;
+            const uint8_t* ef = T.error + (ge >> 1);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) if (2 * b < n) codes |= (uint32_t)ef[b] << (8 * b);
+            float pv[8], av[8], uo[8];
+            Octet<TP>::load(p + o * 8, pv, vec && n == 8, n);
+            Octet<TP>::load(qe + o * 8, av, vec_q && n == 8, n);
+            src.load(o, uo);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t code = (codes >> (8 * (e >> 1) + ((e & 1) ? 0 : 4))) & 0xFu;
+                const float x = round_as(__fadd_rn(0.0f, qinv(code, q)), g_bf16);             // grad.zero_(); grad += Qinv(e)
+                float v = pv[e];
+                if (do_decay) v = Elem<TP>::round(__fmul_rn(v, decay));
+                v = Elem<TP>::round(__fsub_rn(v, av[e]));                                     // p.add_(grad, alpha=-1)
+                v = Elem<TP>::round(__fadd_rn(v, x));                                         // p.add_(grad)
+                av[e] = __fsub_rn(av[e], x);                                                  // quant_err.sub_(grad)
+                pv[e] = fmaf(neg_lr, uo[e], v);
+            }
+            Octet<TP>::store(p + o * 8, pv, vec && n == 8, n);
+            Octet<TP>::store(qe + o * 8, av, vec_q && n == 8, n);
+        }
+        return;
+    }
+    // alpha > 0: u += alpha * Qinv(e); p update; e <- Q((1 - alpha) * Qinv(e)) with fresh statistics
     const int lanes = a.lanes_per_qb;
     const int n_oct_pad = (n_oct + 31) & ~31;
     for (int o = threadIdx.x; o < n_oct_pad; o += NT) {
@@ -500,7 +534,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     return touched;
 }
 
-template <typename TP, int MODE, bool ALPHA>
+template <typename TP, int MODE, int ALPHA>
 __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  int max_k, const WindowArgs& a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -547,7 +581,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         }
         __syncthreads();
         MAB_BTICK(5);
-        if (MODE == MODE_STEP && !ALPHA) {
+        if (MODE == MODE_STEP && ALPHA == 0) {
             // 6. without the alpha term only the touched positions get an update: stream the block for the
             //    weight decay alone (nothing to stream without decay), then update the touched elements
             //    one by one; fma(-lr, 0, x) == x, so the untouched elements are already final
@@ -576,15 +610,15 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     }
 }
 
-template <typename TP, int MODE, bool ALPHA>
-__global__ void __launch_bounds__(WT_THREADS, ALPHA ? 1 : 4)
+template <typename TP, int MODE, int ALPHA>
+__global__ void __launch_bounds__(WT_THREADS, ALPHA == 0 ? 4 : 1)
 window_tile_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int max_k,
                    const __grid_constant__ WindowArgs a) {
     window_tile_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, max_k, a);
 }
 
 // Single tensor whose descriptor travels as a kernel argument (operator-level entry point).
-template <typename TP, int MODE, bool ALPHA>
+template <typename TP, int MODE, int ALPHA>
 __global__ void __launch_bounds__(WT_THREADS)
 window_tile_single_kernel(const __grid_constant__ mab_tensor t, int total_units, int max_k,
                           const __grid_constant__ WindowArgs a) {
@@ -729,7 +763,7 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
 // ------------------------------------------------------------------------------------ wide kernel
 
 // TP: element type of `param` (MODE_STEP) or of the output buffer held in `param` (MODE_WRITE_UPDATE).
-template <typename TP, int MODE, bool ALPHA>
+template <typename TP, int MODE, int ALPHA>
 __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  const WindowArgs& a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -764,13 +798,13 @@ __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ 
     }
 }
 
-template <typename TP, int MODE, bool ALPHA>
+template <typename TP, int MODE, int ALPHA>
 __global__ void __launch_bounds__(WIN_THREADS)
 window_wide_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, const __grid_constant__ WindowArgs a) {
     window_wide_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, a);
 }
 
-template <typename TP, int MODE, bool ALPHA>
+template <typename TP, int MODE, int ALPHA>
 __global__ void __launch_bounds__(WIN_THREADS)
 window_wide_single_kernel(const __grid_constant__ mab_tensor t, int total_units, const __grid_constant__ WindowArgs a) {
     window_wide_body<TP, MODE, ALPHA>(&t, 1, total_units, a);
@@ -781,7 +815,7 @@ window_wide_single_kernel(const __grid_constant__ mab_tensor t, int total_units,
 // `single` != nullptr: one tensor passed by value; else n_tensors descriptors in device memory.
 // units_tile / units_wide are the unit counts of the two variants; rows * max_k (the largest
 // k_block_size of the launch) decides which one runs.
-template <typename TP, int MODE, bool ALPHA>
+template <typename TP, int MODE, int ALPHA>
 static int launch_window_impl(const mab_tensor* dev_tensors, const mab_tensor* single, int n_tensors, int units_tile,
                               int units_wide, int max_k, const WindowArgs& a, cudaStream_t s) {
     const int sms = device_sm_count();
@@ -824,9 +858,11 @@ static int launch_window_impl(const mab_tensor* dev_tensors, const mab_tensor* s
 template <typename TP, int MODE>
 static int launch_window(const mab_tensor* dev_tensors, const mab_tensor* single, int n_tensors, int units_tile,
                          int units_wide, int max_k, const WindowArgs& a, cudaStream_t s) {
+    if (MODE == MODE_STEP && a.alpha == -2.0f)
+        return launch_window_impl<TP, MODE, 2>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
     if (MODE == MODE_STEP && a.alpha != 0.0f)
-        return launch_window_impl<TP, MODE, true>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
-    return launch_window_impl<TP, MODE, false>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
+        return launch_window_impl<TP, MODE, 1>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
+    return launch_window_impl<TP, MODE, 0>(dev_tensors, single, n_tensors, units_tile, units_wide, max_k, a, s);
 }
 
 int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double beta2, double eps, float alpha, int qbs) {

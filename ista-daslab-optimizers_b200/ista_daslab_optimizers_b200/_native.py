@@ -40,6 +40,7 @@ class MabTensor(Structure):
         ('lr', c_double), ('weight_decay', c_double),
         ('decay_f32', c_float), ('neg_lr_f32', c_float),
         ('first_unit_a', c_int32), ('first_unit_b', c_int32),
+        ('quant_err', c_void_p),
     ]
 
 

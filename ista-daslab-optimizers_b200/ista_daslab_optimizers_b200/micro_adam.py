@@ -10,7 +10,8 @@ order of sub-steps.  Differences a caller can observe:
   (torch.topk(sorted=False) at micro_adam.py:193-200 leaves both unspecified);
 * on the fused path `p.grad` is left untouched (the reference uses it as scratch and leaves the
   update in it, micro_adam.py:276-313); on the operator-level path it is scratch as in the reference;
-* alpha == -2 (micro_adam.py:238-273) runs on the operator-level path only (no fused kernel);
+* alpha == -2 (micro_adam.py:238-273) keeps the residual in `quant_err` between the two fused kernels (gradient and
+  parameter of one element type; other combinations take the operator-level path);
 * the logging probes (micro_adam.py:155-156, 306-308, 320-324, 330-350) run only when a `log_fn` is given: every
   `log_interval` steps the step takes the operator-level path, gathers the same seven numbers and hands
   `log_fn` the dictionary the reference sends to wandb;
@@ -69,7 +70,7 @@ class MicroAdam(torch.optim.Optimizer):
         self.device = get_first_device()
         self.shared_memory_carveout = 100
         self.threads = 512
-        self.use_fused = bool(use_fused) and not self.densify_update_using_quant_error   # alpha == -2 has no fused kernel
+        self.use_fused = bool(use_fused)
         self.log_fn = log_fn      # callable(dict) or None; None (the default) switches the probes off
 
         N.load()   # fail here, loudly, if the native library is not built
@@ -127,6 +128,8 @@ class MicroAdam(torch.optim.Optimizer):
         st['error'] = torch.zeros(int(math.ceil(st['d'] / 2)), dtype=torch.uint8, device=dev)
         st['min_vals'] = torch.zeros(st['quant_full_blocks_count'] + 1, dtype=torch.bfloat16, device=dev)
         st['max_vals'] = torch.zeros(st['quant_full_blocks_count'] + 1, dtype=torch.bfloat16, device=dev)
+        if self.densify_update_using_quant_error:                                                      # micro_adam.py:67-68
+            st['quant_err'] = torch.zeros(layer_size, dtype=p.dtype, device=dev)
         if (lo, hi) != (0, p.numel()):
             st['shard_lo'], st['shard_hi'] = lo, hi
 
@@ -314,6 +317,7 @@ class MicroAdam(torch.optim.Optimizer):
         d.topk_full_blocks_count = st['topk_full_blocks_count'] if st['d_index_topk'] > 0 else 0
         d.k_block_size_many, d.k_block_size_few = st['k_block_size_many'], st['k_block_size_few']
         d.param_dtype, d.grad_dtype = N.dtype_code(e.p), N.dtype_code(e.p.grad)
+        d.quant_err = st['quant_err'].data_ptr() if 'quant_err' in st else None
 
     def _fill_dynamic(self, d: N.MabTensor, e: _Entry):
         p, g = e.p, e.p.grad
@@ -385,9 +389,7 @@ class MicroAdam(torch.optim.Optimizer):
         if wd > 0:
             pf.mul_(1 - lr * wd)                                                                       # :234-235
         if self.densify_update_using_quant_error:                                                      # :238-273, the form without lr
-            if 'quant_err' not in st:
-                st['quant_err'] = torch.zeros(d, dtype=p.dtype, device=p.device)                       # :67-68
-            quant_err = st['quant_err']
+            quant_err = st['quant_err']                                                                # :67-68
             quant_err.zero_()
             quant_err.add_(grad)                                                                       # :259-260
             pf.add_(grad, alpha=-1)                                                                    # :263

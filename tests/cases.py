@@ -76,7 +76,7 @@ CASES: Dict[str, Case] = {c.name: c for c in [
     # quantisation blocks that straddle top-k blocks: only the operator-level kernels apply
     Case('qbs_100000', [(100001,), (300, 200)], torch.float32, 3, qbs=100000, alpha=0.5),
     Case('qbs_32_m5', [(65536,), (1000,)], torch.float32, 7, qbs=32, m=5, k_init=0.05),
-    # alpha == -2: the quantisation error is added to the parameters (operator-level path only)
+    # alpha == -2: the quantisation error is added to the parameters
     Case('alpha_m2', [(70000,), (4096,)], torch.float32, 4, alpha=-2, weight_decay=0.1),
     # bf16 with a quantisation block other than 64: the general decode / statistics / encode code of the bf16 kernel
     Case('bf16_qbs32', [(70000,), (4096,), (29056 + 32 * 7,)], torch.bfloat16, 5, qbs=32, weight_decay=0.1, grad_sigma=1e-4),
@@ -89,6 +89,8 @@ CASES: Dict[str, Case] = {c.name: c for c in [
     # few rows of few entries (m = 5, 0.5 % of a block)
     Case('narrow_m5', [(29056 * 3 + 8,), (1000,)], torch.float32, 7, m=5, k_init=0.005, weight_decay=0.1),
     Case('narrow_m5_bf16', [(29056 * 3 + 8,), (1000,)], torch.bfloat16, 7, m=5, k_init=0.005, weight_decay=0.1, grad_sigma=1e-4),
+    # alpha == -2 on bf16 (a tensor with a short last block, an odd-sized one) and with the window wrapping
+    Case('alpha_m2_bf16', [(29056 * 2 + 640,), (4097,)], torch.bfloat16, 12, alpha=-2, weight_decay=0.1, grad_sigma=1e-4),
 ]}
 
 

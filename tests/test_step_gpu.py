@@ -186,3 +186,27 @@ def test_flat_shards_cut_at_arbitrary_elements(dtype):
             assert torch.equal(a['min_vals'][:used].cpu().view(torch.int16), b['min_vals'][:used].view(torch.int16)), (t, i)
             torch.testing.assert_close(p.detach().cpu().float(), cpu_shards[i].float(), rtol=rtol, atol=atol)
     assert _native.device_error() == 0
+
+
+@pytest.mark.parametrize('name', ['alpha_m2', 'alpha_m2_bf16'])
+def test_alpha_m2_runs_fused_and_leaves_the_quantisation_error(name):
+    """alpha == -2 (micro_adam.py:238-273) on the two fused kernels: every tensor takes the fused path, two launches per
+    step, and `quant_err` holds a - Qinv(e) as the oracle computes it."""
+    from ista_daslab_optimizers_b200 import _native
+    case = cases.CASES[name]
+    gpu = cases.CudaAdapter(case, case.params())
+    ref = cases.OracleAdapter(case, case.params())
+    rtol, atol = cases.param_tolerances(case.dtype, case.lr)
+    for t in range(3):
+        grads = case.grads(t)
+        before = _native.kernel_launch_count()
+        gpu.step(grads)
+        assert _native.kernel_launch_count() - before == 2
+        assert all(e.fused for e in gpu.opt._entries)
+        ref.step(grads)
+        for i in range(len(case.shapes)):
+            got = gpu.state(i)['quant_err'].float().cpu()
+            want = ref.opt.state[i]['quant_err'].float().view(-1)
+            # the error is a difference of nearly equal numbers: compared relative to the step of the quantiser
+            step_q = float((ref.opt.state[i]['max_vals'].float() - ref.opt.state[i]['min_vals'].float()).max()) / 15
+            torch.testing.assert_close(got, want, rtol=rtol, atol=max(atol, step_q * (1e-5 if case.dtype == torch.float32 else 1e-2)))
