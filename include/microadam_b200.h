@@ -167,6 +167,16 @@ typedef struct mab_tensor {
                                     residual a in it, kernel B turns it into a - Qinv(e)            */
 } mab_tensor;
 
+/* Slots of the probe buffer (doubles) a step adds to when mab_step_args.probe_out is given: the quantities the
+ * reference logs every log_interval steps (micro_adam.py:155-156, 272-273, 306-308, 320-324). */
+#define MAB_PROBE_NORM_G    0    /* sum of g^2 over the gradients of the call's tensors                */
+#define MAB_PROBE_NORM_U    1    /* sum of u^2 over the updates                                          */
+#define MAB_PROBE_NORM_E    2    /* sum of Qinv(e)^2 over the error feedback the step leaves            */
+#define MAB_PROBE_ZEROS_U   3    /* number of exact zeros in u                                           */
+#define MAB_PROBE_NORM_QE   4    /* alpha == -2: sum of quant_err^2                                      */
+#define MAB_PROBE_ZEROS_QE  5    /* alpha == -2: number of exact zeros in quant_err                      */
+#define MAB_PROBE_SLOTS     8
+
 /* Scalars of one step, the same for every tensor. */
 typedef struct mab_step_args {
     int64_t steps;               /* 1-based step counter (self.steps after the increment)        */
@@ -175,6 +185,12 @@ typedef struct mab_step_args {
     float   alpha;               /* 0 <= alpha < 1, or -2 (micro_adam.py:238-273)                 */
     int32_t reserved0;
     double  beta1, beta2, eps;
+    double* probe_out;           /* NULL, or MAB_PROBE_SLOTS doubles in device memory that the call ADDS its
+                                    probes to (the caller zeroes them): kernel B adds the update's, and one
+                                    more small kernel at the end of the call the gradient's and the error
+                                    feedback's.  mab_fused_ef_topk_quant alone adds the latter two (they
+                                    describe the final state only when alpha is 0 or -2),
+                                    mab_fused_window_adam_update alone the update's.               */
 } mab_step_args;
 
 /* Bytes of device workspace mab_fused_step needs for n_tensors tensors. */

@@ -188,10 +188,14 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
         WindowArgs wa;
         if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
                                       args->quant_block_size)) return rc;
+        wa.probe = args->probe_out;
         for (const Chunk& c : chunks) {
             if (int rc = launch_window_step(dev + c.first, c.count, c.units_a, c.units_b, c.max_k, c.max_dbs, c.param_dtype, wa, s)) return rc;
         }
     }
+    if (args->probe_out && (what & RUN_A))                     // gradient and final error feedback: after the call's last kernel
+        for (const Chunk& c : chunks)
+            if (int rc = launch_probe(dev + c.first, c.count, c.units_a, args->quant_block_size, args->probe_out, s)) return rc;
     return MAB_OK;
 }
 
@@ -292,10 +296,17 @@ extern "C" int mab_fused_step_static(mab_tensor* tensors, int n, const mab_step_
         if (int rc = launch_ef_topk_quant(dev + first, end - first, ua, tensors[first].grad_dtype, args->quant_block_size, md, s)) return rc;
         first = end;
     }
+    wa.probe = args->probe_out;
     for (int first = 0; first < n;) {
         const int end = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
         if (int rc = launch_window_step(dev + first, end - first, ua, ub, mk, md, tensors[first].param_dtype, wa, s)) return rc;
         first = end;
     }
+    if (args->probe_out)
+        for (int first = 0; first < n;) {
+            const int end = static_run_end(tensors, n, first, &ua, &ub, &mk, &md);
+            if (int rc = launch_probe(dev + first, end - first, ua, args->quant_block_size, args->probe_out, s)) return rc;
+            first = end;
+        }
     return MAB_OK;
 }

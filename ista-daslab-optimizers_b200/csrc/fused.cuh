@@ -28,6 +28,9 @@ int launch_window_step(const mab_tensor* dev_tensors, int n_tensors, int units_t
 int units_b_of(const mab_tensor& t);
 int launch_wait_selftest(int probe_limit, cudaStream_t s);
 
+// probe.cu: adds sum g^2 and sum Qinv(e)^2 of the tensors to out[MAB_PROBE_NORM_G] / out[MAB_PROBE_NORM_E]
+int launch_probe(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, double* out, cudaStream_t s);
+
 // ef_topk_quant.cu
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
                          int qbs, int max_dbs, cudaStream_t s);

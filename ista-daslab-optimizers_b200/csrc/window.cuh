@@ -33,6 +33,7 @@ struct WindowArgs {
     float alpha, one_minus_alpha;
     int   qbs;
     int   lanes_per_qb;               // qbs / 8 (fused path only)
+    double* probe;                    // nullptr, or the probe buffer the step adds the update's statistics to
 };
 
 struct WindowSmem {

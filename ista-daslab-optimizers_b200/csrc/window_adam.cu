@@ -164,6 +164,29 @@ struct SparseU {                // touched positions as a bitmap, their updates 
     }
 };
 
+// Per-thread partial sums of the update's logging probes (micro_adam.py:306-308, 272-273); they live across the
+// blocks a CTA works on and reach the probe buffer once, when the kernel ends.
+struct UpdateProbe {
+    float sum_u2 = 0.0f, sum_qe2 = 0.0f;
+    int zeros_u = 0, zeros_qe = 0;
+    __device__ __forceinline__ void flush(double* probe) {
+        if (probe == nullptr) return;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            sum_u2 += __shfl_xor_sync(0xffffffffu, sum_u2, o);
+            sum_qe2 += __shfl_xor_sync(0xffffffffu, sum_qe2, o);
+            zeros_u += __shfl_xor_sync(0xffffffffu, zeros_u, o);
+            zeros_qe += __shfl_xor_sync(0xffffffffu, zeros_qe, o);
+        }
+        if (lane_id() == 0) {
+            if (sum_u2 != 0.0f) atomicAdd(&probe[MAB_PROBE_NORM_U], (double)sum_u2);
+            if (zeros_u != 0) atomicAdd(&probe[MAB_PROBE_ZEROS_U], (double)zeros_u);
+            if (sum_qe2 != 0.0f) atomicAdd(&probe[MAB_PROBE_NORM_QE], (double)sum_qe2);
+            if (zeros_qe != 0) atomicAdd(&probe[MAB_PROBE_ZEROS_QE], (double)zeros_qe);
+        }
+    }
+};
+
 __device__ __forceinline__ float round_as(float v, bool bf16) {
     return bf16 ? bf16_bits_to_f32(f32_to_bf16_bits_rne(v)) : v;
 }
@@ -173,7 +196,9 @@ __device__ __forceinline__ float round_as(float v, bool bf16) {
 // quant_block_size when alpha > 0).  NT threads, all of them must call.  ALPHA selects the form at
 // compile time: 0 = no alpha term, 1 = alpha > 0 (it needs many more registers), 2 = alpha == -2.
 template <typename TP, int MODE, int NT, int ALPHA, typename USrc>
-__device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowArgs& a, const USrc& src, int64_t e0, int len) {
+__device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowArgs& a, const USrc& src, int64_t e0, int len,
+                                             UpdateProbe& pr) {
+    const bool probing = MODE == MODE_STEP && a.probe != nullptr;
     TP* p = reinterpret_cast<TP*>(T.param) + e0;
     const bool vec = aligned16(p);                        // octets stay 16-byte aligned from here
     const int n_oct = (len + 7) >> 3;
@@ -210,6 +235,10 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
                     float pv[8], u[8];
                     cur[i].unpack(pv);
                     src.load(o, u);
+                    if (USrc::has_u && probing) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) { pr.sum_u2 = fmaf(u[e], u[e], pr.sum_u2); pr.zeros_u += (u[e] == 0.0f) ? 1 : 0; }
+                    }
                     update_octet<TP, USrc::has_u>(pv, u, do_decay, decay2, neg_lr2);
                     Octet<TP>::store(p + o * 8, pv, true, 8);
                 }
@@ -223,6 +252,10 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
             float pv[8], u[8];
             Octet<TP>::load(p + o * 8, pv, false, n);
             src.load(o, u);
+            if (USrc::has_u && probing) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) if (e < n) { pr.sum_u2 = fmaf(u[e], u[e], pr.sum_u2); pr.zeros_u += (u[e] == 0.0f) ? 1 : 0; }
+            }
             update_octet<TP, USrc::has_u>(pv, u, do_decay, decay2, neg_lr2);
             Octet<TP>::store(p + o * 8, pv, false, n);
         }
@@ -255,8 +288,12 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
                 if (do_decay) v = Elem<TP>::round(__fmul_rn(v, decay));
                 v = Elem<TP>::round(__fsub_rn(v, av[e]));                                     // p.add_(grad, alpha=-1)
                 v = Elem<TP>::round(__fadd_rn(v, x));                                         // p.add_(grad)
-                av[e] = __fsub_rn(av[e], x);                                                  // quant_err.sub_(grad)
+                av[e] = Elem<TP>::round(__fsub_rn(av[e], x));                                 // quant_err.sub_(grad)
                 pv[e] = fmaf(neg_lr, uo[e], v);
+                if (probing && e < n) {
+                    pr.sum_u2 = fmaf(uo[e], uo[e], pr.sum_u2); pr.zeros_u += (uo[e] == 0.0f) ? 1 : 0;
+                    pr.sum_qe2 = fmaf(av[e], av[e], pr.sum_qe2); pr.zeros_qe += (av[e] == 0.0f) ? 1 : 0;
+                }
             }
             Octet<TP>::store(p + o * 8, pv, vec && n == 8, n);
             Octet<TP>::store(qe + o * 8, av, vec_q && n == 8, n);
@@ -287,6 +324,7 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
                 const uint32_t code = (codes >> (8 * (e >> 1) + ((e & 1) ? 0 : 4))) & 0xFu;
                 const float x1 = qinv(code, q);
                 const float u = round_as(__fadd_rn(uo[e], __fmul_rn(a.alpha, x1)), g_bf16);
+                if (probing && e < n) { pr.sum_u2 = fmaf(u, u, pr.sum_u2); pr.zeros_u += (u == 0.0f) ? 1 : 0; }
                 float x = pv[e];
                 if (do_decay) x = Elem<TP>::round(__fmul_rn(x, decay));
                 pv[e] = fmaf(neg_lr, u, x);
@@ -549,6 +587,8 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     if (t == 0) s_first[n_tensors] = total_units;
     __syncthreads();
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
+    UpdateProbe pr;
+    const bool probing = MODE == MODE_STEP && a.probe != nullptr;
 
     int ti = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
@@ -577,8 +617,11 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         // 5. moments -> update (rounded to the gradient's element type), slot by slot
         for (int s = t; s < touched; s += WT_THREADS) {
             const float2 acc = w.mv[s];
-            w.mv[s].x = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
+            const float u = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
+            w.mv[s].x = u;
+            if (probing && ALPHA == 0) { pr.sum_u2 = fmaf(u, u, pr.sum_u2); pr.zeros_u -= (u != 0.0f) ? 1 : 0; }   // (the other forms count in the stream)
         }
+        if (probing && ALPHA == 0 && t == 0) pr.zeros_u += n_blk;       // every position without a non-zero update is a zero of u
         __syncthreads();
         MAB_BTICK(5);
         if (MODE == MODE_STEP && ALPHA == 0) {
@@ -586,7 +629,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
             //    weight decay alone (nothing to stream without decay), then update the touched elements
             //    one by one; fma(-lr, 0, x) == x, so the untouched elements are already final
             if (T.weight_decay > 0.0) {
-                stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, NoU{}, blk_base, n_blk);
+                stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, NoU{}, blk_base, n_blk, pr);
                 __syncthreads();                               // the decayed values are read back below
             }
             MAB_BTICK(6);
@@ -599,7 +642,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         } else {
             // 6. stream the whole block; each octet finds its updates through the bitmap
             const SparseU src{w.bitmap, w.prefix, w.mv};
-            stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk);
+            stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk, pr);
         }
         MAB_BTICK(7);
         __syncthreads();                                       // everything is reused by the next unit
@@ -608,6 +651,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
         if (threadIdx.x == 0) atomicAdd(&g_stats_b[15], 1ull);
 #endif
     }
+    if (probing) pr.flush(a.probe);
 }
 
 template <typename TP, int MODE, int ALPHA>
@@ -666,6 +710,8 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
     uint32_t parity = 0;
     bool store_in_flight = false;                                               // thread 0 only
+    UpdateProbe pr;
+    const bool probing = a.probe != nullptr;
 
     int ti = 0;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
@@ -740,7 +786,9 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
             const float u = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
             const int pos = w.spos[s];
             tile[pos] = f32_to_bf16_bits_rne(__fmaf_rn(neg_lr, u, bf16_bits_to_f32(tile[pos])));
+            if (probing) { pr.sum_u2 = fmaf(u, u, pr.sum_u2); pr.zeros_u -= (u != 0.0f) ? 1 : 0; }
         }
+        if (probing && t == 0) pr.zeros_u += n_blk;                             // every position without a non-zero update is a zero of u
         MAB_BTICK(7);
         // the tile goes back
         if (bulk) {
@@ -758,6 +806,7 @@ window_resident_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, in
 #endif
     }
     if (t == 0 && store_in_flight) bulk_wait_all();                            // shared memory must outlive the copy engine's reads
+    if (probing) pr.flush(a.probe);
 }
 
 // ------------------------------------------------------------------------------------ wide kernel
@@ -772,6 +821,7 @@ __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ 
     for (int i = threadIdx.x; i < n_tensors; i += WIN_THREADS) s_first[i] = tensors[i].first_unit_b;
     if (threadIdx.x == 0) s_first[n_tensors] = total_units;
     __syncthreads();
+    UpdateProbe pr;
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int ti = find_tensor(s_first, n_tensors, unit);
@@ -793,9 +843,10 @@ __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ 
             for (int i = threadIdx.x; i < len; i += WIN_THREADS) sm.m_acc[i] = round_as(sm.m_acc[i], true);
             __syncthreads();
         }
-        stream_range<TP, MODE, WIN_THREADS, ALPHA>(T, a, DenseU{sm.m_acc}, blk_base + s0, len);
+        stream_range<TP, MODE, WIN_THREADS, ALPHA>(T, a, DenseU{sm.m_acc}, blk_base + s0, len, pr);
         __syncthreads();   // shared accumulators are reused by the next unit
     }
+    if (MODE == MODE_STEP) pr.flush(a.probe);
 }
 
 template <typename TP, int MODE, int ALPHA>
@@ -883,6 +934,7 @@ int fill_window_args(WindowArgs& a, int64_t steps, int m, double beta1, double b
     a.one_minus_alpha = (float)(1.0 - (double)alpha);
     a.qbs = qbs;
     a.lanes_per_qb = qbs >= 8 ? qbs / 8 : 1;
+    a.probe = nullptr;
     return MAB_OK;
 }
 

@@ -19,6 +19,8 @@ MAB_F32, MAB_BF16 = 0, 1
 MAB_K2D, MAB_D2K = 0, 1
 MAB_MAX_WINDOW = 128
 MAB_STATIC_MAX_TENSORS = 1024
+MAB_PROBE_NORM_G, MAB_PROBE_NORM_U, MAB_PROBE_NORM_E, MAB_PROBE_ZEROS_U, MAB_PROBE_NORM_QE, MAB_PROBE_ZEROS_QE = range(6)
+MAB_PROBE_SLOTS = 8
 
 _DTYPE_CODE = {torch.float32: MAB_F32, torch.bfloat16: MAB_BF16}
 
@@ -50,6 +52,7 @@ class MabStepArgs(Structure):
         ('steps', c_int64), ('m', c_int32), ('quant_block_size', c_int32),
         ('alpha', c_float), ('reserved0', c_int32),
         ('beta1', c_double), ('beta2', c_double), ('eps', c_double),
+        ('probe_out', c_void_p),
     ]
 
 

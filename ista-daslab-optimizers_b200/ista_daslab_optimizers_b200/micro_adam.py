@@ -13,8 +13,9 @@ order of sub-steps.  Differences a caller can observe:
 * alpha == -2 (micro_adam.py:238-273) keeps the residual in `quant_err` between the two fused kernels (gradient and
   parameter of one element type; other combinations take the operator-level path);
 * the logging probes (micro_adam.py:155-156, 306-308, 320-324, 330-350) run only when a `log_fn` is given: every
-  `log_interval` steps the step takes the operator-level path, gathers the same seven numbers and hands
-  `log_fn` the dictionary the reference sends to wandb;
+  `log_interval` steps the fused kernels also sum the reference's quantities into a small device buffer (one more
+  small kernel and one device-to-host read on such a step) and `log_fn` gets the dictionary the reference
+  sends to wandb;
 * `state_dict()` also carries the step counter (the reference loses it, micro_adam.py:35).
 
 There is no CPU path: parameters must live on a CUDA device and the native library must be built.
@@ -214,23 +215,46 @@ class MicroAdam(torch.optim.Optimizer):
                 loss = closure()
 
         self._refresh_entries()
-        probe = None
-        if self.log_fn is not None and self.steps % self.log_interval == 0:                          # micro_adam.py:155,306,320
-            probe = dict(norm_g=0.0, norm_u=0.0, norm_e=0.0, sp_u=0.0, t0=time.time())
-        fused = [e for e in self._entries if e.fused and probe is None]
-        generic = [e for e in self._entries if not e.fused or probe is not None]
+        probe = self._probe_begin()
+        fused = [e for e in self._entries if e.fused]
         if fused:
-            self._fused_step(fused)
-        for e in generic:
-            self._generic_update(e, probe)
+            self._fused_step(fused, probe=probe)
+        for e in self._entries:
+            if not e.fused:
+                self._generic_update(e, probe)
         self._after_update()
-        if probe is not None:
-            self._log(probe)
+        self._probe_end(probe)
         if self.kernel_events and len(self.kernel_events[-1]) == 3:
             ev = torch.cuda.Event(enable_timing=True)   # end of whatever _after_update enqueued
             ev.record()
             self.kernel_events[-1].append(ev)
         return loss
+
+    # ------------------------------------------------------------------------------ logging probes
+    def _probe_begin(self) -> Optional[dict]:
+        """On a logging step (micro_adam.py:155,306,320: every `log_interval` steps, here only when a `log_fn` is given):
+        the dictionary the step's probes are summed into.  The fused kernels add theirs to a small device buffer
+        (`probe['buf']`, MAB_PROBE_SLOTS doubles) that is read back once, at the end of the step."""
+        if self.log_fn is None or self.steps % self.log_interval != 0:
+            return None
+        probe = dict(norm_g=0.0, norm_u=0.0, norm_e=0.0, sp_u=0.0, t0=time.time(), buf=None)
+        if self._entries:
+            probe['buf'] = torch.zeros(N.MAB_PROBE_SLOTS, dtype=torch.float64, device=self._entries[0].p.device)
+        return probe
+
+    def _probe_end(self, probe: Optional[dict]):
+        if probe is None:
+            return
+        if probe['buf'] is not None:
+            b = probe['buf'].tolist()                     # the one device-to-host read of a logging step
+            probe['norm_g'] += b[N.MAB_PROBE_NORM_G]
+            probe['norm_u'] += b[N.MAB_PROBE_NORM_U]
+            probe['norm_e'] += b[N.MAB_PROBE_NORM_E]
+            probe['sp_u'] += b[N.MAB_PROBE_ZEROS_U]
+            if self.densify_update_using_quant_error:
+                probe['norm_qe'] = probe.get('norm_qe', 0.0) + b[N.MAB_PROBE_NORM_QE]
+                probe['sp_qe'] = probe.get('sp_qe', 0.0) + b[N.MAB_PROBE_ZEROS_QE]
+        self._log(probe)
 
     def _log(self, probe: dict):
         """micro_adam.py:330-350: sums the probes over the ranks and hands them to `log_fn` (the reference sends the
@@ -239,7 +263,7 @@ class MicroAdam(torch.optim.Optimizer):
                 probe.get('sp_qe', 0.0), time.time() - probe['t0']]
         dist = torch.distributed
         if dist.is_available() and dist.is_initialized():
-            dev = self._entries[0].p.device if self._entries and dist.get_backend() == 'nccl' else 'cpu'
+            dev = self.param_groups[0]['params'][0].device if dist.get_backend() == 'nccl' else 'cpu'
             sync = torch.tensor(vals, dtype=torch.float, device=dev)
             dist.all_reduce(sync, op=dist.ReduceOp.SUM)
             vals = sync.tolist()
@@ -330,8 +354,9 @@ class MicroAdam(torch.optim.Optimizer):
         d.lr = float(group['lr'])                                                                      # micro_adam.py:121
         d.weight_decay = float(group.get('weight_decay', self.weight_decay))                           # micro_adam.py:122
 
-    def _fused_step(self, entries: List[_Entry], group_key=0):
-        """One fused step over `entries`; `group_key` names the group so that its descriptor array is reused."""
+    def _fused_step(self, entries: List[_Entry], group_key=0, probe: Optional[dict] = None):
+        """One fused step over `entries`; `group_key` names the group so that its descriptor array is reused.  On a
+        logging step the kernels add their probes to `probe['buf']`."""
         lib = N.load()
         n = len(entries)
         descs = self._descs.get(group_key)
@@ -347,10 +372,12 @@ class MicroAdam(torch.optim.Optimizer):
         if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
             self._workspace = torch.empty(need, dtype=torch.uint8, device=device)
         args = self._step_args()
+        if probe is not None:
+            args.probe_out = probe['buf'].data_ptr()
         ws, ws_bytes = self._workspace.data_ptr(), self._workspace.numel()
         with torch.cuda.device(device):
             stream = N.current_stream(device)
-            if self.kernel_events is None:
+            if self.kernel_events is None or probe is not None:
                 N.check(lib.mab_fused_step(descs, n, ctypes.byref(args), ws, ws_bytes, stream), 'mab_fused_step')
             else:
                 # the same two kernels through their own entry points, with CUDA events between them

@@ -300,7 +300,7 @@ class ShardedMicroAdam(MicroAdam):
                 d.lr, d.weight_decay = float(grp['lr']), float(grp.get('weight_decay', self.weight_decay))
         return a_pieces, da, db
 
-    def _rows_call(self, fn_name, descs, n):
+    def _rows_call(self, fn_name, descs, n, probe=None):
         if n == 0:
             return
         lib = N.load()
@@ -310,13 +310,16 @@ class ShardedMicroAdam(MicroAdam):
         if ws is None or ws.numel() < need:
             ws = self._rows_ws[fn_name] = torch.empty(need, dtype=torch.uint8, device=device)
         args = self._step_args()
+        if probe is not None:
+            args.probe_out = probe['buf'].data_ptr()
         with torch.cuda.device(device):
             N.check(getattr(lib, fn_name)(descs, n, ctypes.byref(args), ws.data_ptr(), ws.numel(), N.current_stream(device)), fn_name)
 
-    def rows_phase_a(self):
-        """Kernel A on the owned pieces: writes this rank's region of row `ring` of the window."""
+    def rows_phase_a(self, probe=None):
+        """Kernel A on the owned pieces: writes this rank's region of row `ring` of the window.  On a logging step it is
+        followed by the probes of the owned gradients and error feedback."""
         a_pieces, da, _ = self._rows_fill()
-        self._rows_call('mab_fused_ef_topk_quant', da, len(a_pieces))
+        self._rows_call('mab_fused_ef_topk_quant', da, len(a_pieces), probe)
 
     def current_row(self) -> torch.Tensor:
         """The row of the window this step writes, [world, 2 * width] int16: region r is rank r's to fill."""
@@ -327,10 +330,11 @@ class ShardedMicroAdam(MicroAdam):
         this rank received."""
         return gather_row_regions(self.current_row(), self.rank, self.process_group)
 
-    def rows_phase_b(self):
-        """Kernel B over all parameters, then the ring advances."""
+    def rows_phase_b(self, probe=None):
+        """Kernel B over all parameters, then the ring advances.  Every rank computes the same update, so on a logging
+        step only rank 0 takes its probes (the log sums over the ranks)."""
         _, _, db = self._rows_fill()
-        self._rows_call('mab_fused_window_adam_update', db, len(self._rows_pieces))
+        self._rows_call('mab_fused_window_adam_update', db, len(self._rows_pieces), probe if self.rank == 0 else None)
         self._ring = (self._ring + 1) % self.m
         for st in self._rows_state.values():
             st['index'] = self._ring
@@ -343,21 +347,25 @@ class ShardedMicroAdam(MicroAdam):
 
     def _rows_step(self):
         self.rows_prepare()
+        probe = self._probe_begin()
+        if probe is not None and probe['buf'] is None:
+            probe['buf'] = torch.zeros(N.MAB_PROBE_SLOTS, dtype=torch.float64, device=self._all_params[0].device)
         ev = None
         if self.kernel_events is not None:
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
             ev[0].record()
-        self.rows_phase_a()
+        self.rows_phase_a(probe)
         if ev:
             ev[1].record()
         if self.gather:
             self.last_gather_bytes = self.rows_exchange()
         if ev:
             ev[2].record()
-        self.rows_phase_b()
+        self.rows_phase_b(probe)
         if ev:
             ev[3].record()
             self.kernel_events.append(('rows', ev))
+        self._probe_end(probe)
 
     # ---------------------------------------------------------------------------- checkpoint of the 'rows' mode
     def state_dict(self):
@@ -437,6 +445,7 @@ class ShardedMicroAdam(MicroAdam):
             with torch.enable_grad():
                 loss = closure()
         self._refresh_entries()
+        probe = self._probe_begin()
         device = self._all_params[0].device
         if self._comm_stream is None:
             self._comm_stream = torch.cuda.Stream(device=device)
@@ -447,16 +456,17 @@ class ShardedMicroAdam(MicroAdam):
             entries = [e for e in self._entries if id(e.p) in mine]
             fused = [e for e in entries if e.fused]
             if fused:
-                self._fused_step(fused, group_key=ci)
+                self._fused_step(fused, group_key=ci, probe=probe)
             for e in entries:
                 if not e.fused:
-                    self._generic_update(e)
+                    self._generic_update(e, probe)
             ready = torch.cuda.Event()
             ready.record(compute)
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ready)
                 received += exchange_pieces(views, self.rank, self.process_group)
         compute.wait_stream(self._comm_stream)
+        self._probe_end(probe)
         self.last_gather_bytes = received
         if self.kernel_events:
             ev = torch.cuda.Event(enable_timing=True)

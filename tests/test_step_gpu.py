@@ -114,39 +114,69 @@ def test_rejects_bad_alpha_and_cpu_params():
         opt.step()
 
 
-def test_logging_probes_report_the_reference_quantities():
-    """log_fn switches the probes of micro_adam.py:155-156, 306-308, 320-324 on: every log_interval steps the
-    seven numbers of micro_adam.py:330-350 arrive; the state stays what the unprobed optimizer produces."""
+@pytest.mark.parametrize('name', ['bf16_wd', 'c1_fp32_1m', 'mixed_fp32_alpha', 'alpha_m2', 'wide_fp32'])
+def test_logging_probes_report_the_reference_quantities(name):
+    """log_fn switches the probes of micro_adam.py:155-156, 272-273, 306-308, 320-324 on: every log_interval steps the
+    numbers of micro_adam.py:330-350 arrive, taken by the fused kernels (one more small kernel and one read on such a
+    step); the state stays what the unprobed optimizer produces.  Expected values come from the oracle's state."""
     import math
+    from ista_daslab_optimizers_b200 import _native
     from oracle import microadam_oracle as O
-    case = cases.CASES['bf16_wd']
+    case = cases.CASES[name]
     logged = []
     plain = cases.CudaAdapter(case, case.params())
     probed = cases.CudaAdapter(case, case.params())
+    ref = cases.OracleAdapter(case, case.params())
     probed.opt.log_fn = logged.append
     probed.opt.log_interval = 2
+    n_total = sum(int(torch.Size(s).numel()) for s in case.shapes)
     for t in range(4):
         grads = case.grads(t)
         plain.step(grads)
+        before = _native.kernel_launch_count()
         probed.step(grads)
-        if (t + 1) % 2 == 0:
-            rec = logged[-1]
-            assert rec['step/optimizer_steps'] == t + 1
-            norm_g = math.sqrt(sum(float(g.float().norm() ** 2) for g in grads))
-            assert rec['step/norm_g'] == pytest.approx(norm_g, rel=1e-3)
-            norm_e = 0.0
-            for i in range(len(case.shapes)):
-                st = probed.state(i)
-                x = torch.zeros(st['d'], dtype=case.dtype)
-                O.asymm_block_quant_inv(st['d'], case.qbs, st['error'].cpu(), st['min_vals'].cpu(), st['max_vals'].cpu(), x, 1.0)
-                norm_e += float(x.float().norm() ** 2)
-            assert rec['step/norm_error'] == pytest.approx(math.sqrt(norm_e), rel=1e-3)
-            assert 0.0 < rec['step/sparsity_u'] < 100.0 and rec['step/norm_u'] > 0.0
+        launches = _native.kernel_launch_count() - before
+        ref.step(grads)
+        assert all(e.fused for e in probed.opt._entries)
+        if (t + 1) % 2:
+            assert launches == 2
+            continue
+        assert launches == 3
+        rec = logged[-1]
+        assert rec['step/optimizer_steps'] == t + 1
+        norm_g = math.sqrt(sum(float(g.double().norm() ** 2) for g in grads))
+        assert rec['step/norm_g'] == pytest.approx(norm_g, rel=1e-4)
+        norm_e = norm_u = zeros_u = norm_qe = zeros_qe = 0.0
+        for i in range(len(case.shapes)):
+            st = ref.opt.state[i]
+            geo = st['geo']
+            x = torch.zeros(geo.d, dtype=case.dtype)
+            O.asymm_block_quant_inv(geo.d, case.qbs, st['error'], st['min_vals'], st['max_vals'], x, 1.0)
+            norm_e += float(x.double().norm() ** 2)
+            if case.alpha <= 0:                                  # u is the window's update alone: recomputed from the oracle's window
+                u = torch.zeros(geo.d, dtype=case.dtype)
+                O.compute_microadam_update(0, 0, 0, ref.opt.steps, *case.betas, case.eps, geo.d_block_size, geo.k_block_size_many,
+                                           geo.d, case.m, geo.k, st['I'], st['V'], u)
+                norm_u += float(u.double().norm() ** 2)
+                zeros_u += float((u == 0).sum())
+            if case.alpha == -2:
+                norm_qe += float(st['quant_err'].double().norm() ** 2)
+                zeros_qe += float((st['quant_err'] == 0).sum())
+        tol = 1e-3 if case.dtype == torch.float32 else 1e-2
+        assert rec['step/norm_error'] == pytest.approx(math.sqrt(norm_e), rel=tol)
+        if case.alpha <= 0:
+            assert rec['step/norm_u'] == pytest.approx(math.sqrt(norm_u), rel=tol)
+            assert rec['step/sparsity_u'] == pytest.approx(zeros_u / n_total * 100, rel=1e-4)
+        else:
+            assert 0.0 <= rec['step/sparsity_u'] < 100.0 and rec['step/norm_u'] > 0.0
+        if case.alpha == -2:
+            assert rec['step/norm_quant_err'] == pytest.approx(math.sqrt(norm_qe), rel=tol, abs=1e-12)
+            assert rec['step/sparsity_quant_err'] == pytest.approx(zeros_qe / n_total * 100, abs=0.5)
     assert len(logged) == 2
     for i in range(len(case.shapes)):
         a, b = plain.state(i), probed.state(i)
         assert torch.equal(a['I'], b['I']) and torch.equal(a['error'], b['error'])
-        torch.testing.assert_close(plain.param(i).float(), probed.param(i).float(), rtol=1e-2, atol=1e-9)
+        assert torch.equal(plain.param(i), probed.param(i))
 
 
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
