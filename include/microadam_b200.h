@@ -232,7 +232,7 @@ int mab_fused_window_adam_update(mab_tensor* tensors, int n_tensors, const mab_s
  * pass only the buffers its own runtime tracks (parameters, gradients, optimizer state) and not
  * create a new one.  For them the table of tensor descriptors that the two kernels read lives in
  * a fixed array inside the library instead: MAB_STATIC_MAX_TENSORS * sizeof(mab_tensor) bytes
- * (136 KiB) of device memory per GPU, held by every GPU that loads the library until the process
+ * (144 KiB) of device memory per GPU, held by every GPU that loads the library until the process
  * exits.  The call allocates nothing, on the device or on the host.
  *
  * Same arguments, results and errors as mab_fused_step, minus the workspace, with these differences:

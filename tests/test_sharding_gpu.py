@@ -154,3 +154,42 @@ def test_row_exchange_checkpoint_resume():
         full.step(grads)
         rows_step(fresh, grads)
         assert_rows_ranks_equal_unsharded(case, full, fresh, t)
+
+
+def test_row_exchange_logging_probes_add_up_to_the_unsharded_ones():
+    """On a logging step every rank reports the probes of its own slices (gradient, error feedback) and rank 0 those of
+    the update (which every rank computes alike); summed over the ranks, as the log does, they are the unsharded run's."""
+    case = cases.CASES['bf16_wd']
+    full = cases.CudaAdapter(case, case.params())
+    full_log, rank_logs = [], [[], []]
+    full.opt.log_fn, full.opt.log_interval = full_log.append, 2
+    ranks = make_rows_ranks(case, 2)
+    for r, (_, opt) in enumerate(ranks):
+        opt.log_fn, opt.log_interval = rank_logs[r].append, 2
+    for t in range(2):
+        grads = case.grads(t)
+        full.step(grads)
+        for r, (params, opt) in enumerate(ranks):
+            for p, g in zip(params, grads):
+                p.grad = g.cuda()
+        # the public step of the emulated ranks, without a process group: run the phases by hand around the copied row
+        for _, opt in ranks:
+            opt.steps += 1
+            opt.rows_prepare()
+        probes = [opt._probe_begin() for _, opt in ranks]
+        for (_, opt), pr in zip(ranks, probes):
+            if pr is not None and pr['buf'] is None:
+                pr['buf'] = torch.zeros(8, dtype=torch.float64, device='cuda')
+            opt.rows_phase_a(pr)
+        for r_src, (_, src) in enumerate(ranks):
+            for r_dst, (_, dst) in enumerate(ranks):
+                if r_dst != r_src:
+                    dst.current_row()[r_src].copy_(src.current_row()[r_src])
+        for (_, opt), pr in zip(ranks, probes):
+            opt.rows_phase_b(pr)
+            opt._probe_end(pr)
+    assert len(full_log) == 1 and all(len(l) == 1 for l in rank_logs)
+    for key in ('step/norm_g', 'step/norm_u', 'step/norm_error'):
+        total = sum(l[0][key] ** 2 for l in rank_logs) ** 0.5
+        assert total == pytest.approx(full_log[0][key], rel=1e-5), key
+    assert sum(l[0]['step/sparsity_u'] for l in rank_logs) == pytest.approx(full_log[0]['step/sparsity_u'], rel=1e-6)
