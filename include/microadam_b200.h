@@ -193,13 +193,32 @@ typedef struct mab_step_args {
                                     mab_fused_window_adam_update alone the update's.               */
 } mab_step_args;
 
-/* Bytes of device workspace mab_fused_step needs for n_tensors tensors. */
+/* Bytes of device workspace mab_fused_step needs for n_tensors tensors when quant_block_size is a power of two
+ * in [8, 128]. */
 int64_t mab_fused_step_workspace_bytes(int n_tensors);
 
-/* 1 if the fused kernels cover this geometry (quant_block_size a power of two in [8, 128] that
- * divides d_block_size, d_block_size <= 32768, supported dtypes, aligned pointers; alpha in [0, 1), or
- * alpha == -2 with quant_err and equal gradient / parameter element types), else 0. */
+/* Bytes of device workspace for these tensors and this quant_block_size, whatever it is: for a power of two in
+ * [8, 128] the figure above, otherwise also 8 bytes per quantisation block of every tensor (scratch in which
+ * the tiles of a block merge their minima and maxima) and 8 bytes per tensor. */
+int64_t mab_fused_step_workspace_bytes_for(const mab_tensor* tensors, int n_tensors, const mab_step_args* args);
+
+/* Whether the fused kernels cover this geometry (d_block_size <= 32768, supported dtypes, aligned pointers):
+ *   1  quant_block_size is a power of two in [8, 128] that divides d_block_size; alpha in [0, 1), or alpha == -2
+ *      with quant_err and equal gradient / parameter element types.  The gradient buffer is only read.
+ *   2  any other quant_block_size that is a multiple of 8 in [64, 2^30] (the reference's README uses 100000),
+ *      alpha == 0.  Quantisation blocks then ignore the borders of the top-k blocks (micro_adam.py:217-231), so
+ *      kernel A runs in two parts: the first leaves the residual IN THE GRADIENT BUFFER (the reference overwrites
+ *      it in the same step too) and each block's extremes in the workspace, the second writes statistics and
+ *      codes.  The workspace size comes from mab_fused_step_workspace_bytes_for; mab_fused_step_static does
+ *      not take this form.
+ *   0  neither. */
 int mab_fused_supported(const mab_tensor* t, const mab_step_args* args);
+
+/* 1 if mab_fused_window_adam_update alone covers this tensor.  With alpha == 0 kernel B reads neither the error
+ * feedback nor the gradient, so any quant_block_size qualifies and error / min_vals / max_vals / grad may be NULL:
+ * a step whose first half ran on the operator-level calls (quantisation blocks that straddle top-k blocks) can
+ * still take its second half fused.  Otherwise the same conditions as mab_fused_supported. */
+int mab_fused_window_supported(const mab_tensor* t, const mab_step_args* args);
 
 /* The whole step of micro_adam.py:146-328 for n_tensors tensors in two kernels:
  *   A  dequantise EF + add gradient, block top-k into row ring_index of I / V, zero the selected

@@ -88,15 +88,48 @@ extern "C" int64_t mab_fused_step_workspace_bytes(int n_tensors) {
 
 static bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 
+// Quantisation blocks that the one-kernel form of kernel A covers: they tile every top-k block exactly.
+static bool aligned_qbs(int64_t qbs) { return is_pow2(qbs) && qbs >= 8 && qbs <= 128; }
+
+static int64_t round256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+// Workspace of a call whose quantisation blocks have any other size ("loose"): the descriptor table, the first
+// scratch entry of every tensor, and two uint32 per quantisation block for the merged extremes.
+struct LooseLayout { int64_t off_first, off_min, off_max, total_qb, bytes; };
+static LooseLayout loose_layout(const mab_tensor* tensors, int n, int64_t qbs) {
+    LooseLayout L;
+    L.total_qb = 0;
+    for (int i = 0; i < n; ++i) L.total_qb += tensors[i].d > 0 ? ceil_div64(tensors[i].d, qbs) : 0;
+    L.off_first = round256(mab_fused_step_workspace_bytes(n));
+    L.off_min = L.off_first + round256((int64_t)std::max(n, 1) * 8);
+    L.off_max = L.off_min + round256(L.total_qb * 4);
+    L.bytes = L.off_max + round256(L.total_qb * 4);
+    return L;
+}
+
+extern "C" int64_t mab_fused_step_workspace_bytes_for(const mab_tensor* tensors, int n_tensors, const mab_step_args* args) {
+    if (!tensors || !args || n_tensors <= 0 || args->quant_block_size <= 0 || aligned_qbs(args->quant_block_size))
+        return mab_fused_step_workspace_bytes(n_tensors);
+    return loose_layout(tensors, n_tensors, args->quant_block_size).bytes;
+}
+
 // Why a tensor cannot take the fused path, or nullptr if it can.
-static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
+// `window_only`: kernel B alone with alpha == 0 reads neither the error feedback nor the gradient, so the
+// quantisation geometry does not matter (any quant_block_size) and those buffers may be absent.
+static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a, bool window_only = false) {
     if (!t || !a) return "null argument";
     if (t->d <= 0) return "empty tensor";
-    if (!t->param || !t->grad || !t->error || !t->min_vals || !t->max_vals || !t->I || !t->V) return "null buffer";
+    window_only = window_only && a->alpha == 0.0f;
+    if (!t->param || !t->I || !t->V) return "null buffer";
+    if (!window_only && (!t->grad || !t->error || !t->min_vals || !t->max_vals)) return "null buffer";
     if (t->param_dtype != MAB_F32 && t->param_dtype != MAB_BF16) return "param dtype is neither f32 nor bf16";
     if (t->grad_dtype != MAB_F32 && t->grad_dtype != MAB_BF16) return "grad dtype is neither f32 nor bf16";
-    const int qbs = a->quant_block_size;
-    if (!is_pow2(qbs) || qbs < 8 || qbs > 128) return "quant_block_size is not a power of two in [8, 128]";
+    const int qbs = window_only ? 8 : a->quant_block_size;
+    const bool loose = !aligned_qbs(qbs);                  // quantisation blocks that ignore the borders of the top-k blocks
+    if (loose) {
+        if (qbs < 64 || qbs % 8 != 0 || qbs > (1 << 30)) return "quant_block_size is neither a power of two in [8, 128] nor a multiple of 8 in [64, 2^30]";
+        if (a->alpha != 0.0f) return "quantisation blocks that straddle top-k blocks need alpha == 0 on the fused path";
+    }
     if (a->alpha == -2.0f) {
         if (!t->quant_err) return "alpha == -2 needs quant_err";
         if (t->param_dtype != t->grad_dtype) return "alpha == -2 needs gradient and parameter of one element type";
@@ -107,7 +140,8 @@ static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
     const int64_t covered = nfull * t->d_block_size;
     if (nfull < 0 || covered > t->d || t->d - covered >= t->d_block_size) return "block counts inconsistent with d";
     const bool multi = covered < t->d ? nfull >= 1 : nfull > 1;
-    if (multi && t->d_block_size % qbs != 0) return "d_block_size is not a multiple of quant_block_size";
+    if (multi && !loose && t->d_block_size % qbs != 0) return "d_block_size is not a multiple of quant_block_size";
+    if (multi && loose && t->d_block_size % 8 != 0) return "d_block_size is not a multiple of 8";
     if (t->k_block_size_many < 1 || t->k_block_size_many > t->d_block_size) return "k_block_size_many out of range";
     if ((covered < t->d) != (t->k_block_size_few > 0) || t->k_block_size_few > t->d - covered) return "k_block_size_few out of range";
     if (t->k != nfull * t->k_block_size_many + t->k_block_size_few) return "k inconsistent with the block geometry";
@@ -115,14 +149,20 @@ static const char* fused_obstacle(const mab_tensor* t, const mab_step_args* a) {
     if (nfull + 1 >= (int64_t)1 << 28) return "too many blocks";
     if (t->ring_index < 0 || t->ring_index >= a->m) return "ring_index outside [0, m)";
     const size_t pe = t->param_dtype == MAB_F32 ? 4 : 2, ge = t->grad_dtype == MAB_F32 ? 4 : 2;
-    if (!aligned_to(t->param, pe) || !aligned_to(t->grad, ge) || !aligned_to(t->min_vals, 2) ||
-        !aligned_to(t->max_vals, 2) || !aligned_to(t->I, 2) || !aligned_to(t->V, 2) ||
+    if (!aligned_to(t->param, pe) || !aligned_to(t->I, 2) || !aligned_to(t->V, 2) ||
         (t->quant_err && !aligned_to(t->quant_err, pe))) return "buffer not aligned to its element size";
+    if (!window_only && (!aligned_to(t->grad, ge) || !aligned_to(t->min_vals, 2) || !aligned_to(t->max_vals, 2)))
+        return "buffer not aligned to its element size";
     return nullptr;
 }
 
 extern "C" int mab_fused_supported(const mab_tensor* t, const mab_step_args* args) {
-    return fused_obstacle(t, args) == nullptr ? 1 : 0;
+    if (fused_obstacle(t, args) != nullptr) return 0;
+    return aligned_qbs(args->quant_block_size) ? 1 : 2;
+}
+
+extern "C" int mab_fused_window_supported(const mab_tensor* t, const mab_step_args* args) {
+    return fused_obstacle(t, args, true) == nullptr ? 1 : 0;
 }
 
 enum { RUN_A = 1, RUN_B = 2 };
@@ -132,13 +172,16 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
     MAB_REQUIRE(n >= 0, MAB_ERR_BAD_ARG, "fused step: n_tensors=%d", n);
     if (n == 0) return MAB_OK;
     MAB_REQUIRE(tensors && args && workspace, MAB_ERR_BAD_ARG, "fused step: null argument");
-    MAB_REQUIRE(workspace_bytes >= mab_fused_step_workspace_bytes(n), MAB_ERR_BAD_ARG,
-                "fused step: workspace of %lld bytes, %lld needed", (long long)workspace_bytes,
-                (long long)mab_fused_step_workspace_bytes(n));
+    const bool loose = (what & RUN_A) && !aligned_qbs(args->quant_block_size);
+    MAB_REQUIRE(args->quant_block_size > 0, MAB_ERR_BAD_ARG, "fused step: quant_block_size=%d", args->quant_block_size);
+    const int64_t need = loose ? mab_fused_step_workspace_bytes_for(tensors, n, args) : mab_fused_step_workspace_bytes(n);
+    MAB_REQUIRE(workspace_bytes >= need, MAB_ERR_BAD_ARG,
+                "fused step: workspace of %lld bytes, %lld needed%s", (long long)workspace_bytes, (long long)need,
+                loose ? " (mab_fused_step_workspace_bytes_for gives the size for this quant_block_size)" : "");
     MAB_REQUIRE(aligned_to(workspace, 16), MAB_ERR_BAD_ARG, "fused step: workspace must be 16-byte aligned");
     MAB_REQUIRE(args->steps >= 1, MAB_ERR_BAD_ARG, "fused step: steps=%lld", (long long)args->steps);
     for (int i = 0; i < n; ++i) {
-        const char* why = fused_obstacle(&tensors[i], args);
+        const char* why = fused_obstacle(&tensors[i], args, what == RUN_B);
         MAB_REQUIRE(why == nullptr, MAB_ERR_UNSUPPORTED, "fused step: tensor %d: %s", i, why);
     }
     if (device_sm_count() < 0) return MAB_ERR_CUDA;
@@ -181,9 +224,36 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
     MAB_CUDA_TRY(cudaMemcpyAsync(workspace, staged.data(), (size_t)n * sizeof(mab_tensor), cudaMemcpyHostToDevice, s));
     const mab_tensor* dev = reinterpret_cast<const mab_tensor*>(workspace);
 
-    if (what & RUN_A)
+    if (loose) {
+        // kernel A in two parts: residual + merged block extremes, then statistics + codes.  The gradient
+        // buffers end up holding the residual, so their probe runs first.
+        const int qbs = args->quant_block_size;
+        const LooseLayout L = loose_layout(tensors, n, qbs);
+        unsigned char* ws = static_cast<unsigned char*>(workspace);
+        static thread_local std::vector<int64_t> qb_first;
+        qb_first.resize(n);
+        int64_t at = 0;
+        for (int i = 0; i < n; ++i) { qb_first[i] = at; at += ceil_div64(staged[i].d, qbs); }
+        MAB_CUDA_TRY(cudaMemcpyAsync(ws + L.off_first, qb_first.data(), (size_t)n * 8, cudaMemcpyHostToDevice, s));
+        MAB_CUDA_TRY(cudaMemsetAsync(ws + L.off_min, 0xFF, (size_t)L.total_qb * 4, s));
+        MAB_CUDA_TRY(cudaMemsetAsync(ws + L.off_max, 0x00, (size_t)L.total_qb * 4, s));
+        if (args->probe_out)
+            for (const Chunk& c : chunks)
+                if (int rc = launch_probe(dev + c.first, c.count, c.units_a, qbs, args->probe_out, s, PROBE_G)) return rc;
+        for (const Chunk& c : chunks) {
+            const LooseArgs la = {qbs, reinterpret_cast<uint32_t*>(ws + L.off_min), reinterpret_cast<uint32_t*>(ws + L.off_max),
+                                  reinterpret_cast<const int64_t*>(ws + L.off_first) + c.first};
+            if (int rc = launch_ef_topk_quant(dev + c.first, c.count, c.units_a, c.grad_dtype, qbs, c.max_dbs, s, &la)) return rc;
+        }
+        for (const Chunk& c : chunks) {
+            const LooseArgs la = {qbs, reinterpret_cast<uint32_t*>(ws + L.off_min), reinterpret_cast<uint32_t*>(ws + L.off_max),
+                                  reinterpret_cast<const int64_t*>(ws + L.off_first) + c.first};
+            if (int rc = launch_requant_loose(dev + c.first, c.count, c.units_a, c.grad_dtype, la, s)) return rc;
+        }
+    } else if (what & RUN_A) {
         for (const Chunk& c : chunks)
             if (int rc = launch_ef_topk_quant(dev + c.first, c.count, c.units_a, c.grad_dtype, args->quant_block_size, c.max_dbs, s)) return rc;
+    }
     if (what & RUN_B) {
         WindowArgs wa;
         if (int rc = fill_window_args(wa, args->steps, args->m, args->beta1, args->beta2, args->eps, args->alpha,
@@ -195,7 +265,8 @@ static int fused_run(mab_tensor* tensors, int n, const mab_step_args* args, void
     }
     if (args->probe_out && (what & RUN_A))                     // gradient and final error feedback: after the call's last kernel
         for (const Chunk& c : chunks)
-            if (int rc = launch_probe(dev + c.first, c.count, c.units_a, args->quant_block_size, args->probe_out, s)) return rc;
+            if (int rc = launch_probe(dev + c.first, c.count, c.units_a, args->quant_block_size, args->probe_out, s,
+                                      loose ? PROBE_E : PROBE_G | PROBE_E)) return rc;
     return MAB_OK;
 }
 
@@ -271,6 +342,9 @@ extern "C" int mab_fused_step_static(mab_tensor* tensors, int n, const mab_step_
     if (n == 0) return MAB_OK;
     MAB_REQUIRE(tensors && args, MAB_ERR_BAD_ARG, "mab_fused_step_static: null argument");
     MAB_REQUIRE(args->steps >= 1, MAB_ERR_BAD_ARG, "mab_fused_step_static: steps=%lld", (long long)args->steps);
+    MAB_REQUIRE(aligned_qbs(args->quant_block_size), MAB_ERR_UNSUPPORTED,
+                "mab_fused_step_static: quant_block_size=%d needs scratch memory (a power of two in [8, 128] does not); use mab_fused_step",
+                args->quant_block_size);
     for (int i = 0; i < n; ++i) {
         const char* why = fused_obstacle(&tensors[i], args);
         MAB_REQUIRE(why == nullptr, MAB_ERR_UNSUPPORTED, "mab_fused_step_static: tensor %d: %s", i, why);

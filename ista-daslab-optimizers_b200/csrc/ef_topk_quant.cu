@@ -128,7 +128,7 @@ struct Stage {
 
 // Starts the copies of a staged tile: one thread arms the barrier and issues the bulk copies of the
 // gradient and the codes (one copy each); the statistics (a few hundred bf16) go through cp.async.
-template <typename TG>
+template <typename TG, bool WITH_STATS = true>
 __device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG>& st, uint64_t* bar, int qshift) {
     if (threadIdx.x == SEL_THREADS - 32) {           // first lane of the last warp: warp 0 has serial work of its own
         const uint32_t gb = (uint32_t)r.n * (uint32_t)sizeof(TG), eb = (uint32_t)r.n >> 1;
@@ -136,6 +136,7 @@ __device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG
         bulk_g2s(st.g, r.g, gb, bar);
         bulk_g2s(st.ef, r.ef, eb, bar);
     }
+    if (!WITH_STATS) return;
     const int words = (((r.n >> qshift) + r.stat_skip) + 1) >> 1;      // 4-byte words covering the tile's statistics
     const uint32_t* mn_src = reinterpret_cast<const uint32_t*>(r.mn - r.stat_skip);
     const uint32_t* mx_src = reinterpret_cast<const uint32_t*>(r.mx - r.stat_skip);
@@ -146,14 +147,69 @@ __device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG
     cp_async_commit();
 }
 
+// ---- quantisation blocks of any size ("loose": they ignore the borders of the top-k blocks, micro_adam.py:217-231) ----
+//
+// A quantisation block may then span several tiles, so a tile cannot requantise its residual by itself.  The
+// kernel below runs in a second form for that case: the old statistics are read per octet from global memory,
+// and instead of statistics + codes it leaves (1) the residual, in the gradient buffer (which the reference
+// overwrites in the same step too) and (2) per quantisation block the minimum and maximum of the residual in
+// two scratch arrays, as order-preserving unsigned keys merged with atomicMin / atomicMax.  A second kernel
+// (requant_loose_kernel) then reads the residual once, rounds the merged statistics to bf16 and writes codes
+// and statistics.  Octets never straddle a quantisation block: quant_block_size is a multiple of 8.
+constexpr int LOOSE_MAX_QB = SEL_MAX_TILE / 64 + 2;   // quantisation blocks a tile can touch
+
 template <typename TG>
+__device__ __forceinline__ TileRef<TG> tile_ref_loose(const mab_tensor& T, int blk) {
+    TileRef<TG> r;
+    const int dbs = T.d_block_size;
+    const int64_t base = (int64_t)blk * dbs;
+    r.n = (int)min((int64_t)dbs, T.d - base);
+    r.k = (blk < T.topk_full_blocks_count) ? T.k_block_size_many : T.k_block_size_few;
+    r.g = reinterpret_cast<const TG*>(T.grad) + base;
+    r.ef = T.error + (base >> 1);
+    r.mn = T.min_vals; r.mx = T.max_vals; r.stat_skip = 0;       // statistics are indexed per octet, from the tensor's first
+    r.staged = (r.n & 31) == 0 && aligned16(r.g) && aligned16(r.ef);
+    return r;
+}
+
+template <typename TG>
+__device__ __forceinline__ void store_residual_octet(TG* dst, const float (&a)[8], bool vec, int cnt);
+template <>
+__device__ __forceinline__ void store_residual_octet<float>(float* dst, const float (&a)[8], bool vec, int cnt) {
+    if (vec && cnt >= 8) {
+        reinterpret_cast<float4*>(dst)[0] = make_float4(a[0], a[1], a[2], a[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(a[4], a[5], a[6], a[7]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) if (e < cnt) dst[e] = a[e];
+    }
+}
+template <>
+__device__ __forceinline__ void store_residual_octet<uint16_t>(uint16_t* dst, const float (&a)[8], bool vec, int cnt) {
+    if (vec && cnt >= 8) {                              // the values are bf16 already: the high halves are exact
+        uint4 w;
+        w.x = (__float_as_uint(a[0]) >> 16) | (__float_as_uint(a[1]) & 0xFFFF0000u);
+        w.y = (__float_as_uint(a[2]) >> 16) | (__float_as_uint(a[3]) & 0xFFFF0000u);
+        w.z = (__float_as_uint(a[4]) >> 16) | (__float_as_uint(a[5]) & 0xFFFF0000u);
+        w.w = (__float_as_uint(a[6]) >> 16) | (__float_as_uint(a[7]) & 0xFFFF0000u);
+        *reinterpret_cast<uint4*>(dst) = w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) if (e < cnt) dst[e] = (uint16_t)(__float_as_uint(a[e]) >> 16);
+    }
+}
+
+template <typename TG, bool LOOSE>
 __global__ void __launch_bounds__(SEL_THREADS, 1)
-ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
+ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems,
+                     LooseArgs la) {
     extern __shared__ __align__(128) unsigned char stage_raw[];      // [staging area | SelectSmem | FastSelSmem]
     SelectSmem& sm = *reinterpret_cast<SelectSmem*>(stage_raw + Stage<TG>::bytes(stage_elems, qshift));
     FastSelSmem& fs = *reinterpret_cast<FastSelSmem*>(stage_raw + Stage<TG>::bytes(stage_elems, qshift) + sizeof(SelectSmem));
     __shared__ int s_first[A_MAX_TENSORS + 1];
     __shared__ __align__(8) uint64_t s_bar;
+    __shared__ uint32_t s_qlo[LOOSE ? LOOSE_MAX_QB : 1], s_qhi[LOOSE ? LOOSE_MAX_QB : 1];   // loose: the tile's part of the block statistics
+    const bool big_qb = LOOSE && la.qbs >= SEL_MAX_TILE;        // a tile then touches at most two quantisation blocks
     const Stage<TG> st(stage_raw, stage_elems, qshift);
     int guess = 0;                                  // lower bound found for the previous tile, as key bits
     for (int i = threadIdx.x; i < n_tensors; i += SEL_THREADS) s_first[i] = tensors[i].first_unit_a;
@@ -167,19 +223,26 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
     bool cur_staged = false;
     if ((int)blockIdx.x < total_units) {
         const int ti = find_tensor(s_first, n_tensors, blockIdx.x);
-        const TileRef<TG> r = tile_ref<TG>(tensors[ti], blockIdx.x - s_first[ti], qshift);
+        const TileRef<TG> r = LOOSE ? tile_ref_loose<TG>(tensors[ti], blockIdx.x - s_first[ti])
+                                    : tile_ref<TG>(tensors[ti], blockIdx.x - s_first[ti], qshift);
         cur_staged = r.staged && r.n <= stage_elems;
-        if (cur_staged) stage_issue(r, st, &s_bar, qshift);
+        if (cur_staged) stage_issue<TG, !LOOSE>(r, st, &s_bar, qshift);
     }
 
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int ti = find_tensor(s_first, n_tensors, unit);
         const mab_tensor& T = tensors[ti];
         const int blk = unit - s_first[ti];
-        const TileRef<TG> tr = tile_ref<TG>(T, blk, qshift);
+        const TileRef<TG> tr = LOOSE ? tile_ref_loose<TG>(T, blk) : tile_ref<TG>(T, blk, qshift);
         const int n = tr.n, k = tr.k;
         const int64_t base = (int64_t)blk * T.d_block_size;
         const bool vec_e = (reinterpret_cast<uintptr_t>(tr.ef) & 3) == 0;
+        // loose: the tile's first quantisation block and where the tile starts inside it
+        const int64_t lqb0 = LOOSE ? base / la.qbs : 0;
+        const int lrem0 = LOOSE ? (int)(base - lqb0 * la.qbs) : 0;
+        if (LOOSE) {
+            for (int i = threadIdx.x; i < LOOSE_MAX_QB; i += SEL_THREADS) { s_qlo[i] = 0xFFFFFFFFu; s_qhi[i] = 0u; }
+        }
 
         MAB_TICK_DECL
         // ---- a = g + Qinv(e), rounded to the gradient's element type ------------------------
@@ -201,7 +264,13 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 const int o = j * SEL_THREADS + (int)threadIdx.x;
                 omax[j] = 0.0f;
                 if (o < n_oct) {
-                    const QParams q = qparams(s_mn[o >> oshift], s_mx[o >> oshift]);
+                    QParams q;
+                    if (LOOSE) {
+                        const int64_t qb = lqb0 + loose_block(lrem0 + o * 8, la.qbs, big_qb);
+                        q = qparams(__ldg(tr.mn + qb), __ldg(tr.mx + qb));
+                    } else {
+                        q = qparams(s_mn[o >> oshift], s_mx[o >> oshift]);
+                    }
                     float gv[8], x[8];
                     staged_octet(st.g + o * 8, gv);
                     decode_octet(st.ef[o], q, x);
@@ -221,7 +290,8 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 const int cnt = n - o * 8;               // >= 8: full octet, 1..7: the tensor's last, <= 0: none
                 omax[j] = 0.0f;
                 if (cnt > 0) {
-                    const QParams q = qparams(tr.mn[o >> oshift], tr.mx[o >> oshift]);
+                    const int64_t qb = LOOSE ? lqb0 + loose_block(lrem0 + o * 8, la.qbs, big_qb) : (int64_t)(o >> oshift);
+                    const QParams q = qparams(tr.mn[qb], tr.mx[qb]);
                     uint32_t w = 0;
                     if (vec_e && cnt >= 8) w = __ldg(reinterpret_cast<const uint32_t*>(tr.ef + o * 4));
                     else {
@@ -249,9 +319,10 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
         if (unit + (int)gridDim.x < total_units) {
             const int nu = unit + gridDim.x;
             const int nti = find_tensor(s_first, n_tensors, nu);
-            const TileRef<TG> nr = tile_ref<TG>(tensors[nti], nu - s_first[nti], qshift);
+            const TileRef<TG> nr = LOOSE ? tile_ref_loose<TG>(tensors[nti], nu - s_first[nti])
+                                         : tile_ref<TG>(tensors[nti], nu - s_first[nti], qshift);
             cur_staged = nr.staged && nr.n <= stage_elems;
-            if (cur_staged) stage_issue(nr, st, &s_bar, qshift);
+            if (cur_staged) stage_issue<TG, !LOOSE>(nr, st, &s_bar, qshift);
         }
 
         MAB_TICK(11);
@@ -320,6 +391,21 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
 #pragma unroll
                 for (int e = 0; e < 8; ++e) if (e < cnt) { lo = fminf(lo, a[j][e]); hi = fmaxf(hi, a[j][e]); }
             }
+            if (LOOSE) {
+                // the residual goes back to the gradient buffer, its extremes to the tile's entries of the block statistics
+                if (cnt > 0) store_residual_octet<TG>(const_cast<TG*>(tr.g) + o * 8, a[j], aligned16(tr.g), cnt);
+                const int qi = cnt > 0 ? loose_block(lrem0 + o * 8, la.qbs, big_qb) : -1;
+                uint32_t klo = ord_key(lo), khi = ord_key(hi);          // an octet past the end holds (+inf, -inf): neutral
+                const int q_first = __shfl_sync(0xffffffffu, qi, 0), q_last = __shfl_sync(0xffffffffu, qi, 31);
+                if (q_first == q_last) {                                 // the warp's 32 octets lie in one block (or past the end)
+                    klo = __reduce_min_sync(0xffffffffu, klo);
+                    khi = __reduce_max_sync(0xffffffffu, khi);
+                    if (lane_id() == 0 && qi >= 0) { atomicMin(&s_qlo[qi], klo); atomicMax(&s_qhi[qi], khi); }
+                } else if (qi >= 0) {
+                    atomicMin(&s_qlo[qi], klo); atomicMax(&s_qhi[qi], khi);
+                }
+                continue;
+            }
             // bf16 rounding is monotone and odd, so the block statistics are the lane-wise maximum of the
             // rounded (-min, max) pairs: one packed value and one packed max per shuffle step
             uint32_t st_b = pack_bf16x2_rne(-lo, hi);
@@ -344,6 +430,15 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
         }
         MAB_TICK(14);
         __syncthreads();   // selection scratch is reused by the next unit
+        if (LOOSE) {
+            const int n_qb = loose_block(lrem0 + n - 1, la.qbs, false) + 1;      // blocks the tile touches
+            const int64_t at = la.qb_first[ti] + lqb0;
+            for (int i = threadIdx.x; i < n_qb; i += SEL_THREADS) {
+                atomicMin(la.st_min + at + i, s_qlo[i]);
+                atomicMax(la.st_max + at + i, s_qhi[i]);
+            }
+            __syncthreads();   // the entries are reset at the start of the next unit
+        }
         MAB_TICK(15);
     }
 }
@@ -351,32 +446,36 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
 int units_a_of(const mab_tensor& t) { return t.topk_full_blocks_count + (t.k_block_size_few > 0 ? 1 : 0); }
 
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
-                         int qbs, int max_dbs, cudaStream_t s) {
-    if (grad_dtype == MAB_BF16) {          // bf16 tiles are small enough for two shared-memory resident CTAs per SM
+                         int qbs, int max_dbs, cudaStream_t s, const LooseArgs* loose) {
+    if (grad_dtype == MAB_BF16 && loose == nullptr) {   // bf16 tiles are small enough for two shared-memory resident CTAs per SM
         const int rc = launch_ef_topk_quant_bf16(dev_tensors, n_tensors, total_units, qbs, max_dbs, s);
         if (rc <= 0) return rc;
     }
     const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count());
     int qshift = 0;
-    while ((1 << qshift) < qbs) ++qshift;
+    if (loose == nullptr) while ((1 << qshift) < qbs) ++qshift;
+    else qshift = 6;                                    // only sizes the (unused) statistics area of the staging buffer
+    LooseArgs la = {0, nullptr, nullptr, nullptr};
+    if (loose) la = *loose;
     // stage whole tiles when they fit beside the kernel's static shared memory, else load directly
     const int scratch = (int)(sizeof(SelectSmem) + sizeof(FastSelSmem));
-    const int limit = device_max_optin_smem() - 4 * 1024 - scratch;
+    const int limit = device_max_optin_smem() - 4 * 1024 - scratch - (loose ? 2 * LOOSE_MAX_QB * 4 : 0);
+    auto run = [&](auto kern, int stage_bytes_full) -> int {
+        const int stage_elems = stage_bytes_full > limit ? 0 : max_dbs;
+        const int smem = (stage_elems ? stage_bytes_full : 0) + scratch;
+        MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems, la);
+        return MAB_OK;
+    };
+    int rc;
     if (grad_dtype == MAB_F32) {
-        int stage_elems = max_dbs;
-        if (Stage<float>::bytes(stage_elems, qshift) > limit) stage_elems = 0;
-        const int smem = Stage<float>::bytes(stage_elems, qshift) + scratch;
-        auto kern = ef_topk_quant_kernel<float>;
-        MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems);
+        const int full = Stage<float>::bytes(max_dbs, qshift);
+        rc = loose ? run(ef_topk_quant_kernel<float, true>, full) : run(ef_topk_quant_kernel<float, false>, full);
     } else {
-        int stage_elems = max_dbs;
-        if (Stage<uint16_t>::bytes(stage_elems, qshift) > limit) stage_elems = 0;
-        const int smem = Stage<uint16_t>::bytes(stage_elems, qshift) + scratch;
-        auto kern = ef_topk_quant_kernel<uint16_t>;
-        MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        kern<<<grid, SEL_THREADS, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, stage_elems);
+        const int full = Stage<uint16_t>::bytes(max_dbs, qshift);
+        rc = loose ? run(ef_topk_quant_kernel<uint16_t, true>, full) : run(ef_topk_quant_kernel<uint16_t, false>, full);
     }
+    if (rc) return rc;
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_kernel launch");

@@ -76,7 +76,9 @@ SIGNATURES = {
     'mab_sparse_rows_dot': (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     'mab_sparse_rows_combine': (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     'mab_fused_step_workspace_bytes': (c_int64, [c_int]),
+    'mab_fused_step_workspace_bytes_for': (c_int64, [POINTER(MabTensor), c_int, POINTER(MabStepArgs)]),
     'mab_fused_supported': (c_int, [POINTER(MabTensor), POINTER(MabStepArgs)]),
+    'mab_fused_window_supported': (c_int, [POINTER(MabTensor), POINTER(MabStepArgs)]),
     'mab_fused_step': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),
     'mab_fused_ef_topk_quant': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),
     'mab_fused_window_adam_update': (c_int, [POINTER(MabTensor), c_int, POINTER(MabStepArgs), c_void_p, c_int64, c_void_p]),

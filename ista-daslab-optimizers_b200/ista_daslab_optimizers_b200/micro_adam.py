@@ -10,6 +10,11 @@ order of sub-steps.  Differences a caller can observe:
   (torch.topk(sorted=False) at micro_adam.py:193-200 leaves both unspecified);
 * on the fused path `p.grad` is left untouched (the reference uses it as scratch and leaves the
   update in it, micro_adam.py:276-313); on the operator-level path it is scratch as in the reference;
+* a `quant_block_size` that is not a power of two in [8, 128] (the reference's README uses 100000) makes
+  quantisation blocks ignore the borders of the top-k blocks (micro_adam.py:217-231).  With alpha == 0 and a
+  multiple of 8 >= 64 the step is then three kernels (selection + residual, statistics + codes, update) and
+  `p.grad` ends up holding the residual; other values take the operator-level kernels, with the update
+  itself still fused when alpha == 0;
 * alpha == -2 (micro_adam.py:238-273) keeps the residual in `quant_err` between the two fused kernels (gradient and
   parameter of one element type; other combinations take the operator-level path);
 * the logging probes (micro_adam.py:155-156, 306-308, 320-324, 330-350) run only when a `log_fn` is given: every
@@ -35,10 +40,11 @@ from .tools import CopyDirection, block_split, get_first_device
 
 class _Entry:
     """One flat slice of one parameter that this process updates."""
-    __slots__ = ('p', 'st', 'lo', 'hi', 'fused', 'group')
+    __slots__ = ('p', 'st', 'lo', 'hi', 'fused', 'window_fused', 'group')
 
     def __init__(self, p, st, lo, hi, group):
         self.p, self.st, self.lo, self.hi, self.fused, self.group = p, st, lo, hi, False, group
+        self.window_fused = False       # second half of the step (window -> update -> parameters) on the fused kernel
 
 
 class MicroAdam(torch.optim.Optimizer):
@@ -93,6 +99,7 @@ class MicroAdam(torch.optim.Optimizer):
         self._entries_key: Optional[tuple] = None
         self._descs = {}          # descriptor arrays of the fused step, one per group of entries
         self._workspace: Optional[torch.Tensor] = None
+        self._window_workspace: Optional[torch.Tensor] = None
         # set to a list to have every fused step append [start, between the two kernels, end] CUDA events
         self.kernel_events: Optional[list] = None
 
@@ -222,6 +229,9 @@ class MicroAdam(torch.optim.Optimizer):
         for e in self._entries:
             if not e.fused:
                 self._generic_update(e, probe)
+        late = [e for e in self._entries if not e.fused and e.window_fused]
+        if late:
+            self._fused_window_update(late, probe)
         self._after_update()
         self._probe_end(probe)
         if self.kernel_events and len(self.kernel_events[-1]) == 3:
@@ -323,6 +333,8 @@ class MicroAdam(torch.optim.Optimizer):
                 self._fill_static(d, e)
                 self._fill_dynamic(d, e)
                 e.fused = bool(N.load().mab_fused_supported(ctypes.byref(d), ctypes.byref(args)))
+                e.window_fused = (not e.fused and self.alpha == 0 and
+                                  bool(N.load().mab_fused_window_supported(ctypes.byref(d), ctypes.byref(args))))
 
     def _step_args(self) -> N.MabStepArgs:
         a = N.MabStepArgs()
@@ -368,10 +380,10 @@ class MicroAdam(torch.optim.Optimizer):
             self._fill_dynamic(d, e)
             e.st['index'] = (e.st['index'] + 1) % self.m                                               # micro_adam.py:211
         device = entries[0].p.device
-        need = lib.mab_fused_step_workspace_bytes(n)
+        args = self._step_args()
+        need = lib.mab_fused_step_workspace_bytes_for(descs, n, ctypes.byref(args))    # with scratch for loose quantisation blocks
         if self._workspace is None or self._workspace.numel() < need or self._workspace.device != device:
             self._workspace = torch.empty(need, dtype=torch.uint8, device=device)
-        args = self._step_args()
         if probe is not None:
             args.probe_out = probe['buf'].data_ptr()
         ws, ws_bytes = self._workspace.data_ptr(), self._workspace.numel()
@@ -391,9 +403,36 @@ class MicroAdam(torch.optim.Optimizer):
                 ev[2].record()
                 self.kernel_events.append(ev)
 
+    def _fused_window_update(self, entries: List[_Entry], probe: Optional[dict] = None):
+        """Second half of the step (micro_adam.py:234-235, 276-304 with alpha == 0) for entries whose first half ran
+        on the operator-level calls: weight decay, window -> Adam update, parameter update in one kernel over all of
+        them.  With alpha == 0 that kernel reads neither the gradient nor the error feedback, so quantisation blocks
+        that straddle top-k blocks do not matter to it; the update is not written to `p.grad`."""
+        lib = N.load()
+        n = len(entries)
+        descs = self._descs.get('window')
+        if descs is None or len(descs) != n:
+            descs = self._descs['window'] = (N.MabTensor * n)()
+            for d, e in zip(descs, entries):
+                self._fill_static(d, e)
+        for d, e in zip(descs, entries):
+            self._fill_dynamic(d, e)
+        device = entries[0].p.device
+        need = lib.mab_fused_step_workspace_bytes(n)
+        if self._window_workspace is None or self._window_workspace.numel() < need or self._window_workspace.device != device:
+            self._window_workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        args = self._step_args()
+        if probe is not None:
+            args.probe_out = probe['buf'].data_ptr()
+        with torch.cuda.device(device):
+            N.check(lib.mab_fused_window_adam_update(descs, n, ctypes.byref(args), self._window_workspace.data_ptr(),
+                                                     self._window_workspace.numel(), N.current_stream(device)),
+                    'mab_fused_window_adam_update')
+
     def _generic_update(self, e: _Entry, probe: Optional[dict] = None):
         """The reference's update_step (micro_adam.py:146-328) on the operator-level kernels; `probe` collects the
-        squared norms and the zero count the reference logs."""
+        squared norms and the zero count the reference logs.  For an entry marked `window_fused` it stops after the
+        error feedback has been requantised (micro_adam.py:231); `_fused_window_update` does the rest."""
         p, st = e.p, e.st
         group = self.param_groups[e.group]
         lr, wd = group['lr'], group.get('weight_decay', self.weight_decay)
@@ -413,6 +452,12 @@ class MicroAdam(torch.optim.Optimizer):
         N.zerorize_block_components(grad, I[index], d, k, dbs, k_many)                                 # :214
         N.quant_stats(d, qbs, min_vals, max_vals, grad)                                                # :217-228
         N.asymm_block_quant(d, qbs, error, min_vals, max_vals, grad)                                   # :231
+        if e.window_fused:
+            if probe is not None:                                                                      # :320-324
+                grad.zero_()
+                N.asymm_block_quant_inv(d, qbs, error, min_vals, max_vals, grad, 1.0)
+                probe['norm_e'] += float(grad.float().norm(p=2) ** 2)
+            return
         if wd > 0:
             pf.mul_(1 - lr * wd)                                                                       # :234-235
         if self.densify_update_using_quant_error:                                                      # :238-273, the form without lr

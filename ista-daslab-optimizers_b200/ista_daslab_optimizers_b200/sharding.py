@@ -305,11 +305,11 @@ class ShardedMicroAdam(MicroAdam):
             return
         lib = N.load()
         device = self._all_params[0].device
-        need = lib.mab_fused_step_workspace_bytes(n)
+        args = self._step_args()
+        need = lib.mab_fused_step_workspace_bytes_for(descs, n, ctypes.byref(args))
         ws = self._rows_ws.get(fn_name)
         if ws is None or ws.numel() < need:
             ws = self._rows_ws[fn_name] = torch.empty(need, dtype=torch.uint8, device=device)
-        args = self._step_args()
         if probe is not None:
             args.probe_out = probe['buf'].data_ptr()
         with torch.cuda.device(device):

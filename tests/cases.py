@@ -75,6 +75,14 @@ CASES: Dict[str, Case] = {c.name: c for c in [
     Case('bf16_alpha', [(4096,), (70000,)], torch.bfloat16, 6, alpha=0.25, weight_decay=0.1, grad_kind='student_t3_ties'),
     # quantisation blocks that straddle top-k blocks: only the operator-level kernels apply
     Case('qbs_100000', [(100001,), (300, 200)], torch.float32, 3, qbs=100000, alpha=0.5),
+    # the same without the alpha term: kernel A in two parts (residual + merged block extremes, then statistics + codes)
+    Case('qbs_100000_a0', [(100001,), (300, 200), (29056 * 3 + 8,), (29056 * 7 + 4097,)], torch.float32, 4, qbs=100000, weight_decay=0.1),
+    Case('qbs_100000_a0_bf16', [(100001,), (300, 200), (29056 * 4,)], torch.bfloat16, 4, qbs=100000, weight_decay=0.1, grad_sigma=1e-4),
+    # many loose quantisation blocks per top-k block (1000 and 72 elements), blocks that end mid-tile
+    Case('qbs_1000_a0', [(29056 * 2 + 1000,), (4096,), (70001,)], torch.float32, 4, qbs=1000, weight_decay=0.1),
+    Case('qbs_72_a0_bf16', [(29056 * 2 + 72 * 5,), (4100,)], torch.bfloat16, 4, qbs=72, grad_sigma=1e-4),
+    # not a multiple of 8: the operator-level first half, the update (window -> parameters) still fused
+    Case('qbs_100_a0', [(100001,), (300, 200)], torch.float32, 4, qbs=100, weight_decay=0.1),
     Case('qbs_32_m5', [(65536,), (1000,)], torch.float32, 7, qbs=32, m=5, k_init=0.05),
     # alpha == -2: the quantisation error is added to the parameters
     Case('alpha_m2', [(70000,), (4096,)], torch.float32, 4, alpha=-2, weight_decay=0.1),
