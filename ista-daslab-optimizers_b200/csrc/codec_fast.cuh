@@ -169,6 +169,48 @@ __device__ __forceinline__ uint32_t encode_octet(const float (&r)[8], const QPar
     return encode_octet_fast<CLAMP>(r, q, c);
 }
 
+// Codes of one octet by the defining form floor(RN(RN((r - mn) / u) + 0.5)) itself, two elements per
+// instruction and without division or conversion instructions; u in [2^-100, 2^100].  The IEEE quotient
+// comes from the correctly rounded reciprocal r0 = RN(1 / u): q = RN(d * r0) is within 1.5 ulp of d / u, one
+// residual correction q <- RN(q + RN(d - q * u) * r0) (the residual is exact in an FMA) makes it faithful,
+// and a second one makes it the correctly rounded quotient (Markstein's theorem on the final step of a
+// division).  Values far below half a step, where the residual could underflow, get code 0 from any
+// quotient below 0.5.  floor: adding 2^23 with rounding down leaves the integer in the low mantissa bits.
+// CLAMP: values may lie outside [mn, mn + 15 u] (statistics rounded to bf16): s is clamped to [0, 15.5]
+// before the floor, which gives the codes the defining clamp(floor(s), 0, 15) gives.
+struct DivConsts { float2 nmn2, r02, nu2; };
+
+__device__ __forceinline__ DivConsts div_consts(const QParams& q) {
+    DivConsts c;
+    const float r0 = __frcp_rn(q.u);
+    c.nmn2 = make_float2(-q.mn, -q.mn); c.r02 = make_float2(r0, r0); c.nu2 = make_float2(-q.u, -q.u);
+    return c;
+}
+
+template <bool CLAMP>
+__device__ __forceinline__ uint32_t encode_octet_div_f32(const float (&r)[8], const DivConsts& c) {
+    const float2 half2 = make_float2(0.5f, 0.5f), magic2 = make_float2(8388608.0f, 8388608.0f);
+    uint32_t y[8];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const float2 d = __fadd2_rn(make_float2(r[2 * p], r[2 * p + 1]), c.nmn2);   // r - mn
+        float2 q = __fmul2_rn(d, c.r02);
+        q = __ffma2_rn(__ffma2_rn(q, c.nu2, d), c.r02, q);
+        q = __ffma2_rn(__ffma2_rn(q, c.nu2, d), c.r02, q);                          // RN(d / u)
+        float2 s = __fadd2_rn(q, half2);
+        if (CLAMP) {
+            s.x = fminf(fmaxf(s.x, 0.0f), 15.5f);
+            s.y = fminf(fmaxf(s.y, 0.0f), 15.5f);
+        }
+        const float2 f = __fadd2_rd(s, magic2);                                     // 2^23 + floor(s)
+        y[2 * p] = __float_as_uint(f.x); y[2 * p + 1] = __float_as_uint(f.y);
+    }
+    // byte 0 of every float is the code; even elements go to the high nibbles
+    const uint32_t ev = __byte_perm(__byte_perm(y[0], y[2], 0x0040), __byte_perm(y[4], y[6], 0x0040), 0x5410);
+    const uint32_t od = __byte_perm(__byte_perm(y[1], y[3], 0x0040), __byte_perm(y[5], y[7], 0x0040), 0x5410);
+    return (ev << 4) | od;
+}
+
 // Two floats -> two bf16 (round to nearest even) in one conversion; low half = first value.
 __device__ __forceinline__ uint32_t pack_bf16x2_rne(float a, float b) {
     uint32_t d;

@@ -156,7 +156,6 @@ __device__ __forceinline__ void stage_issue(const TileRef<TG>& r, const Stage<TG
 // two scratch arrays, as order-preserving unsigned keys merged with atomicMin / atomicMax.  A second kernel
 // (requant_loose_kernel) then reads the residual once, rounds the merged statistics to bf16 and writes codes
 // and statistics.  Octets never straddle a quantisation block: quant_block_size is a multiple of 8.
-constexpr int LOOSE_MAX_QB = SEL_MAX_TILE / 64 + 2;   // quantisation blocks a tile can touch
 
 template <typename TG>
 __device__ __forceinline__ TileRef<TG> tile_ref_loose(const mab_tensor& T, int blk) {
@@ -358,6 +357,8 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
         uint16_t* mn_out = T.min_vals + (base >> qshift);
         uint16_t* mx_out = T.max_vals + (base >> qshift);
         const uint8_t* sel_bytes = reinterpret_cast<const uint8_t*>(sm.sel_bm);
+        int l_cur = -1;                                   // loose: the block whose extremes the thread is collecting
+        uint32_t l_lo = 0xFFFFFFFFu, l_hi = 0u;
 #pragma unroll
         for (int j = 0; j < SEL_OCTETS; ++j) {
             const int o = j * SEL_THREADS + (int)threadIdx.x;
@@ -394,15 +395,14 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
             if (LOOSE) {
                 // the residual goes back to the gradient buffer, its extremes to the tile's entries of the block statistics
                 if (cnt > 0) store_residual_octet<TG>(const_cast<TG*>(tr.g) + o * 8, a[j], aligned16(tr.g), cnt);
-                const int qi = cnt > 0 ? loose_block(lrem0 + o * 8, la.qbs, big_qb) : -1;
-                uint32_t klo = ord_key(lo), khi = ord_key(hi);          // an octet past the end holds (+inf, -inf): neutral
-                const int q_first = __shfl_sync(0xffffffffu, qi, 0), q_last = __shfl_sync(0xffffffffu, qi, 31);
-                if (q_first == q_last) {                                 // the warp's 32 octets lie in one block (or past the end)
-                    klo = __reduce_min_sync(0xffffffffu, klo);
-                    khi = __reduce_max_sync(0xffffffffu, khi);
-                    if (lane_id() == 0 && qi >= 0) { atomicMin(&s_qlo[qi], klo); atomicMax(&s_qhi[qi], khi); }
-                } else if (qi >= 0) {
-                    atomicMin(&s_qlo[qi], klo); atomicMax(&s_qhi[qi], khi);
+                if (cnt > 0) {
+                    const int qi = loose_block(lrem0 + o * 8, la.qbs, big_qb);
+                    if (qi != l_cur) {                                   // hand the collected extremes over when the block changes (blocks longer than a tile: at most once)
+                        if (l_cur >= 0) { atomicMin(&s_qlo[l_cur], l_lo); atomicMax(&s_qhi[l_cur], l_hi); }
+                        l_cur = qi; l_lo = 0xFFFFFFFFu; l_hi = 0u;
+                    }
+                    l_lo = min(l_lo, ord_key(lo));
+                    l_hi = max(l_hi, ord_key(hi));
                 }
                 continue;
             }
@@ -428,6 +428,16 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 }
             }
         }
+        if (LOOSE) {
+            const int c_first = __shfl_sync(0xffffffffu, l_cur, 0);
+            if (__all_sync(0xffffffffu, l_cur == c_first)) {             // the whole warp ended in one block (or holds nothing)
+                l_lo = __reduce_min_sync(0xffffffffu, l_lo);
+                l_hi = __reduce_max_sync(0xffffffffu, l_hi);
+                if (lane_id() == 0 && l_cur >= 0) { atomicMin(&s_qlo[l_cur], l_lo); atomicMax(&s_qhi[l_cur], l_hi); }
+            } else if (l_cur >= 0) {
+                atomicMin(&s_qlo[l_cur], l_lo); atomicMax(&s_qhi[l_cur], l_hi);
+            }
+        }
         MAB_TICK(14);
         __syncthreads();   // selection scratch is reused by the next unit
         if (LOOSE) {
@@ -447,8 +457,8 @@ int units_a_of(const mab_tensor& t) { return t.topk_full_blocks_count + (t.k_blo
 
 int launch_ef_topk_quant(const mab_tensor* dev_tensors, int n_tensors, int total_units, int grad_dtype,
                          int qbs, int max_dbs, cudaStream_t s, const LooseArgs* loose) {
-    if (grad_dtype == MAB_BF16 && loose == nullptr) {   // bf16 tiles are small enough for two shared-memory resident CTAs per SM
-        const int rc = launch_ef_topk_quant_bf16(dev_tensors, n_tensors, total_units, qbs, max_dbs, s);
+    if (grad_dtype == MAB_BF16) {          // bf16 tiles are small enough for two shared-memory resident CTAs per SM
+        const int rc = launch_ef_topk_quant_bf16(dev_tensors, n_tensors, total_units, qbs, max_dbs, s, loose);
         if (rc <= 0) return rc;
     }
     const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count());

@@ -223,10 +223,15 @@ __device__ __forceinline__ float dequant_octet(uint4* tile4, int o, int o_out, i
 // a = bf16(g + Qinv(e)) in place for the thread's octets t, t + S_NT, ...; per-octet maxima to omax.
 // The first FS octets of every thread are promised to exist, to be whole and to find their block in
 // the table, so their code is one branch-free block whose octets the compiler can interleave.
+// loose_qbs != 0: quantisation blocks of that many elements that ignore the tile's borders; the tile starts
+// lrem0 elements into the block mn_g / mx_g point at.
 template <int FS>
 __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, bool tables, const uint16_t* mn_g, const uint16_t* mx_g,
-                                              int cshift, int n, int n_oct, const uint32_t (&cw)[S_SLOTS], float (&omax)[S_SLOTS]) {
+                                              int cshift, int n, int n_oct, const uint32_t (&cw)[S_SLOTS], float (&omax)[S_SLOTS],
+                                              int loose_qbs = 0, int lrem0 = 0) {
     const int t = threadIdx.x;
+    const bool big = loose_qbs >= SEL_MAX_TILE;
+    auto block_of = [&](int o) { return loose_qbs ? loose_block(lrem0 + o * 8, loose_qbs, big) : (o >> cshift); };
     uint32_t slow = 0u;                                      // octets whose block needs the defining decode
 #pragma unroll
     for (int j = 0; j < S_SLOTS; ++j) {
@@ -234,7 +239,7 @@ __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, b
         const int o = t + j * S_NT;
         if (j < FS) {
             if (j % S_GROUP == 0) asm volatile("" ::: "memory");   // octets are interleaved within a group only (register pressure)
-            const float2 c = ss.qt.mu[o >> 3];
+            const float2 c = ss.qt.mu[block_of(o)];
             const QParams q = {c.x, c.y};
             const DecodeConsts dc = decode_consts(q);
             const float m = dequant_octet<true, false>(tile4, o, o, n, cw[j], q, dc, dc.fast);
@@ -242,8 +247,9 @@ __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, b
             slow |= dc.fast ? 0u : (1u << j);
         } else if (o < n_oct) {
             QParams q;
-            if (tables) { const float2 c = ss.qt.mu[o >> 3]; q.mn = c.x; q.u = c.y; }
-            else q = qparams(mn_g[o >> cshift], mx_g[o >> cshift]);
+            const int b = block_of(o);
+            if (tables) { const float2 c = ss.qt.mu[b]; q.mn = c.x; q.u = c.y; }
+            else q = qparams(mn_g[b], mx_g[b]);
             const DecodeConsts dc = decode_consts(q);
             if (!dc.fast) slow |= 1u << j;
             else omax[j] = dequant_octet<true, true>(tile4, o, o, n, cw[j], q, dc, true);
@@ -254,7 +260,8 @@ __device__ __forceinline__ void dequant_phase(uint4* tile4, const SmemSel& ss, b
         for (int j = 0; j < S_SLOTS; ++j) {
             if ((slow >> j) & 1u) {
                 const int o = t + j * S_NT;
-                const QParams q = qparams(mn_g[o >> cshift], mx_g[o >> cshift]);
+                const int b = block_of(o);
+                const QParams q = qparams(mn_g[b], mx_g[b]);
                 omax[j] = dequant_octet<false, true>(tile4, o, o, n, cw[j], q, decode_consts(q), true);
             }
         }
@@ -367,9 +374,13 @@ __device__ __forceinline__ void encode_phase(const uint4* tile4, const SmemSel& 
 
 // QB64: quant_block_size is 64: the per-block constants fit the shared-memory tables and the loops
 // over a block's 8 octets unroll.
-template <bool QB64>
+// LOOSE: quantisation blocks of la.qbs elements that ignore the borders of the top-k blocks; the kernel then ends
+// a tile with the residual written back to the gradient buffer and the extremes of every block it touches merged
+// into la.st_min / la.st_max (requant_loose.cu finishes the job), instead of statistics and codes.
+template <bool QB64, bool LOOSE>
 __global__ void __launch_bounds__(S_NT, S_CTAS)
-ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems) {
+ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int qshift, int stage_elems,
+                          LooseArgs la) {
     extern __shared__ __align__(128) unsigned char smem_raw[];       // [tile][SmemSel]
     __shared__ int s_first[S_MAX_TENSORS + 1];
     __shared__ __align__(8) uint64_t s_bar;
@@ -407,11 +418,14 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         const uint16_t* g = reinterpret_cast<const uint16_t*>(T.grad) + base;
         const uint8_t* ef_in = T.error + (base >> 1);
         uint8_t* ef_out = T.error + (base >> 1);
-        const int64_t qb0 = base >> qshift;
-        const int n_oct = (n + 7) >> 3, n_qb = (n + (1 << qshift) - 1) >> qshift;
+        const int64_t qb0 = LOOSE ? base / la.qbs : base >> qshift;
+        const int lrem0 = LOOSE ? (int)(base - qb0 * la.qbs) : 0;   // loose: where the tile starts inside its first block
+        // quantisation blocks of the tile; loose ones are at least 72 elements long, so the tables hold those a tile touches
+        const int n_oct = (n + 7) >> 3;
+        const int n_qb = LOOSE ? loose_block(lrem0 + n - 1, la.qbs, false) + 1 : (n + (1 << qshift) - 1) >> qshift;
         const bool staged = (n & 7) == 0 && aligned16(g);            // the bulk copy moves whole 16-byte pieces
         const bool ef_al4 = (reinterpret_cast<uintptr_t>(ef_in) & 3) == 0;
-        const bool tables = QB64 && n_qb <= S_QTAB;
+        const bool tables = (QB64 || LOOSE) && n_qb <= S_QTAB;
         const uint16_t* mn_g = T.min_vals + qb0;
         const uint16_t* mx_g = T.max_vals + qb0;
         const int64_t row_off = (int64_t)T.ring_index * row_pitch_of(T) + (int64_t)blk * T.k_block_size_many;
@@ -482,7 +496,7 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
             n_next = (int)nn;
             // gradients: 128-byte lines over all threads; codes and statistics: a warp each (they are 4 and 64 times smaller)
             prefetch_l2<S_NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(N.grad) + nbase), nn * 2);
-            if (warp < 3) {
+            if (warp < (LOOSE ? 1 : 3)) {
                 const uintptr_t pb = warp == 0 ? reinterpret_cast<uintptr_t>(N.error + (nbase >> 1))
                                    : reinterpret_cast<uintptr_t>((warp == 1 ? N.min_vals : N.max_vals) + (nbase >> qshift));
                 const int64_t bytes = warp == 0 ? (nn + 1) >> 1 : ((nn >> qshift) + 1) * 2;
@@ -495,9 +509,11 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // ---- a = bf16(g + Qinv(e)) in place; per-octet maxima stay in registers ------------------------
         float omax[S_SLOTS];
         // regular tile: whole blocks of 64, 14 whole octets per thread, aligned codes, every block with the fast decode
-        const bool swz = tables && (n & 63) == 0 && n_oct >= S_FULL * S_NT && ef_al4 && ss.ctrl[slow_slot] == 0 && T.quant_err == nullptr;
+        const bool swz = !LOOSE && tables && (n & 63) == 0 && n_oct >= S_FULL * S_NT && ef_al4 && ss.ctrl[slow_slot] == 0 && T.quant_err == nullptr;
         if (swz) dequant_phase_regular(tile4, ss, n_oct, cw, omax);
-        else dequant_phase<0>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax);
+        else if (LOOSE && tables && (n & 7) == 0 && n_oct >= S_FULL * S_NT && ef_al4)   // a full tile: branch-free first octets
+            dequant_phase<S_FULL>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax, la.qbs, lrem0);
+        else dequant_phase<0>(tile4, ss, tables, mn_g, mx_g, cshift, n, n_oct, cw, omax, LOOSE ? la.qbs : 0, lrem0);
 
         MAB_CTICK(1);
         // ---- exact top-k ---------------------------------------------------------------------------
@@ -763,7 +779,74 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
         // ---- statistics and codes of the residual ----------------------------------------------------------
         uint16_t* mn_out = T.min_vals + qb0;
         uint16_t* mx_out = T.max_vals + qb0;
-        if (swz) {
+        if (LOOSE) {
+            // the residual goes back to the gradient buffer, the extremes of every quantisation block the tile
+            // touches to the scratch arrays
+            uint16_t* g_w = const_cast<uint16_t*>(g);
+            uint32_t* s_qlo = ss.cand;                       // the candidate list is free again
+            uint32_t* s_qhi = ss.cand + LOOSE_MAX_QB;
+            static_assert(2 * LOOSE_MAX_QB <= S_CAND_CAP, "block extremes reuse the candidate list");
+            for (int i = t; i < LOOSE_MAX_QB; i += S_NT) { s_qlo[i] = 0xFFFFFFFFu; s_qhi[i] = 0u; }
+            __syncthreads();
+            if (!staged)
+                for (int i = t; i < n; i += S_NT) g_w[i] = tile[i];
+            MAB_CTICK(6);
+            const bool big = la.qbs >= SEL_MAX_TILE;
+            const int n_whole = n >> 3;                      // octets without padding
+            // a thread's octets are S_NT apart: it keeps the extremes of the block it is in and hands them over
+            // when the block changes (for blocks longer than a tile: at most once)
+            int cur = -1;
+            uint32_t alo = 0x7F807F80u, ahi = 0xFF80FF80u;   // packed bf16 pairs: running minimum from +inf, maximum from -inf
+#pragma unroll
+            for (int j = 0; j < S_SLOTS; ++j) {
+                const int o = t + j * S_NT;
+                if (o < n_whole) {
+                    const uint4 v = tile4[o];
+                    if (staged) reinterpret_cast<uint4*>(g_w)[o] = v;   // whole octets, 16-byte aligned: the residual goes home
+                    const int qi = loose_block(lrem0 + o * 8, la.qbs, big);
+                    if (qi != cur) {
+                        if (cur >= 0) {
+                            alo = min_bf16x2(alo, alo >> 16 | alo << 16); ahi = max_bf16x2(ahi, ahi >> 16 | ahi << 16);
+                            atomicMin(&s_qlo[cur], ord_key(__uint_as_float(alo << 16)));
+                            atomicMax(&s_qhi[cur], ord_key(__uint_as_float(ahi << 16)));
+                        }
+                        cur = qi; alo = 0x7F807F80u; ahi = 0xFF80FF80u;
+                    }
+                    ahi = max_bf16x2(max_bf16x2(ahi, v.x), max_bf16x2(max_bf16x2(v.y, v.z), v.w));
+                    alo = min_bf16x2(min_bf16x2(alo, v.x), min_bf16x2(min_bf16x2(v.y, v.z), v.w));
+                }
+            }
+            if (t == S_NT - 1 && n_whole < n_oct) {           // the tensor's last, short octet: element by element
+                const int qi = loose_block(lrem0 + n_whole * 8, la.qbs, big);
+                for (int e = n_whole * 8; e < n; ++e) {
+                    const uint32_t key = ord_key(__uint_as_float((uint32_t)tile[e] << 16));
+                    atomicMin(&s_qlo[qi], key); atomicMax(&s_qhi[qi], key);
+                }
+            }
+            {
+                alo = min_bf16x2(alo, alo >> 16 | alo << 16); ahi = max_bf16x2(ahi, ahi >> 16 | ahi << 16);
+                uint32_t klo = ord_key(__uint_as_float(alo << 16)), khi = ord_key(__uint_as_float(ahi << 16));
+                const int c_first = __shfl_sync(0xffffffffu, cur, 0);
+                if (__all_sync(0xffffffffu, cur == c_first)) {  // the whole warp ended in one block (or holds nothing)
+                    klo = __reduce_min_sync(0xffffffffu, klo);
+                    khi = __reduce_max_sync(0xffffffffu, khi);
+                    if (lane == 0 && cur >= 0) { atomicMin(&s_qlo[cur], klo); atomicMax(&s_qhi[cur], khi); }
+                } else if (cur >= 0) {
+                    atomicMin(&s_qlo[cur], klo); atomicMax(&s_qhi[cur], khi);
+                }
+            }
+            MAB_CTICK(7);
+            __syncthreads();
+            {
+                const int64_t at = la.qb_first[ti] + qb0;
+                for (int i = t; i < n_qb; i += S_NT) {
+                    atomicMin(la.st_min + at + i, s_qlo[i]);
+                    atomicMax(la.st_max + at + i, s_qhi[i]);
+                }
+            }
+            MAB_CTICK(9);
+            __syncthreads();                                 // the tile is overwritten by the next load
+        } else if (swz) {
             stats_encode_regular(tile4, n_qb, mn_out, mx_out, ef_out, (reinterpret_cast<uintptr_t>(ef_out) & 15) == 0);
             __syncthreads();                                 // the tile is overwritten by the next load
         } else if (tables && (n & 63) == 0) {
@@ -848,20 +931,24 @@ ef_topk_quant_bf16_kernel(const mab_tensor* __restrict__ tensors, int n_tensors,
     }
 }
 
-int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s) {
+int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s,
+                              const LooseArgs* loose) {
     int qshift = 0;
-    while ((1 << qshift) < qbs) ++qshift;
+    if (loose == nullptr) while ((1 << qshift) < qbs) ++qshift;
     const int smem = ((max_dbs * 2 + 127) & ~127) + (int)sizeof(SmemSel);
     const int per_sm = std::min(S_CTAS, (device_max_optin_smem() + 1024) / (smem + 3 * 1024 + 128));
     if (per_sm < 2) return 1;                                // not even two CTAs per SM: the caller uses the other kernel
     const int grid = (int)std::min<int64_t>(total_units, (int64_t)device_sm_count() * per_sm);
-    if (qshift == 6) {
-        MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        ef_topk_quant_bf16_kernel<true><<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
-    } else {
-        MAB_CUDA_TRY(cudaFuncSetAttribute(ef_topk_quant_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        ef_topk_quant_bf16_kernel<false><<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs);
-    }
+    LooseArgs la = {0, nullptr, nullptr, nullptr};
+    if (loose) la = *loose;
+    auto run = [&](auto kern) -> int {
+        MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        kern<<<grid, S_NT, smem, s>>>(dev_tensors, n_tensors, total_units, qshift, max_dbs, la);
+        return MAB_OK;
+    };
+    const int rc = loose ? run(ef_topk_quant_bf16_kernel<false, true>)
+                 : qshift == 6 ? run(ef_topk_quant_bf16_kernel<true, false>) : run(ef_topk_quant_bf16_kernel<false, false>);
+    if (rc) return rc;
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "ef_topk_quant_bf16_kernel launch");

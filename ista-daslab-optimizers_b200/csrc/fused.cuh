@@ -44,6 +44,8 @@ struct LooseArgs {
     const int64_t* qb_first;       // first scratch entry of every tensor of the call
 };
 
+constexpr int LOOSE_MAX_QB = 32768 / 64 + 2;        // quantisation blocks (>= 64 elements) a tile of at most 32768 elements can touch
+
 // Monotone map float -> uint32 (negative values below positive ones, -0 below +0) and back.
 __device__ __forceinline__ uint32_t ord_key(float f) {
     const uint32_t b = __float_as_uint(f);
@@ -69,7 +71,8 @@ int launch_requant_loose(const mab_tensor* dev_tensors, int n_tensors, int total
                          const LooseArgs& la, cudaStream_t s);
 
 // ef_topk_quant_bf16.cu: returns 1 (without launching) when two CTAs of its shared memory do not fit an SM
-int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s);
+int launch_ef_topk_quant_bf16(const mab_tensor* dev_tensors, int n_tensors, int total_units, int qbs, int max_dbs, cudaStream_t s,
+                              const LooseArgs* loose = nullptr);
 
 // Each kernel file keeps its own "a bounded wait gave up" flag (no relocatable device code): these read
 // it into *out and optionally clear it.

@@ -11,30 +11,21 @@ namespace mab {
 
 constexpr int RQ_THREADS = 256;
 
+// A whole octet of the residual, 16-byte aligned, as floats.
 template <typename TG> struct ResidualOctet;
 template <> struct ResidualOctet<float> {
-    __device__ __forceinline__ static void load(const float* p, float (&v)[8], bool vec, int cnt) {
-        if (vec && cnt >= 8) {
-            const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = (e < cnt) ? p[e] : 0.0f;
-        }
+    __device__ __forceinline__ static void load(const float* p, float (&v)[8]) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     }
 };
 template <> struct ResidualOctet<uint16_t> {
-    __device__ __forceinline__ static void load(const uint16_t* p, float (&v)[8], bool vec, int cnt) {
-        if (vec && cnt >= 8) {
-            const uint4 a = *reinterpret_cast<const uint4*>(p);
-            v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
-            v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
-            v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
-            v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = (e < cnt) ? bf16_bits_to_f32(p[e]) : 0.0f;
-        }
+    __device__ __forceinline__ static void load(const uint16_t* p, float (&v)[8]) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
     }
 };
 
@@ -63,8 +54,12 @@ requant_loose_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
         int cached = -1;                                 // the block whose constants the thread holds
         uint16_t mn_b = 0, mx_b = 0;
         QParams q = {0.0f, 0.0f};
-        for (int o = threadIdx.x; o * 8 < n; o += RQ_THREADS) {
-            const int cnt = n - o * 8;
+        DivConsts dc = {};
+        bool fast = false;                               // the block's step is in the range of the division-free encoder
+        // constants of the block an octet lies in (kept while consecutive octets stay in it); the octet that opens
+        // a block writes its statistics: a tile that starts inside a block leaves them to the tile that holds
+        // the block's first element
+        auto enter_block = [&](int o) {
             const int r = rem0 + o * 8;
             const int qi = loose_block(r, la.qbs, big);
             if (qi != cached) {
@@ -72,24 +67,52 @@ requant_loose_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 mn_b = f32_to_bf16_bits_rne(ord_value(__ldg(st_min + qi)));
                 mx_b = f32_to_bf16_bits_rne(ord_value(__ldg(st_max + qi)));
                 q = qparams(mn_b, mx_b);
+                fast = q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX;
+                dc = div_consts(q);
             }
-            // the octet that opens a block writes its statistics; a tile that starts inside a block leaves
-            // them to the tile that holds the block's first element
             if (r - qi * la.qbs == 0) { T.min_vals[qb0 + qi] = mn_b; T.max_vals[qb0 + qi] = mx_b; }
-            float a[8];
-            ResidualOctet<TG>::load(r_in + o * 8, a, vec_r, cnt);
-            if (cnt >= 8) {
-                const uint32_t w = encode_octet<true>(a, q);
-                if (vec_e) *reinterpret_cast<uint32_t*>(ef_out + o * 4) = w;
-                else {
+        };
+        const int n_whole = n >> 3;                      // octets without padding
+        if (vec_r && vec_e) {
+            constexpr int U = 4;                         // octets in flight per thread
+            for (int o0 = threadIdx.x; o0 < n_whole; o0 += U * RQ_THREADS) {
+                float a[U][8];
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) ef_out[o * 4 + b] = (uint8_t)(w >> (8 * b));
+                for (int i = 0; i < U; ++i) {
+                    const int o = o0 + i * RQ_THREADS;
+                    if (o < n_whole) ResidualOctet<TG>::load(r_in + o * 8, a[i]);
                 }
-            } else {
-                const uint32_t w = encode_octet_exact(a, q, cnt);
 #pragma unroll
-                for (int b = 0; b < 4; ++b) if (2 * b < cnt) ef_out[o * 4 + b] = (uint8_t)(w >> (8 * b));
+                for (int i = 0; i < U; ++i) {
+                    const int o = o0 + i * RQ_THREADS;
+                    if (o < n_whole) {
+                        enter_block(o);
+                        // fp32 residuals can lie outside the bf16-rounded statistics (clamp); bf16 ones cannot
+                        reinterpret_cast<uint32_t*>(ef_out)[o] = fast ? encode_octet_div_f32<sizeof(TG) == 4>(a[i], dc)
+                                                                      : encode_octet_exact(a[i], q, 8);
+                    }
+                }
             }
+        } else {
+            for (int o = threadIdx.x; o < n_whole; o += RQ_THREADS) {
+                float a[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = Elem<TG>::load(r_in, o * 8 + e);
+                enter_block(o);
+                const uint32_t w = fast ? encode_octet_div_f32<sizeof(TG) == 4>(a, dc) : encode_octet_exact(a, q, 8);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) ef_out[o * 4 + b] = (uint8_t)(w >> (8 * b));
+            }
+        }
+        if ((n & 7) != 0 && threadIdx.x == RQ_THREADS - 1) {     // the tensor's last, short octet
+            const int o = n_whole, cnt = n & 7;
+            float a[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = (e < cnt) ? Elem<TG>::load(r_in, o * 8 + e) : 0.0f;
+            enter_block(o);
+            const uint32_t w = encode_octet_exact(a, q, cnt);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) if (2 * b < cnt) ef_out[o * 4 + b] = (uint8_t)(w >> (8 * b));
         }
     }
 }
