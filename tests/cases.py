@@ -94,6 +94,9 @@ CASES: Dict[str, Case] = {c.name: c for c in [
     Case('wide_bf16_wd', [(29056 * 2 + 640,), (4096,)], torch.bfloat16, 14, m=20, k_init=0.05, weight_decay=0.1, grad_sigma=1e-4),
     Case('wide_fp32_alpha', [(29056 + 64 * 9,), (300, 200)], torch.float32, 14, m=20, k_init=0.05, alpha=0.5, weight_decay=0.1,
          grad_kind='student_t3_ties'),
+    # k larger than the number of 8-element groups of a block: the selection cannot start from group maxima
+    Case('dense_topk_fp32', [(4096,), (29056 + 64,)], torch.float32, 3, k_init=0.2, m=3),
+    Case('dense_topk_bf16', [(4096,), (29056 + 64,)], torch.bfloat16, 3, k_init=0.2, m=3, grad_sigma=1e-4),
     # few rows of few entries (m = 5, 0.5 % of a block)
     Case('narrow_m5', [(29056 * 3 + 8,), (1000,)], torch.float32, 7, m=5, k_init=0.005, weight_decay=0.1),
     Case('narrow_m5_bf16', [(29056 * 3 + 8,), (1000,)], torch.bfloat16, 7, m=5, k_init=0.005, weight_decay=0.1, grad_sigma=1e-4),

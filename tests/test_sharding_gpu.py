@@ -12,7 +12,7 @@ def bits(t):
 
 
 @pytest.mark.parametrize('world', [2, 3])
-@pytest.mark.parametrize('name', ['bf16_wd', 'mixed_fp32_alpha'])
+@pytest.mark.parametrize('name', ['bf16_wd', 'mixed_fp32_alpha', 'qbs_100000_a0'])
 def test_sharded_equals_unsharded(name, world):
     from ista_daslab_optimizers_b200.sharding import ShardedMicroAdam
     case = cases.CASES[name]
@@ -96,7 +96,7 @@ def assert_rows_ranks_equal_unsharded(case, full, ranks, t):
 
 
 @pytest.mark.parametrize('world', [1, 2, 3])
-@pytest.mark.parametrize('name', ['bf16_wd', 'c1_fp32_1m'])
+@pytest.mark.parametrize('name', ['bf16_wd', 'c1_fp32_1m', 'qbs_100000_a0_bf16'])
 def test_row_exchange_equals_unsharded(name, world):
     """exchange='rows': kernel A sharded, window rows exchanged (copied by hand between the emulated
     ranks here), kernel B on every rank over all parameters: every rank ends with the unsharded result."""
