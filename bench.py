@@ -10,10 +10,13 @@ same model is sharded over the N GPUs (strong scaling); by default (`--exchange 
 feedback and the top-k selection are sharded, the ranks all-gather the window row the step produced
 and every rank applies the update to all parameters; `--exchange params` shards both kernels ZeRO-1
 style and all-gathers the updated parameters instead.  Rank 0 prints one JSON line.  At N = 1 the line
-also carries a `configs.gpt2_flat` record (the fp32 single-GPU configuration), at N > 1 a
+also carries a `configs.gpt2_flat` record (the fp32 single-GPU configuration) and a
+`configs.llama3_8b_quant_block_100000` record (the list with the reference README's quant_block_size), at N > 1 a
 `params_mode` record (the same model with the parameter all-gather) and the time of the gradient
 reduce-scatter of the shard plan; `param_checksum` is a checksum of all parameters that is equal for
-every N exactly when the N-GPU run is bit-identical to the 1-GPU run.
+every N exactly when the N-GPU run is bit-identical to the 1-GPU run.  `e2e` is the same step with its
+gradients coming from pinned host memory (the copy of the next step's gradients overlaps the current step,
+both inside the timed region) and a checksum of all parameters read back every step.
 
 `--workload sweep` times one fp32 flat tensor over the grid d x k_init x m x quant_block_size and
 prints per-kernel and per-step GB/s for every point.
@@ -404,18 +407,52 @@ def run_workload(spec, args, world, rank, local_rank, exchange, steps, warmup, e
         chunked = True
     set_grads(0)
     h2d_bytes = (my_hi - my_lo) * gflat.element_size()
-    barrier()
-    t0 = time.perf_counter()
-    checksum = None
-    for t in range(e2e_steps):
+    # The copy of step t + 1's gradients runs on its own stream while step t computes (two device buffers, the
+    # second gradient set's storage): every step's copy lies inside the timed region, the first one exposed.
+    pipelined = len(grad_sets) >= 2
+    copy_stream = torch.cuda.Stream(device=device) if pipelined else None
+    compute = torch.cuda.current_stream(device)
+
+    def copy_in(dst):
         if not chunked:
-            gflat[my_lo:my_hi].copy_(host, non_blocking=True)
+            dst[my_lo:my_hi].copy_(host, non_blocking=True)
         else:
             for o in range(my_lo, my_hi, host.numel()):
                 n = min(host.numel(), my_hi - o)
-                gflat[o:o + n].copy_(host[:n], non_blocking=True)
-        opt.step()
-        checksum = whole_buffer_checksum(flat_p)                       # 8-byte device-to-host read, synchronises
+                dst[o:o + n].copy_(host[:n], non_blocking=True)
+
+    def copy_in_async(dst, after):
+        """Enqueues the copy on the copy stream once `after` (the last step that read `dst`) has passed."""
+        with torch.cuda.stream(copy_stream):
+            if after is not None:
+                copy_stream.wait_event(after)
+            copy_in(dst)
+            ev = torch.cuda.Event()
+            ev.record(copy_stream)
+        return ev
+
+    barrier()
+    t0 = time.perf_counter()
+    checksum = None
+    if pipelined:
+        read_done = [None, None]                       # per buffer: the event after the last step that read it
+        ready = copy_in_async(grad_sets[0][0], None)
+        for t in range(e2e_steps):
+            cur = t % 2
+            compute.wait_event(ready)
+            set_grads(cur)
+            if t + 1 < e2e_steps:
+                ready = copy_in_async(grad_sets[1 - cur][0], read_done[1 - cur])
+            opt.step()
+            read_done[cur] = torch.cuda.Event()
+            read_done[cur].record(compute)
+            checksum = whole_buffer_checksum(flat_p)                   # 8-byte device-to-host read, synchronises
+        set_grads(0)
+    else:
+        for t in range(e2e_steps):
+            copy_in(gflat)
+            opt.step()
+            checksum = whole_buffer_checksum(flat_p)                   # 8-byte device-to-host read, synchronises
     barrier()
     e2e_s = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
     for _ in range(plain_tail_steps):
@@ -517,7 +554,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--workload', default='llama3_8b', help='llama3_8b | gpt2_flat | flat_<bf16|f32>_<numel> | sweep')
     ap.add_argument('--grad-sets', type=int, default=2, help='distinct pre-generated gradient sets cycled over the steps')
-    ap.add_argument('--e2e-steps', type=int, default=3)
+    ap.add_argument('--e2e-steps', type=int, default=5)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-extra', action='store_true',
                     help='only the headline workload: no GPT-2-flat sub-record (N = 1), no parameter-exchange sub-record (N > 1)')
@@ -600,7 +637,8 @@ def main():
         'kernels': kernels,
         'step_hbm': step_hbm,
         'e2e': {'value': r['e2e_value'], 'unit': UNIT, 'h2d_bytes_per_step': r['h2d_bytes'], 'd2h_bytes_per_step': 8,
-                'steps': e2e_steps},
+                'steps': e2e_steps,
+                'copies': 'step t + 1 copied from pinned host memory on a second stream while step t computes; all inside the timed region'},
         # wrapping 64-bit sum of all parameter bit patterns after `optimizer_steps` steps: identical on every rank
         # (checked) and for every N exactly when the N-GPU parameters equal the 1-GPU ones bit for bit
         'param_checksum': {'value': r['checksum'], 'optimizer_steps': r['optimizer_steps']},
