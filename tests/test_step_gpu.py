@@ -192,8 +192,9 @@ def test_logging_probes_report_the_reference_quantities(name):
         assert torch.equal(plain.param(i), probed.param(i))
 
 
+@pytest.mark.parametrize('qbs', [64, 1000], ids=['qbs64', 'qbs1000'])
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
-def test_flat_shards_cut_at_arbitrary_elements(dtype):
+def test_flat_shards_cut_at_arbitrary_elements(dtype, qbs):
     """FSDP-style use (micro_adam.py:158-160 sizes the state lazily so that it fits whatever shard a rank holds): the
     parameters handed to the optimizer are slices [lo, hi) of one flat buffer, cut at arbitrary elements, so their
     storage starts at odd offsets (2-byte alignment only for bf16) and top-k blocks are counted from the shard's
@@ -204,7 +205,7 @@ def test_flat_shards_cut_at_arbitrary_elements(dtype):
     cuts = [0, 1, 29056 + 3, 2 * 29056 + 1001, total]                 # shards of 1, 29058, 30054 and 40464 elements
     gen = torch.Generator().manual_seed(11)
     flat = (torch.randn(total, generator=gen) * 0.02).to(dtype)
-    hyper = dict(m=10, lr=1e-3, quant_block_size=64, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0.1, eps=1e-8)
+    hyper = dict(m=10, lr=1e-3, quant_block_size=qbs, k_init=0.01, alpha=0, betas=(0.9, 0.999), weight_decay=0.1, eps=1e-8)
     flat_gpu = flat.cuda()
     grad_gpu = torch.zeros_like(flat_gpu)
     shards = [torch.nn.Parameter(flat_gpu[a:b]) for a, b in zip(cuts, cuts[1:])]
@@ -225,9 +226,10 @@ def test_flat_shards_cut_at_arbitrary_elements(dtype):
             assert torch.equal(a['I'][row].cpu(), b['I'][row]), (t, i)
             assert torch.equal(a['V'][row].cpu().view(torch.int16), b['V'][row].view(torch.int16)), (t, i)
             assert torch.equal(a['error'].cpu(), b['error']), (t, i)
-            used = (p.numel() + 63) // 64
+            used = (p.numel() + qbs - 1) // qbs
             assert torch.equal(a['min_vals'][:used].cpu().view(torch.int16), b['min_vals'][:used].view(torch.int16)), (t, i)
             torch.testing.assert_close(p.detach().cpu().float(), cpu_shards[i].float(), rtol=rtol, atol=atol)
+    assert all(e.fused for e in opt._entries)
     assert _native.device_error() == 0
 
 
