@@ -11,6 +11,9 @@
 
 namespace mab {
 
+constexpr int SPR_SR = 7296;          // elements of a block one CTA accumulates at a time (57 * 128)
+constexpr int SPR_THREADS = 512;
+
 constexpr int SP_THREADS = 1024;
 
 template <typename T> __device__ __forceinline__ float load_value(const void* p, int64_t i);
@@ -46,31 +49,31 @@ sparse_rows_dot_kernel(int64_t k, int64_t dbs, int64_t kbs, const TG* __restrict
 // with a dense fp32 accumulator in shared memory; rows are added in row order (positions are unique inside a
 // row, so a row needs no atomics).
 template <typename TO, typename TV>
-__global__ void __launch_bounds__(WIN_THREADS)
+__global__ void __launch_bounds__(SPR_THREADS)
 sparse_rows_combine_kernel(int64_t d, int rows, int64_t k, int dbs, int kbs, int nfull, int k_few, const float* __restrict__ M,
                            const int16_t* __restrict__ I, const void* __restrict__ V, TO* __restrict__ out, int total_units) {
-    __shared__ float acc[WIN_SR];
-    const int subs_per_block = (dbs + WIN_SR - 1) / WIN_SR;
+    __shared__ float acc[SPR_SR];
+    const int subs_per_block = (dbs + SPR_SR - 1) / SPR_SR;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         int blk = unit / subs_per_block, sub = unit - blk * subs_per_block;
         if (blk > nfull) { sub += (blk - nfull) * subs_per_block; blk = nfull; }
         const int64_t blk_base = (int64_t)blk * dbs;
         const int n_blk = (int)min((int64_t)dbs, d - blk_base);
         const int kcnt = (blk < nfull) ? kbs : k_few;
-        const int s0 = sub * WIN_SR;
-        const int len = min(WIN_SR, n_blk - s0);
-        for (int i = threadIdx.x; i < len; i += WIN_THREADS) acc[i] = 0.0f;
+        const int s0 = sub * SPR_SR;
+        const int len = min(SPR_SR, n_blk - s0);
+        for (int i = threadIdx.x; i < len; i += SPR_THREADS) acc[i] = 0.0f;
         __syncthreads();
         for (int r = 0; r < rows; ++r) {
             const int64_t row0 = (int64_t)r * k + (int64_t)blk * kbs;
             const float coef = M[r];
-            for (int j = threadIdx.x; j < kcnt; j += WIN_THREADS) {
+            for (int j = threadIdx.x; j < kcnt; j += SPR_THREADS) {
                 const int pos = (int)I[row0 + j] - s0;
                 if (pos >= 0 && pos < len) acc[pos] = __fadd_rn(acc[pos], __fmul_rn(coef, load_value<TV>(V, row0 + j)));
             }
             __syncthreads();
         }
-        for (int i = threadIdx.x; i < len; i += WIN_THREADS) {
+        for (int i = threadIdx.x; i < len; i += SPR_THREADS) {
             const int64_t e = blk_base + s0 + i;
             Elem<TO>::store(out, e, __fadd_rn(Elem<TO>::load(out, e), acc[i]));
         }
@@ -130,13 +133,13 @@ extern "C" int mab_sparse_rows_combine(int64_t d, int64_t rows, int64_t k, int64
                 "sparse_rows_combine: dtypes %d, %d", out_dtype, v_dtype);
     if (device_sm_count() < 0) return MAB_ERR_CUDA;
     const int dbs = (int)d_block_size;
-    const int subs = (dbs + WIN_SR - 1) / WIN_SR;
+    const int subs = (dbs + SPR_SR - 1) / SPR_SR;
     const int64_t tail = d - (int64_t)nfull * dbs;
-    const int64_t units = (int64_t)nfull * subs + (tail > 0 ? (tail + WIN_SR - 1) / WIN_SR : 0);
+    const int64_t units = (int64_t)nfull * subs + (tail > 0 ? (tail + SPR_SR - 1) / SPR_SR : 0);
     if (units == 0) return MAB_OK;
     const int grid = (int)std::min<int64_t>(units, (int64_t)device_sm_count() * 4);
     cudaStream_t s = (cudaStream_t)stream;
-#define MAB_LAUNCH_COMBINE(TO, TV) sparse_rows_combine_kernel<TO, TV><<<grid, WIN_THREADS, 0, s>>>( \
+#define MAB_LAUNCH_COMBINE(TO, TV) sparse_rows_combine_kernel<TO, TV><<<grid, SPR_THREADS, 0, s>>>( \
         d, (int)rows, k, dbs, (int)k_block_size, nfull, k_few, M, I, V, (TO*)out, (int)units)
     if (out_dtype == MAB_F32 && v_dtype == MAB_BF16) MAB_LAUNCH_COMBINE(float, uint16_t);
     else if (out_dtype == MAB_F32) MAB_LAUNCH_COMBINE(float, float);

@@ -4,24 +4,22 @@
 // every sub-range starts on a quantisation-block boundary for quant_block_size <= 128).  For one
 // sub-range the CTA
 //   1. zeroes two float accumulators (first and second moment) of WIN_SR elements,
-//   2. loads the window entries of the block (rows r < rows, the block's slice of I / V),
-//      keeps those whose position falls in the sub-range in "slots",
-//   3. adds them row after row with a barrier between rows (positions are unique inside a
-//      row, so a row needs no atomics, and the fixed row order makes the float sums
-//      reproducible bit for bit on any grid and any GPU count),
-//   4. turns (m, v) into the update u at the touched positions only (the expensive divide and
-//      square root run on ~10 % of the elements), leaving u = 0 elsewhere in the first array.
+//   2. walks the window entries of the block (rows r < rows, the block's slice of I / V) row after row with a
+//      barrier between rows and adds those whose position falls in the sub-range (positions are unique inside
+//      a row, so a row needs no atomics, and the fixed row order makes the float sums reproducible bit for
+//      bit on any grid and any GPU count),
+//   3. turns (m, v) into the update u wherever the second moment is non-zero (one pass over the
+//      accumulators instead of a second pass over the entries), leaving u = 0 elsewhere in the first array.
 // The caller then streams over the sub-range reading u from shared memory.
 #pragma once
 #include "common.cuh"
 
 namespace mab {
 
-constexpr int WIN_SR = 7296;          // 57 * 128 elements per sub-range
-constexpr int WIN_THREADS = 512;
-constexpr int WIN_SLOTS = 3072;       // window entries examined per batch
-constexpr int WIN_SLOTS_PER_THREAD = WIN_SLOTS / WIN_THREADS;
-constexpr int WIN_SMEM_BYTES = 2 * WIN_SR * 4 + WIN_SLOTS * 4;
+constexpr int WIN_SR = 7296;          // 57 * 128 elements per sub-range: a 29 056-element block is four sub-ranges
+constexpr int WIN_THREADS = 512;      // two CTAs per SM
+constexpr int WIN_EPT = 4;            // window entries of a row a thread holds in registers
+constexpr int WIN_SMEM_BYTES = 2 * WIN_SR * 4;
 constexpr int WIN_MAX_TENSORS = 512;  // tensors per launch (their unit prefix sits in shared memory)
 
 struct WindowArgs {
@@ -39,10 +37,8 @@ struct WindowArgs {
 struct WindowSmem {
     float*    m_acc;                  // after finalize: u
     float*    v_acc;
-    uint32_t* slots;                  // (bf16 value bits << 16) | (local position), or 0xFFFFFFFF
     __device__ explicit WindowSmem(unsigned char* base)
-        : m_acc(reinterpret_cast<float*>(base)), v_acc(m_acc + WIN_SR),
-          slots(reinterpret_cast<uint32_t*>(v_acc + WIN_SR)) {}
+        : m_acc(reinterpret_cast<float*>(base)), v_acc(m_acc + WIN_SR) {}
 };
 
 __device__ __forceinline__ float adam_update_value(float m, float v, const WindowArgs& a) {
@@ -58,73 +54,54 @@ __device__ __forceinline__ void window_to_update(const int16_t* __restrict__ I_b
                                                  const WindowArgs& a, WindowSmem& sm) {
     const int t = threadIdx.x;
     for (int i = t; i < WIN_SR; i += WIN_THREADS) { sm.m_acc[i] = 0.0f; sm.v_acc[i] = 0.0f; }
-    const int64_t total = (int64_t)a.rows * kcnt;            // flattened (row, j) entries
-    const int nbatch = (int)((total + WIN_SLOTS - 1) / WIN_SLOTS);
-
-    for (int pass = 0; pass < 2; ++pass) {                   // 0: accumulate, 1: finalize
-        for (int bi = 0; bi < nbatch; ++bi) {
-            const int64_t q0 = (int64_t)bi * WIN_SLOTS;
-            const int nq = (int)min((int64_t)WIN_SLOTS, total - q0);
-            if (pass == 0 || nbatch > 1) {
-                __syncthreads();                             // slots free (and, first time, zeroing done)
+    __syncthreads();
+    // row after row, straight from global memory; a thread's first WIN_EPT entries of the next row are fetched
+    // before the work on the current one (one exposed load latency per row at most)
+    int n_pos[WIN_EPT];
+    uint32_t n_val[WIN_EPT];
 #pragma unroll
-                for (int s = 0; s < WIN_SLOTS_PER_THREAD; ++s) {
-                    const int q = s * WIN_THREADS + t;
-                    uint32_t slot = 0xFFFFFFFFu;
-                    if (q < nq) {
-                        const int64_t g = q0 + q;
-                        const int r = (int)(g / kcnt), j = (int)(g - (int64_t)r * kcnt);
-                        const int pos = (int)I_blk[(int64_t)r * row_pitch + j] - s0;
-                        if (pos >= 0 && pos < len)
-                            slot = ((uint32_t)V_blk[(int64_t)r * row_pitch + j] << 16) | (uint32_t)pos;
-                    }
-                    sm.slots[q] = slot;
-                }
-                __syncthreads();
-            }
-            if (pass == 0) {
-                const int r_lo = (int)(q0 / kcnt), r_hi = (int)((q0 + nq - 1) / kcnt);
-                for (int r = r_lo; r <= r_hi; ++r) {
-                    const int lo = (int)max((int64_t)r * kcnt - q0, (int64_t)0);
-                    const int hi = (int)min((int64_t)(r + 1) * kcnt - q0, (int64_t)nq);
-                    const float w1 = a.w1[r], w2 = a.w2[r];
-                    for (int q = lo + t; q < hi; q += WIN_THREADS) {
-                        const uint32_t slot = sm.slots[q];
-                        if (slot != 0xFFFFFFFFu) {
-                            const int pos = slot & 0xFFFF;
-                            const float val = __uint_as_float(slot & 0xFFFF0000u);
-                            sm.m_acc[pos] = __fadd_rn(sm.m_acc[pos], __fmul_rn(val, w1));
-                            sm.v_acc[pos] = __fadd_rn(sm.v_acc[pos], __fmul_rn(__fmul_rn(val, val), w2));
-                        }
-                    }
-                    __syncthreads();
-                }
-            } else {
-                float u[WIN_SLOTS_PER_THREAD];
+    for (int e = 0; e < WIN_EPT; ++e) {
+        const int j = t + e * WIN_THREADS;
+        n_pos[e] = (j < kcnt) ? (int)I_blk[j] : -1;
+        n_val[e] = (j < kcnt) ? (uint32_t)V_blk[j] : 0u;
+    }
+    for (int r = 0; r < a.rows; ++r) {
+        const int16_t* I_r = I_blk + (int64_t)r * row_pitch;
+        const uint16_t* V_r = V_blk + (int64_t)r * row_pitch;
+        const float w1 = a.w1[r], w2 = a.w2[r];
+        int pos[WIN_EPT];
+        uint32_t vb[WIN_EPT];
 #pragma unroll
-                for (int s = 0; s < WIN_SLOTS_PER_THREAD; ++s) {
-                    const int q = s * WIN_THREADS + t;
-                    u[s] = 0.0f;
-                    const uint32_t slot = (q < nq) ? sm.slots[q] : 0xFFFFFFFFu;
-                    if (slot != 0xFFFFFFFFu) {
-                        const int pos = slot & 0xFFFF;
-                        const float v = sm.v_acc[pos];
-                        u[s] = (v < 0.0f) ? sm.m_acc[pos] : adam_update_value(sm.m_acc[pos], v, a);
-                    }
-                }
-                __syncthreads();
+        for (int e = 0; e < WIN_EPT; ++e) { pos[e] = n_pos[e] - s0; vb[e] = n_val[e]; }
+        if (r + 1 < a.rows) {
 #pragma unroll
-                for (int s = 0; s < WIN_SLOTS_PER_THREAD; ++s) {
-                    const int q = s * WIN_THREADS + t;
-                    const uint32_t slot = (q < nq) ? sm.slots[q] : 0xFFFFFFFFu;
-                    if (slot != 0xFFFFFFFFu) {
-                        const int pos = slot & 0xFFFF;
-                        sm.m_acc[pos] = u[s];       // duplicates of a position write the same value
-                        sm.v_acc[pos] = -1.0f;      // marks "already an update" for later batches
-                    }
-                }
+            for (int e = 0; e < WIN_EPT; ++e) {
+                const int j = t + e * WIN_THREADS;
+                if (j < kcnt) { n_pos[e] = (int)I_r[row_pitch + j]; n_val[e] = (uint32_t)V_r[row_pitch + j]; }
             }
         }
+#pragma unroll
+        for (int e = 0; e < WIN_EPT; ++e) {
+            if (t + e * WIN_THREADS < kcnt && pos[e] >= 0 && pos[e] < len) {
+                const float val = __uint_as_float(vb[e] << 16);
+                sm.m_acc[pos[e]] = __fadd_rn(sm.m_acc[pos[e]], __fmul_rn(val, w1));
+                sm.v_acc[pos[e]] = __fadd_rn(sm.v_acc[pos[e]], __fmul_rn(__fmul_rn(val, val), w2));
+            }
+        }
+        for (int j = t + WIN_EPT * WIN_THREADS; j < kcnt; j += WIN_THREADS) {   // rows longer than WIN_EPT entries per thread
+            const int p = (int)I_r[j] - s0;
+            if (p >= 0 && p < len) {
+                const float val = __uint_as_float((uint32_t)V_r[j] << 16);
+                sm.m_acc[p] = __fadd_rn(sm.m_acc[p], __fmul_rn(val, w1));
+                sm.v_acc[p] = __fadd_rn(sm.v_acc[p], __fmul_rn(__fmul_rn(val, val), w2));
+            }
+        }
+        __syncthreads();
+    }
+    // a position nothing was added to, or only zeros, has v == 0 and m == 0, and its update 0 / (0 + eps) is 0 as well
+    for (int i = t; i < len; i += WIN_THREADS) {
+        const float v = sm.v_acc[i];
+        if (v != 0.0f) sm.m_acc[i] = adam_update_value(sm.m_acc[i], v, a);
     }
     __syncthreads();
 }

@@ -356,7 +356,6 @@ __device__ __forceinline__ void stream_range(const mab_tensor& T, const WindowAr
 
 // ------------------------------------------------------------------------------------ tile kernel
 
-constexpr int WT_THREADS = 256;
 constexpr int WT_WORDS = 1024;            // bitmap words (32768 positions)
 constexpr int WT_MAX_ENTRIES = 16384;     // window entries of one block the compact arrays may hold
 constexpr int WT_KEEP = 6;                // window entries a thread keeps in registers between marking and numbering
@@ -572,7 +571,7 @@ __device__ __forceinline__ int window_tile_moments(const mab_tensor& T, int blk,
     return touched;
 }
 
-template <typename TP, int MODE, int ALPHA>
+template <typename TP, int MODE, int ALPHA, int NT>
 __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units,
                                                  int max_k, const WindowArgs& a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -583,7 +582,7 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     const WindowTileSmem w(smem_raw, rows, max_k);
     const int t = threadIdx.x;
 
-    for (int i = t; i < n_tensors; i += WT_THREADS) s_first[i] = tensors[i].first_unit_a;
+    for (int i = t; i < n_tensors; i += NT) s_first[i] = tensors[i].first_unit_a;
     if (t == 0) s_first[n_tensors] = total_units;
     __syncthreads();
     const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
@@ -606,16 +605,16 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
                 prefetch_window_rows(tensors[nti], nu - s_first[nti], rows, threadIdx.x);
             }
             // this block's parameters travel to L2 while the window is worked on
-            prefetch_l2<WT_THREADS>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
+            prefetch_l2<NT>(reinterpret_cast<uintptr_t>(reinterpret_cast<TP*>(T.param) + blk_base), (int64_t)n_blk * sizeof(TP));
         }
         const int kcnt = (blk < nfull) ? T.k_block_size_many : T.k_block_size_few;
         const bool g_bf16 = (T.grad_dtype == MAB_BF16);
 
         MAB_BTICK_DECL
-        const int touched = window_tile_moments<WT_THREADS>(T, blk, n_blk, kcnt, a, w, s_scan, s_pos_off, s_val_off);
+        const int touched = window_tile_moments<NT>(T, blk, n_blk, kcnt, a, w, s_scan, s_pos_off, s_val_off);
         MAB_BTICK(9);
         // 5. moments -> update (rounded to the gradient's element type), slot by slot
-        for (int s = t; s < touched; s += WT_THREADS) {
+        for (int s = t; s < touched; s += NT) {
             const float2 acc = w.mv[s];
             const float u = round_as(adam_update_fast(acc.x, acc.y, inv_bc1, inv_bc2, a.eps), g_bf16);
             w.mv[s].x = u;
@@ -629,20 +628,20 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
             //    weight decay alone (nothing to stream without decay), then update the touched elements
             //    one by one; fma(-lr, 0, x) == x, so the untouched elements are already final
             if (T.weight_decay > 0.0) {
-                stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, NoU{}, blk_base, n_blk, pr);
+                stream_range<TP, MODE, NT, ALPHA>(T, a, NoU{}, blk_base, n_blk, pr);
                 __syncthreads();                               // the decayed values are read back below
             }
             MAB_BTICK(6);
             TP* p = reinterpret_cast<TP*>(T.param) + blk_base;
             const float neg_lr = T.neg_lr_f32;
-            for (int s2 = t; s2 < touched; s2 += WT_THREADS) {
+            for (int s2 = t; s2 < touched; s2 += NT) {
                 const int pos = w.spos[s2];
                 Elem<TP>::store(p, pos, __fmaf_rn(neg_lr, w.mv[s2].x, Elem<TP>::load(p, pos)));
             }
         } else {
             // 6. stream the whole block; each octet finds its updates through the bitmap
             const SparseU src{w.bitmap, w.prefix, w.mv};
-            stream_range<TP, MODE, WT_THREADS, ALPHA>(T, a, src, blk_base, n_blk, pr);
+            stream_range<TP, MODE, NT, ALPHA>(T, a, src, blk_base, n_blk, pr);
         }
         MAB_BTICK(7);
         __syncthreads();                                       // everything is reused by the next unit
@@ -654,19 +653,21 @@ __device__ __forceinline__ void window_tile_body(const mab_tensor* __restrict__ 
     if (probing) pr.flush(a.probe);
 }
 
-template <typename TP, int MODE, int ALPHA>
-__global__ void __launch_bounds__(WT_THREADS, ALPHA == 0 ? 4 : 1)
+// NT threads per CTA: 256 while four CTAs fit an SM; windows whose arrays leave room for two CTAs or one get 512 or
+// 1024 threads instead, so that an SM always has 32 warps to hide the latency of the barrier-separated phases.
+template <typename TP, int MODE, int ALPHA, int NT>
+__global__ void __launch_bounds__(NT, ALPHA == 0 ? 1024 / NT : 1)
 window_tile_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, int max_k,
                    const __grid_constant__ WindowArgs a) {
-    window_tile_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, max_k, a);
+    window_tile_body<TP, MODE, ALPHA, NT>(tensors, n_tensors, total_units, max_k, a);
 }
 
 // Single tensor whose descriptor travels as a kernel argument (operator-level entry point).
-template <typename TP, int MODE, int ALPHA>
-__global__ void __launch_bounds__(WT_THREADS)
+template <typename TP, int MODE, int ALPHA, int NT>
+__global__ void __launch_bounds__(NT)
 window_tile_single_kernel(const __grid_constant__ mab_tensor t, int total_units, int max_k,
                           const __grid_constant__ WindowArgs a) {
-    window_tile_body<TP, MODE, ALPHA>(&t, 1, total_units, max_k, a);
+    window_tile_body<TP, MODE, ALPHA, NT>(&t, 1, total_units, max_k, a);
 }
 
 // ------------------------------------------------------------------------------------ resident-tile kernel
@@ -850,7 +851,7 @@ __device__ __forceinline__ void window_wide_body(const mab_tensor* __restrict__ 
 }
 
 template <typename TP, int MODE, int ALPHA>
-__global__ void __launch_bounds__(WIN_THREADS)
+__global__ void __launch_bounds__(WIN_THREADS, 2)
 window_wide_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, const __grid_constant__ WindowArgs a) {
     window_wide_body<TP, MODE, ALPHA>(tensors, n_tensors, total_units, a);
 }
@@ -876,15 +877,27 @@ static int launch_window_impl(const mab_tensor* dev_tensors, const mab_tensor* s
         const int smem = smem_tile;
         const int per_sm = std::max(1, std::min(8, (227 * 1024) / (smem + 3072)));
         const int grid = (int)std::min<int64_t>(units_tile, (int64_t)sms * per_sm);
-        if (single) {
-            auto kern = window_tile_single_kernel<TP, MODE, ALPHA>;
-            MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            kern<<<grid, WT_THREADS, smem, s>>>(*single, units_tile, max_k, a);
+        // fewer resident CTAs (large windows) get more threads each; the forms with the alpha term keep 256
+        const int nt = (ALPHA != 0 || per_sm >= 4) ? 256 : per_sm >= 2 ? 512 : 1024;
+        auto run = [&](auto kern_single, auto kern_multi, int threads) -> int {
+            if (single) {
+                MAB_CUDA_TRY(cudaFuncSetAttribute(kern_single, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+                kern_single<<<grid, threads, smem, s>>>(*single, units_tile, max_k, a);
+            } else {
+                MAB_CUDA_TRY(cudaFuncSetAttribute(kern_multi, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+                kern_multi<<<grid, threads, smem, s>>>(dev_tensors, n_tensors, units_tile, max_k, a);
+            }
+            return MAB_OK;
+        };
+        int rc;
+        if constexpr (ALPHA == 0) {
+            if (nt == 1024) rc = run(window_tile_single_kernel<TP, MODE, 0, 1024>, window_tile_kernel<TP, MODE, 0, 1024>, 1024);
+            else if (nt == 512) rc = run(window_tile_single_kernel<TP, MODE, 0, 512>, window_tile_kernel<TP, MODE, 0, 512>, 512);
+            else rc = run(window_tile_single_kernel<TP, MODE, 0, 256>, window_tile_kernel<TP, MODE, 0, 256>, 256);
         } else {
-            auto kern = window_tile_kernel<TP, MODE, ALPHA>;
-            MAB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-            kern<<<grid, WT_THREADS, smem, s>>>(dev_tensors, n_tensors, units_tile, max_k, a);
+            rc = run(window_tile_single_kernel<TP, MODE, ALPHA, 256>, window_tile_kernel<TP, MODE, ALPHA, 256>, 256);
         }
+        if (rc) return rc;
     } else {
         const int grid = (int)std::min<int64_t>(units_wide, (int64_t)sms * 2);
         if (single) {
