@@ -41,10 +41,12 @@ struct WindowSmem {
         : m_acc(reinterpret_cast<float*>(base)), v_acc(m_acc + WIN_SR) {}
 };
 
-__device__ __forceinline__ float adam_update_value(float m, float v, const WindowArgs& a) {
-    const float m_hat = __fdiv_rn(m, a.bc1);
-    const float v_hat = __fdiv_rn(v, a.bc2);
-    return __fdiv_rn(m_hat, __fadd_rn(__fsqrt_rn(v_hat), a.eps));
+// Fast (not correctly rounded) form of m_hat / (sqrt(v_hat) + eps): the update is specified to
+// a tolerance, and the approximations are deterministic.
+__device__ __forceinline__ float adam_update_fast(float m, float v, float inv_bc1, float inv_bc2, float eps) {
+    float s;
+    asm("sqrt.approx.f32 %0, %1;" : "=f"(s) : "f"(v * inv_bc2));
+    return __fdividef(m * inv_bc1, s + eps);
 }
 
 // I_blk / V_blk point at the block's slice of row 0; row_pitch = k; kcnt entries per row;
@@ -99,9 +101,10 @@ __device__ __forceinline__ void window_to_update(const int16_t* __restrict__ I_b
         __syncthreads();
     }
     // a position nothing was added to, or only zeros, has v == 0 and m == 0, and its update 0 / (0 + eps) is 0 as well
+    const float inv_bc1 = 1.0f / a.bc1, inv_bc2 = 1.0f / a.bc2;
     for (int i = t; i < len; i += WIN_THREADS) {
         const float v = sm.v_acc[i];
-        if (v != 0.0f) sm.m_acc[i] = adam_update_value(sm.m_acc[i], v, a);
+        if (v != 0.0f) sm.m_acc[i] = adam_update_fast(sm.m_acc[i], v, inv_bc1, inv_bc2, a.eps);
     }
     __syncthreads();
 }

@@ -370,14 +370,6 @@ __host__ __device__ constexpr int wt_smem_bytes(int rows, int max_k) {
     return 8 * e + rows * 2 * wt_row_stride(max_k) + 4 * WT_WORDS + 2 * WT_WORDS + 2 * e;
 }
 
-// Fast (not correctly rounded) form of m_hat / (sqrt(v_hat) + eps): the update is specified to
-// a tolerance, and the approximations are deterministic.
-__device__ __forceinline__ float adam_update_fast(float m, float v, float inv_bc1, float inv_bc2, float eps) {
-    float s;
-    asm("sqrt.approx.f32 %0, %1;" : "=f"(s) : "f"(v * inv_bc2));
-    return __fdividef(m * inv_bc1, s + eps);
-}
-
 // Asks L2 for one unit's slices of the valid window rows: one thread per row slice of I or V.
 // `who` = index of the calling thread among those that ask (the first 2 * rows of them do).
 __device__ __forceinline__ void prefetch_window_rows(const mab_tensor& T, int blk, int rows, int who) {
