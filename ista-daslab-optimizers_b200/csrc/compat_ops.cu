@@ -3,6 +3,8 @@
 // geometries faster; these are the general path and the operator-level drop-in surface.
 #include "common.cuh"
 #include "select.cuh"
+#include "select_fast.cuh"
+#include "codec_fast.cuh"
 
 namespace mab {
 
@@ -57,6 +59,108 @@ quant_kernel(int64_t d, int64_t qbs, uint8_t* __restrict__ error, const uint16_t
             if (e + 1 < n) w.next();
         }
         if (n & 1) error[(i0 + n - 1) >> 1] = (uint8_t)byte;   // odd d: low nibble of the last byte is 0
+    }
+}
+
+// ---- octet-wide forms of the three codec operators ----------------------------------------------------------
+//
+// One thread per 8 consecutive elements, consecutive lanes on consecutive octets, vector loads and stores.
+// Conditions (checked by the callers): d and qbs multiples of 8 (an octet lies in one quantisation block and
+// no octet is short), x 16-byte aligned, error 4-byte aligned.  Same arithmetic as the element-wise kernels
+// above, so the two forms give the same bits.
+
+template <typename T> struct XOctet;
+template <> struct XOctet<float> {
+    __device__ __forceinline__ static void load(const float* p, float (&v)[8]) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    __device__ __forceinline__ static void store(float* p, const float (&v)[8]) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+template <> struct XOctet<uint16_t> {
+    __device__ __forceinline__ static void load(const uint16_t* p, float (&v)[8]) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p);
+        v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
+    }
+    __device__ __forceinline__ static void store(uint16_t* p, const float (&v)[8]) {
+        uint4 w;
+        w.x = pack_bf16x2_rne(v[0], v[1]); w.y = pack_bf16x2_rne(v[2], v[3]);
+        w.z = pack_bf16x2_rne(v[4], v[5]); w.w = pack_bf16x2_rne(v[6], v[7]);
+        *reinterpret_cast<uint4*>(p) = w;
+    }
+};
+
+// Quantisation block of octet o: a shift when qbs is a power of two (qshift >= 0), else a division.
+__device__ __forceinline__ int64_t octet_block(int64_t o, int64_t qbs, int qshift) {
+    return qshift >= 0 ? (o << 3) >> qshift : (o << 3) / qbs;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+quant_inv_octet_kernel(int64_t n_oct, int64_t qbs, int qshift, const uint8_t* __restrict__ error, const uint16_t* __restrict__ mn,
+                       const uint16_t* __restrict__ mx, T* __restrict__ x, float alpha) {
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < n_oct; o += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = octet_block(o, qbs, qshift);
+        const QParams q = qparams(mn[b], mx[b]);
+        float v[8], r[8];
+        XOctet<T>::load(x + o * 8, v);
+        decode_octet(reinterpret_cast<const uint32_t*>(error)[o], q, r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __fadd_rn(v[e], __fmul_rn(alpha, r[e]));
+        XOctet<T>::store(x + o * 8, v);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+quant_octet_kernel(int64_t n_oct, int64_t qbs, int qshift, uint8_t* __restrict__ error, const uint16_t* __restrict__ mn,
+                   const uint16_t* __restrict__ mx, const T* __restrict__ x) {
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < n_oct; o += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = octet_block(o, qbs, qshift);
+        const QParams q = qparams(mn[b], mx[b]);
+        float v[8];
+        XOctet<T>::load(x + o * 8, v);
+        // the division-free form needs a step in range and quotients that stay far from overflow (the caller's values
+        // need not lie between the statistics); everything else takes the defining form
+        bool fast = q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX;
+        const DivConsts dc = div_consts(q);
+        if (fast) {
+            float big = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) big = fmaxf(big, fabsf(__fmul_rn(__fsub_rn(v[e], q.mn), dc.r02.x)));
+            fast = big < 64.0f;                      // false for NaN as well
+        }
+        reinterpret_cast<uint32_t*>(error)[o] = fast ? encode_octet_div_f32<true>(v, dc) : encode_octet_exact(v, q, 8);
+    }
+}
+
+// Power-of-two qbs in [8, 256]: the qbs / 8 lanes of a block combine their octets' extremes by shuffles.
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS)
+quant_stats_octet_kernel(int64_t n_oct, int qshift, uint16_t* __restrict__ mn, uint16_t* __restrict__ mx, const T* __restrict__ x) {
+    const int lanes = 1 << (qshift - 3);
+    const int64_t n_pad = (n_oct + 31) & ~(int64_t)31;           // whole warps take part in the shuffles
+    for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < n_pad; o += (int64_t)gridDim.x * blockDim.x) {
+        float lo = INFINITY, hi = -INFINITY;
+        if (o < n_oct) {
+            float v[8];
+            XOctet<T>::load(x + o * 8, v);
+            octet_min_max(v, lo, hi);
+        }
+        for (int off = 1; off < lanes; off <<= 1) {
+            lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+            hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+        }
+        if (o < n_oct && (o & (lanes - 1)) == 0) {
+            const int64_t b = (o << 3) >> qshift;
+            mn[b] = f32_to_bf16_bits_rne(lo); mx[b] = f32_to_bf16_bits_rne(hi);
+        }
     }
 }
 
@@ -115,29 +219,44 @@ quant_stats_kernel(int64_t d, int64_t qbs, int64_t nblocks, uint16_t* __restrict
     }
 }
 
-// One CTA per top-k block: keys to registers, exact k-th key by bisection, ordered emission.
+// One CTA per top-k block: keys to registers, exact k-th key (through the candidates of select_fast.cuh, by
+// bisection where that does not apply), ordered emission.
 template <typename T>
 __global__ void __launch_bounds__(SEL_THREADS, 1)
 block_topk_kernel(int64_t d, int dbs, int nfull, int k_many, int k_few, const T* __restrict__ x,
                   int16_t* __restrict__ out) {
-    __shared__ SelectSmem sm;
+    extern __shared__ __align__(16) unsigned char topk_raw[];            // [SelectSmem | FastSelSmem]
+    SelectSmem& sm = *reinterpret_cast<SelectSmem*>(topk_raw);
+    FastSelSmem& fs = *reinterpret_cast<FastSelSmem*>(topk_raw + sizeof(SelectSmem));
     const int nblocks = nfull + (k_few > 0 ? 1 : 0);
+    int guess = 0;
     for (int blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
         const int64_t base = (int64_t)blk * dbs;
         const int n = (int)min((int64_t)dbs, d - base);
         const int k = (blk < nfull) ? k_many : k_few;
-        float key[SEL_OCTETS][8];
+        const bool vec = (reinterpret_cast<uintptr_t>(x + base) & 15) == 0;
+        float key[SEL_OCTETS][8], omax[SEL_OCTETS];
 #pragma unroll
-        for (int j = 0; j < SEL_OCTETS; ++j)
+        for (int j = 0; j < SEL_OCTETS; ++j) {
+            const int o = j * SEL_THREADS + (int)threadIdx.x;
+            if (vec && o * 8 + 8 <= n) {
+                XOctet<T>::load(x + base + o * 8, key[j]);
+            } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int i = (j * SEL_THREADS + (int)threadIdx.x) * 8 + e;
-                key[j][e] = (i < n) ? Elem<T>::load(x, base + i) : 0.0f;
+                for (int e = 0; e < 8; ++e) key[j][e] = (o * 8 + e < n) ? Elem<T>::load(x, base + o * 8 + e) : 0.0f;
             }
-        int need;
-        const int T_key = block_kth_key_bisect(key, k, sm, need);
-        publish_masks(key, T_key, sm);
-        resolve_selection(need, sm);
+            omax[j] = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) omax[j] = fmaxf(omax[j], fabsf(key[j][e]));
+        }
+        int n_cand, oct_slot[SEL_OCTETS];
+        bool compact_octets;
+        if (!fast_select(key, omax, n, k, guess, sm, fs, n_cand, oct_slot, compact_octets, sizeof(T) == 2 ? 16 : 0)) {
+            int need;
+            const int T_key = block_kth_key_bisect(key, k, sm, need);
+            publish_masks(key, T_key, sm);
+            resolve_selection(need, sm);
+        }
         emit_indices(sm, out + (int64_t)blk * k_many);
         __syncthreads();
     }
@@ -156,6 +275,19 @@ using namespace mab;
 #define MAB_CHECK_LAUNCH(name)                                                     \
     do { mab::count_launch(); cudaError_t _e = cudaGetLastError(); if (_e != cudaSuccess) return cuda_fail(_e, name); } while (0)
 
+// log2 of a power of two, else -1.
+static int shift_of(int64_t v) {
+    if (v <= 0 || (v & (v - 1)) != 0) return -1;
+    int sh = 0;
+    while (((int64_t)1 << sh) < v) ++sh;
+    return sh;
+}
+
+// Whether the octet-wide kernels apply: whole octets inside one quantisation block each, vector-aligned buffers.
+static bool octet_form_ok(int64_t d, int64_t qbs, const void* x, const void* error) {
+    return d % 8 == 0 && qbs % 8 == 0 && aligned_to(x, 16) && aligned_to(error, 4);
+}
+
 static int check_dtype(int dt, const char* what) {
     MAB_REQUIRE(dt == MAB_F32 || dt == MAB_BF16, MAB_ERR_UNSUPPORTED, "%s: dtype code %d is neither MAB_F32 nor MAB_BF16", what, dt);
     return MAB_OK;
@@ -168,10 +300,16 @@ extern "C" int mab_asymm_block_quant_inv(int64_t d, int64_t qbs, const uint8_t* 
     MAB_REQUIRE(error && mn && mx && x, MAB_ERR_BAD_ARG, "asymm_block_quant_inv: null pointer");
     if (int rc = check_dtype(x_dtype, "asymm_block_quant_inv")) return rc;
     if (device_sm_count() < 0) return MAB_ERR_CUDA;
-    const int grid = grid_for(ceil_div64(d, EW_CHUNK), EW_THREADS);
     cudaStream_t s = (cudaStream_t)stream;
-    if (x_dtype == MAB_F32) quant_inv_kernel<float><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (float*)x, alpha);
-    else quant_inv_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (uint16_t*)x, alpha);
+    if (octet_form_ok(d, qbs, x, error)) {
+        const int grid = grid_for(d / 8, EW_THREADS);
+        if (x_dtype == MAB_F32) quant_inv_octet_kernel<float><<<grid, EW_THREADS, 0, s>>>(d / 8, qbs, shift_of(qbs), error, mn, mx, (float*)x, alpha);
+        else quant_inv_octet_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d / 8, qbs, shift_of(qbs), error, mn, mx, (uint16_t*)x, alpha);
+    } else {
+        const int grid = grid_for(ceil_div64(d, EW_CHUNK), EW_THREADS);
+        if (x_dtype == MAB_F32) quant_inv_kernel<float><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (float*)x, alpha);
+        else quant_inv_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (uint16_t*)x, alpha);
+    }
     MAB_CHECK_LAUNCH("asymm_block_quant_inv");
     return MAB_OK;
 }
@@ -183,10 +321,16 @@ extern "C" int mab_asymm_block_quant(int64_t d, int64_t qbs, uint8_t* error, con
     MAB_REQUIRE(error && mn && mx && x, MAB_ERR_BAD_ARG, "asymm_block_quant: null pointer");
     if (int rc = check_dtype(x_dtype, "asymm_block_quant")) return rc;
     if (device_sm_count() < 0) return MAB_ERR_CUDA;
-    const int grid = grid_for(ceil_div64(d, EW_CHUNK), EW_THREADS);
     cudaStream_t s = (cudaStream_t)stream;
-    if (x_dtype == MAB_F32) quant_kernel<float><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (const float*)x);
-    else quant_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (const uint16_t*)x);
+    if (octet_form_ok(d, qbs, x, error)) {
+        const int grid = grid_for(d / 8, EW_THREADS);
+        if (x_dtype == MAB_F32) quant_octet_kernel<float><<<grid, EW_THREADS, 0, s>>>(d / 8, qbs, shift_of(qbs), error, mn, mx, (const float*)x);
+        else quant_octet_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d / 8, qbs, shift_of(qbs), error, mn, mx, (const uint16_t*)x);
+    } else {
+        const int grid = grid_for(ceil_div64(d, EW_CHUNK), EW_THREADS);
+        if (x_dtype == MAB_F32) quant_kernel<float><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (const float*)x);
+        else quant_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d, qbs, error, mn, mx, (const uint16_t*)x);
+    }
     MAB_CHECK_LAUNCH("asymm_block_quant");
     return MAB_OK;
 }
@@ -236,7 +380,11 @@ extern "C" int mab_quant_stats(int64_t d, int64_t qbs, uint16_t* mn, uint16_t* m
     const int64_t nblocks = ceil_div64(d, qbs);
     cudaStream_t s = (cudaStream_t)stream;
     const int64_t cap = (int64_t)device_sm_count() * 16;
-    if (qbs >= 2048) {
+    if (d % 8 == 0 && shift_of(qbs) >= 3 && qbs <= 256 && aligned_to(x, 16)) {
+        const int grid = grid_for(d / 8, EW_THREADS);
+        if (x_dtype == MAB_F32) quant_stats_octet_kernel<float><<<grid, EW_THREADS, 0, s>>>(d / 8, shift_of(qbs), mn, mx, (const float*)x);
+        else quant_stats_octet_kernel<uint16_t><<<grid, EW_THREADS, 0, s>>>(d / 8, shift_of(qbs), mn, mx, (const uint16_t*)x);
+    } else if (qbs >= 2048) {
         const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(nblocks, cap));
         if (x_dtype == MAB_F32) quant_stats_kernel<float, true><<<grid, EW_THREADS, 0, s>>>(d, qbs, nblocks, mn, mx, (const float*)x);
         else quant_stats_kernel<uint16_t, true><<<grid, EW_THREADS, 0, s>>>(d, qbs, nblocks, mn, mx, (const uint16_t*)x);
@@ -267,8 +415,14 @@ extern "C" int mab_block_topk(int64_t d, int64_t dbs, int64_t k_many, int64_t k_
     if (nblocks == 0) return MAB_OK;
     const int grid = (int)std::min<int64_t>(nblocks, (int64_t)device_sm_count() * 4);
     cudaStream_t s = (cudaStream_t)stream;
-    if (x_dtype == MAB_F32) block_topk_kernel<float><<<grid, SEL_THREADS, 0, s>>>(d, (int)dbs, (int)nfull, (int)k_many, (int)k_few, (const float*)x, out);
-    else block_topk_kernel<uint16_t><<<grid, SEL_THREADS, 0, s>>>(d, (int)dbs, (int)nfull, (int)k_many, (int)k_few, (const uint16_t*)x, out);
+    const int smem = (int)(sizeof(SelectSmem) + sizeof(FastSelSmem));
+    if (x_dtype == MAB_F32) {
+        MAB_CUDA_TRY(cudaFuncSetAttribute(block_topk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        block_topk_kernel<float><<<grid, SEL_THREADS, smem, s>>>(d, (int)dbs, (int)nfull, (int)k_many, (int)k_few, (const float*)x, out);
+    } else {
+        MAB_CUDA_TRY(cudaFuncSetAttribute(block_topk_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        block_topk_kernel<uint16_t><<<grid, SEL_THREADS, smem, s>>>(d, (int)dbs, (int)nfull, (int)k_many, (int)k_few, (const uint16_t*)x, out);
+    }
     MAB_CHECK_LAUNCH("block_topk");
     return MAB_OK;
 }

@@ -24,7 +24,7 @@ namespace mab {
 #ifdef MAB_STATS
 // Development-only tile statistics (compiled in with -DMAB_STATS): [0] fast tiles, [1..6] tiles sent
 // to the slow path by reason, [7] lower-bound probes, [8] candidates, [9] histogram levels.
-__device__ unsigned long long g_stats[32];
+static __device__ unsigned long long g_stats[32];
 #define MAB_STAT(i, v) do { if (threadIdx.x == 0) atomicAdd(&g_stats[i], (unsigned long long)(v)); } while (0)
 // phase timer: adds the cycles since the previous mark to slot i (thread 0's clock)
 #define MAB_TICK(i) do { if (threadIdx.x == 0) { const long long _now = clock64(); atomicAdd(&g_stats[i], (unsigned long long)(_now - g_tick)); g_tick = _now; } } while (0)
