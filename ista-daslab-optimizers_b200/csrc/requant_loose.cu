@@ -11,26 +11,37 @@ namespace mab {
 
 constexpr int RQ_THREADS = 256;
 
-// A whole octet of the residual, 16-byte aligned, as floats.
+// A whole octet of the residual, 16-byte aligned: loaded as raw words (so that several octets in flight cost few
+// registers), turned into floats when it is worked on.
 template <typename TG> struct ResidualOctet;
 template <> struct ResidualOctet<float> {
-    __device__ __forceinline__ static void load(const float* p, float (&v)[8]) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    struct Raw { float4 lo, hi; };
+    __device__ __forceinline__ static Raw load(const float* p) {
+        Raw r;
+        r.lo = __ldg(reinterpret_cast<const float4*>(p)); r.hi = __ldg(reinterpret_cast<const float4*>(p) + 1);
+        return r;
+    }
+    __device__ __forceinline__ static void unpack(const Raw& r, float (&v)[8]) {
+        v[0] = r.lo.x; v[1] = r.lo.y; v[2] = r.lo.z; v[3] = r.lo.w; v[4] = r.hi.x; v[5] = r.hi.y; v[6] = r.hi.z; v[7] = r.hi.w;
     }
 };
 template <> struct ResidualOctet<uint16_t> {
-    __device__ __forceinline__ static void load(const uint16_t* p, float (&v)[8]) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
-        v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xFFFF0000u);
-        v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xFFFF0000u);
-        v[4] = __uint_as_float(a.z << 16); v[5] = __uint_as_float(a.z & 0xFFFF0000u);
-        v[6] = __uint_as_float(a.w << 16); v[7] = __uint_as_float(a.w & 0xFFFF0000u);
+    struct Raw { uint4 w; };
+    __device__ __forceinline__ static Raw load(const uint16_t* p) {
+        Raw r;
+        r.w = __ldg(reinterpret_cast<const uint4*>(p));
+        return r;
+    }
+    __device__ __forceinline__ static void unpack(const Raw& r, float (&v)[8]) {
+        v[0] = __uint_as_float(r.w.x << 16); v[1] = __uint_as_float(r.w.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(r.w.y << 16); v[3] = __uint_as_float(r.w.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(r.w.z << 16); v[5] = __uint_as_float(r.w.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(r.w.w << 16); v[7] = __uint_as_float(r.w.w & 0xFFFF0000u);
     }
 };
 
 template <typename TG>
-__global__ void __launch_bounds__(RQ_THREADS)
+__global__ void __launch_bounds__(RQ_THREADS, 4)
 requant_loose_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int total_units, LooseArgs la) {
     __shared__ int s_first[WIN_MAX_TENSORS + 1];
     for (int i = threadIdx.x; i < n_tensors; i += RQ_THREADS) s_first[i] = tensors[i].first_unit_a;
@@ -76,20 +87,22 @@ requant_loose_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
         if (vec_r && vec_e) {
             constexpr int U = 4;                         // octets in flight per thread
             for (int o0 = threadIdx.x; o0 < n_whole; o0 += U * RQ_THREADS) {
-                float a[U][8];
+                typename ResidualOctet<TG>::Raw raw[U];
 #pragma unroll
                 for (int i = 0; i < U; ++i) {
                     const int o = o0 + i * RQ_THREADS;
-                    if (o < n_whole) ResidualOctet<TG>::load(r_in + o * 8, a[i]);
+                    if (o < n_whole) raw[i] = ResidualOctet<TG>::load(r_in + o * 8);
                 }
 #pragma unroll
                 for (int i = 0; i < U; ++i) {
                     const int o = o0 + i * RQ_THREADS;
                     if (o < n_whole) {
                         enter_block(o);
+                        float a[8];
+                        ResidualOctet<TG>::unpack(raw[i], a);
                         // fp32 residuals can lie outside the bf16-rounded statistics (clamp); bf16 ones cannot
-                        reinterpret_cast<uint32_t*>(ef_out)[o] = fast ? encode_octet_div_f32<sizeof(TG) == 4>(a[i], dc)
-                                                                      : encode_octet_exact(a[i], q, 8);
+                        reinterpret_cast<uint32_t*>(ef_out)[o] = fast ? encode_octet_div_f32<sizeof(TG) == 4>(a, dc)
+                                                                      : encode_octet_exact(a, q, 8);
                     }
                 }
             }
