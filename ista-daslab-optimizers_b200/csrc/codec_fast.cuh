@@ -91,7 +91,7 @@ struct EncodeConsts { float2 nmn2, r02; bool fast; };
 __device__ __forceinline__ EncodeConsts encode_consts(const QParams& q) {
     EncodeConsts c;
     c.fast = q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX;
-    const float r0 = __frcp_rn(q.u);
+    const float r0 = c.fast ? rcp_rn_normal(q.u) : 0.0f;
     c.nmn2 = make_float2(-q.mn, -q.mn); c.r02 = make_float2(r0, r0);
     return c;
 }
@@ -182,7 +182,7 @@ struct DivConsts { float2 nmn2, r02, nu2; };
 
 __device__ __forceinline__ DivConsts div_consts(const QParams& q) {
     DivConsts c;
-    const float r0 = __frcp_rn(q.u);
+    const float r0 = (q.u >= CODEC_U_MIN && q.u <= CODEC_U_MAX) ? rcp_rn_normal(q.u) : 0.0f;   // (unused outside that range)
     c.nmn2 = make_float2(-q.mn, -q.mn); c.r02 = make_float2(r0, r0); c.nu2 = make_float2(-q.u, -q.u);
     return c;
 }

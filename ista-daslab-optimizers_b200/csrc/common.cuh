@@ -55,10 +55,34 @@ template <> struct Elem<uint16_t> {   // bf16 bits
 // One quantisation block's decode constants: u = (max - min) / 15 with one rounding per operation.
 struct QParams { float mn, u; };
 
+// RN(d / 15).  For 2^-100 <= |d| <= 2^100 the quotient is d * RN(1/15) with one residual correction (the
+// residual d - 15 q is exact in an FMA): equal to the IEEE division for every float in that range (checked
+// exhaustively on a CPU), without the division's special-function instruction and its slow-path branch.
+__device__ __forceinline__ float div15_rn(float d) {
+    const float ad = fabsf(d);
+    if (!(ad >= 7.8886091e-31f && ad <= 1.2676506e30f)) return __fdiv_rn(d, 15.0f);   // zero, tiny, huge, NaN
+    const float c = 0.0666666701436042785644531f;                                      // RN(1 / 15)
+    const float q = __fmul_rn(d, c);
+    return __fmaf_rn(__fmaf_rn(-15.0f, q, d), c, q);
+}
+
+// RN(1 / u) for 2^-100 <= u <= 2^100: the approximate reciprocal (within 3 ulp) and two Newton steps give the
+// correctly rounded one for every float in that range but those whose mantissa bits are all ones (checked
+// exhaustively on a CPU, for every start within 3 ulp); those take the library's form.
+__device__ __forceinline__ float rcp_rn_normal(float u) {
+    if ((__float_as_uint(u) & 0x7FFFFFu) == 0x7FFFFFu) return __frcp_rn(u);
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(u));
+    float e = __fmaf_rn(-u, y, 1.0f);
+    y = __fmaf_rn(y, e, y);
+    e = __fmaf_rn(-u, y, 1.0f);
+    return __fmaf_rn(y, e, y);
+}
+
 __device__ __forceinline__ QParams qparams(uint16_t mn_bits, uint16_t mx_bits) {
     QParams q;
     q.mn = bf16_bits_to_f32(mn_bits);
-    q.u = __fdiv_rn(__fsub_rn(bf16_bits_to_f32(mx_bits), q.mn), 15.0f);
+    q.u = div15_rn(__fsub_rn(bf16_bits_to_f32(mx_bits), q.mn));
     return q;
 }
 

@@ -415,7 +415,10 @@ ef_topk_quant_kernel(const mab_tensor* __restrict__ tensors, int n_tensors, int 
                 if ((o & (lanes_per_qb - 1)) == 0) { mn_out[o >> oshift] = mn_b; mx_out[o >> oshift] = mx_b; }
                 const QParams q2 = qparams(mn_b, mx_b);
                 if (cnt >= 8) {
-                    const uint32_t w = encode_octet<true>(a[j], q2);
+                    // the defining form without division instructions (values can lie outside statistics that were
+                    // rounded to bf16: the clamped form); the scalar definition where the step is out of its range
+                    const uint32_t w = (q2.u >= CODEC_U_MIN && q2.u <= CODEC_U_MAX) ? encode_octet_div_f32<true>(a[j], div_consts(q2))
+                                                                                    : encode_octet_exact(a[j], q2, 8);
                     if (vec_e) *reinterpret_cast<uint32_t*>(ef_out + o * 4) = w;
                     else {
 #pragma unroll

@@ -324,7 +324,7 @@ __device__ __forceinline__ void stats_encode_regular(const uint4* tile4, int n_q
             encode_block_exact(row, key, mn_b, mx_b, dst);
             continue;
         }
-        const float r0 = __frcp_rn(q2.u);
+        const float r0 = rcp_rn_normal(q2.u);
         const float2 nmn2 = make_float2(-q2.mn, -q2.mn), r02 = make_float2(r0, r0), nu2 = make_float2(-q2.u, -q2.u);
         uint4 lo4, hi4;
         lo4.x = encode_octet_div(row[0 ^ key], nmn2, r02, nu2);
