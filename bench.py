@@ -552,7 +552,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=10)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='llama3_8b', help='llama3_8b | gpt2_flat | flat_<bf16|f32>_<numel> | sweep')
+    ap.add_argument('--workload', default='llama3_8b', help='llama3_8b | gpt2_flat | flat_<bf16|f32>_<numel> | loose_<one of those> | sweep')
     ap.add_argument('--grad-sets', type=int, default=2, help='distinct pre-generated gradient sets cycled over the steps')
     ap.add_argument('--e2e-steps', type=int, default=5)
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -564,9 +564,24 @@ def main():
     ap.add_argument('--exchange', default='rows', choices=['rows', 'params'],
                     help='N > 1: what the ranks exchange (window rows, or updated parameters)')
     ap.add_argument('--sweep-max-log2', type=int, default=31, help='sweep: largest tensor is 2^this elements')
+    ap.add_argument('--quant-block-size', type=int, default=None,
+                    help='quant_block_size of the headline workload (default 64).  Values that are no power of two in [8, 128] '
+                         'take the path that leaves the residual in the gradient buffers: later steps then see those as gradients, '
+                         'which is fine for timing and profiling a kernel, not for the parameter checksum')
     args = ap.parse_args()
+    if args.quant_block_size is not None:
+        HYPER['quant_block_size'] = args.quant_block_size
     if args.workload == 'sweep':
         sweep(args)
+        return
+    if args.workload.startswith('loose_'):
+        # loose_<workload>: the kernels for quantisation blocks that ignore top-k block borders (quant_block_size
+        # 100000 unless --quant-block-size says otherwise), every step on freshly restored gradients; one GPU
+        assert torch.cuda.is_available(), 'bench.py needs a CUDA device'
+        torch.cuda.set_device(0)
+        rec = loose_blocks_record(workload_spec(args.workload[len('loose_'):]), args, 0, max(1, args.steps),
+                                  qbs=args.quant_block_size or 100000)
+        print(json.dumps({'metric': METRIC, 'unit': UNIT, 'data': 'synthetic', **rec}))
         return
     spec = workload_spec(args.workload)
     if args.impl == 'reference':
