@@ -45,8 +45,7 @@ struct __align__(16) FastSelSmem {
     uint16_t cand_pos[FS_CAND_CAP];       // position in the tile; bit 15 set once selected
     uint16_t cand_ref[FS_CAND_CAP];       // 8 * (index in oct_val) + element, when the compact copy is in use
     uint16_t oct_id[FS_OCT_CAP];          // tile octet of each compact octet
-    int      wcount[SEL_OCTETS * 32];      // candidate octets per (octet row, warp), then their exclusive prefix
-    int      n_oct;
+    int      n_oct, n_cand;               // compact octets / candidates handed out so far
     int      hist[256];
     int      member[32];                  // candidate indices of the members of the final bin
     int      rot[64];                     // rotating counters of the octet-level probes
@@ -122,7 +121,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
 #pragma unroll
     for (int j = 0; j < SEL_OCTETS; ++j) oct_slot[j] = -1;
     // block maximum key
-    if (t == 0) fs.kmax = 0;
+    if (t == 0) { fs.kmax = 0; fs.n_oct = 0; fs.n_cand = 0; }
     __syncthreads();
     {
         const int wm = __reduce_max_sync(0xffffffffu, __float_as_int(tmax));
@@ -145,31 +144,22 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
     int C = 0;
     bool by_octets = !octets;                                  // small k: through the compact octet copy
     if (by_octets) {
-        // slots of the compact copy: (octet row, warp) segments in a fixed order, lanes in order inside
+        // slots of the compact copy: one shared-memory atomic per warp reserves a run for its octets (the order of
+        // the copy does not matter: everything downstream goes by the positions the entries carry)
         unsigned ball[SEL_OCTETS];
+        int tot = 0;
 #pragma unroll
         for (int j = 0; j < SEL_OCTETS; ++j) {
             ball[j] = __ballot_sync(0xffffffffu, omax[j] >= T_lo_f);
-            if (lane == 0) fs.wcount[j * 32 + warp] = __popc(ball[j]);
+            tot += __popc(ball[j]);
         }
-        __syncthreads();
-        if (warp == 0) {
-            int c[SEL_OCTETS], sum = 0;
-#pragma unroll
-            for (int i = 0; i < SEL_OCTETS; ++i) { c[i] = fs.wcount[lane * SEL_OCTETS + i]; sum += c[i]; }
-            int inc = sum;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += v; }
-            int run = inc - sum;
-#pragma unroll
-            for (int i = 0; i < SEL_OCTETS; ++i) { fs.wcount[lane * SEL_OCTETS + i] = run; run += c[i]; }
-            if (lane == 31) fs.n_oct = inc;
-        }
-        __syncthreads();
+        int run = 0;
+        if (lane == 0 && tot) run = atomicAdd(&fs.n_oct, tot);
+        run = __shfl_sync(0xffffffffu, run, 0);
 #pragma unroll
         for (int j = 0; j < SEL_OCTETS; ++j) {
             if ((ball[j] >> lane) & 1u) {
-                const int slot = fs.wcount[j * 32 + warp] + __popc(ball[j] & ((1u << lane) - 1u));
+                const int slot = run + __popc(ball[j] & ((1u << lane) - 1u));
                 if (slot < FS_OCT_CAP) {
                     reinterpret_cast<float4*>(fs.oct_val[slot])[0] = make_float4(a[j][0], a[j][1], a[j][2], a[j][3]);
                     reinterpret_cast<float4*>(fs.oct_val[slot])[1] = make_float4(a[j][4], a[j][5], a[j][6], a[j][7]);
@@ -177,6 +167,7 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
                     oct_slot[j] = slot;
                 }
             }
+            run += __popc(ball[j]);
         }
         __syncthreads();
         const int n_oct = fs.n_oct;
@@ -185,27 +176,37 @@ __device__ __forceinline__ bool fast_select(const float (&a)[SEL_OCTETS][8], con
 #pragma unroll
             for (int j = 0; j < SEL_OCTETS; ++j) oct_slot[j] = -1;
         } else {
-            // one compact octet per thread (FS_OCT_CAP <= SEL_THREADS); read once to count, once to copy
-            int mine = 0;
+            // one compact octet per thread (FS_OCT_CAP <= SEL_THREADS); candidate slots again by one atomic per warp
+            uint32_t mask = 0u;
             if (t < n_oct) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) mine += (fabsf(fs.oct_val[t][e]) >= T_lo_f) ? 1 : 0;
+                for (int e = 0; e < 8; ++e) mask |= (fabsf(fs.oct_val[t][e]) >= T_lo_f) ? (1u << e) : 0u;
             }
-            int at = block_exclusive_scan(mine, sm.scan, C);
-            if (C > FS_CAND_CAP) { MAB_STAT(4, 1); return false; }
+            const int mine = __popc(mask);
+            int incl = mine;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, d); if (lane >= d) incl += v; }
+            int base = 0;
+            if (lane == 31 && incl) base = atomicAdd(&fs.n_cand, incl);
+            base = __shfl_sync(0xffffffffu, base, 31);
+            int at = base + incl - mine;
             if (mine) {
                 const uint32_t o = fs.oct_id[t];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const float ve = fs.oct_val[t][e];
-                    if (fabsf(ve) >= T_lo_f) {
-                        fs.cand_val[at] = ve;
-                        fs.cand_pos[at] = (uint16_t)((o << 3) | e);
-                        fs.cand_ref[at] = (uint16_t)((t << 3) | e);
+                    if (mask & (1u << e)) {
+                        if (at < FS_CAND_CAP) {
+                            fs.cand_val[at] = fs.oct_val[t][e];
+                            fs.cand_pos[at] = (uint16_t)((o << 3) | e);
+                            fs.cand_ref[at] = (uint16_t)((t << 3) | e);
+                        }
                         ++at;
                     }
                 }
             }
+            __syncthreads();
+            C = fs.n_cand;
+            if (C > FS_CAND_CAP) { MAB_STAT(4, 1); return false; }
         }
     }
     if (!by_octets) {
